@@ -1,0 +1,697 @@
+// Tensor-core GEMM for B200 (sm_100a): tcgen05.mma with fp32 accumulators in
+// tensor memory (TMEM), operands staged in shared memory by TMA through a
+// multi-stage mbarrier ring, warp-specialised roles, persistent CTAs.
+//
+// It replaces the reference's WMMA-tiled GEMM family
+// (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:133-286 and :458-509) and
+// the naive kernel behind its C launcher
+// (src/cuda_kernels/sm120_pure_kernels.cu:19-65), and adds the strided-batch
+// form of src/cuda_kernels/sm120_dynamic_shapes.cu:107-183 and the fused
+// bias + activation + cast epilogue.
+//
+// One CTA = 6 warps:
+//   warp 0      TMA producer (one lane): fills the shared-memory ring
+//   warp 1      TMEM allocator; one lane issues tcgen05.mma and the commits
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (32 TMEM lanes per warp),
+//               alpha/scale, beta*C, bias, activation, cast, 16-byte stores
+// The CTA tile is 128 x BN (BN = 64, 128 or 256) and the accumulator is double
+// buffered in TMEM (2*BN columns), so the epilogue of one tile overlaps the
+// main loop of the next.  Tiles are handed out statically (tile = blockIdx.x +
+// i*gridDim.x); there is no split-K and no atomic, so results are bitwise
+// reproducible from run to run.
+//
+// Operand layouts.  Each operand tile in shared memory is a sequence of
+// 128-byte-swizzled atoms exactly as TMA writes them:
+//   K-major operand (K contiguous in memory: A not transposed, B transposed):
+//     one box {BK, rows}: row r at r*128 B, 8-row groups 1024 B apart.
+//   MN-major operand (M or N contiguous: A transposed, B not transposed):
+//     rows*es/128 boxes {128/es, BK}: box j covers 128 bytes of M/N; inside a box
+//     k-row k is at k*128 B.
+// BK is always 128 bytes of K (64 bf16/fp16, 128 fp8, 32 tf32), i.e. 4 MMA
+// K-steps of 32 bytes.
+//
+// Every wait on an mbarrier is bounded by a wall-clock limit.  A role whose
+// wait runs out records a code in g_sm120_status, raises the CTA's abort flag
+// and leaves; the other roles see the flag in their own wait loops; the CTA then
+// waits (bounded) for its TMA copies and MMAs in flight, frees its TMEM and
+// returns normally.
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <atomic>
+
+#include "gemm_common.h"
+
+namespace sm120 {
+
+// status word 0: first timeout code seen (role<<28 | barrier kind<<24 | CTA),
+// word 1: number of CTAs that aborted.
+__device__ unsigned int g_sm120_status[4];
+
+enum : int { KIND_F16 = 0, KIND_F8 = 1, KIND_TF32 = 2 };
+
+constexpr int BM = 128;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 8;
+
+struct TcParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, k_blocks, num_tiles;
+    uint32_t idesc;
+    int a_mn_major, b_mn_major;
+    int a_batched, b_batched;
+    void* C;
+    long long ldc, stride_c;
+    int out_dtype;
+    int c_vec_ok;                   // C rows may be written with 16-byte stores
+    const void* bias;
+    int bias_dtype;
+    int bias_vec_ok;                // bias is fp32 and 16-byte aligned
+    float alpha, beta;
+    const float* scale_a_dev;
+    const float* scale_b_dev;
+    int activation;
+    int debug_skip_kblock;          // >= 0: the producer never fills this k-block of its first tile (wait-limit test)
+    unsigned long long wait_limit_ns;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+// Tiled TMA load of one 3-D box into this CTA's shared memory; completion is
+// signalled as transaction bytes on `bar`.  No cluster multicast.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (KIND == KIND_F16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (KIND == KIND_F8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+
+// 32 TMEM lanes x 32 consecutive 32-bit columns -> 32 registers per thread
+// (thread i of the warp owns lane i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05 form, version 1, 128-byte swizzle):
+//   bits  0..13  start address >> 4
+//   bits 16..29  leading-dimension byte offset >> 4
+//   bits 32..45  stride-dimension byte offset >> 4
+//   bits 46..47  descriptor version (1 on sm_100)
+//   bits 61..63  layout type (2 = 128-byte swizzle)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFF);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// ---------------------------------------------------------------------------
+// Bounded wait.  `code` identifies role and barrier for the status word.
+// ---------------------------------------------------------------------------
+struct WaitCtx {
+    volatile uint32_t* abort_flag;
+    unsigned long long limit_ns;
+};
+
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code, bool watch_abort) {
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0u) {
+            if (watch_abort && *w.abort_flag != 0u) return false;
+            if (global_timer_ns() - t0 > w.limit_ns) {
+                *w.abort_flag = 1u;
+                atomicCAS(&g_sm120_status[0], 0u, code | (blockIdx.x & 0xFFFFFFu));
+                atomicAdd(&g_sm120_status[1], 1u);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code, bool watch_abort = true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, w, code, watch_abort);
+}
+
+__device__ __forceinline__ void decode_tile(int tile, const TcParams& p, int& bz, int& tm, int& tn) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    bz = tile / per_batch;
+    const int t = tile - bz * per_batch;
+    const int group_span = GROUP_M * p.tiles_n;
+    const int g = t / group_span;
+    const int first_m = g * GROUP_M;
+    const int gm = min(p.tiles_m - first_m, GROUP_M);
+    const int r = t - g * group_span;
+    tm = first_m + r % gm;
+    tn = r / gm;
+}
+
+// Epilogue for 32 consecutive columns of one row held in registers.
+__device__ __forceinline__ void epilogue_row32(const TcParams& p, float alpha, uint32_t (&acc)[32], int bz, int row, int col0, bool row_ok) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[j]);
+
+    const int ncols = min(32, p.N - col0);
+    const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
+
+    if (p.beta != 0.0f && row_ok) {
+        for (int j = 0; j < ncols; ++j) v[j] += p.beta * load_as_float(p.C, off + j, p.out_dtype);
+    }
+    if (p.bias != nullptr) {
+        if (ncols == 32 && p.bias_vec_ok) {
+            const float4* b4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 b = __ldg(b4 + j);
+                v[4 * j + 0] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
+            }
+        } else {
+            for (int j = 0; j < ncols; ++j) v[j] += load_as_float(p.bias, col0 + j, p.bias_dtype);
+        }
+    }
+    if (p.activation != SM120_ACTIVATION_NONE) {
+        const int act = p.activation;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_activation(v[j], act);
+    }
+    if (!row_ok) return;
+
+    if (ncols == 32 && p.c_vec_ok) {
+        if (p.out_dtype == SM120_DTYPE_FLOAT32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.C) + off);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+            uint32_t packed[16];
+            if (p.out_dtype == SM120_DTYPE_BFLOAT16) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                    packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                    packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            }
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.C) + off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        }
+    } else {
+        for (int j = 0; j < ncols; ++j) store_from_float(p.C, off + j, p.out_dtype, v[j]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+template <int KIND, int BN, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                          const __grid_constant__ CUtensorMap tmap_b,
+                          const TcParams p) {
+    constexpr int ES = (KIND == KIND_F16) ? 2 : (KIND == KIND_F8 ? 1 : 4);
+    constexpr int EPB = 128 / ES;          // elements per 128 bytes
+    constexpr int BK = EPB;                // K elements per stage
+    constexpr int UMMA_K = 32 / ES;        // K elements per tcgen05.mma
+    constexpr uint32_t A_BYTES = BM * 128;
+    constexpr uint32_t B_BYTES = BN * 128;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t MN_BOX_BYTES = BK * 128;   // one {128 B of M/N, BK} box
+    constexpr uint32_t TMEM_COLS = 2 * BN;        // 128, 256 or 512: a power of two >= 32
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    const uint32_t full_bar = smem_u32(bars);                       // [STAGES]
+    const uint32_t empty_bar = smem_u32(bars + STAGES);             // [STAGES]
+    const uint32_t acc_full_bar = smem_u32(bars + 2 * STAGES);      // [2]
+    const uint32_t acc_empty_bar = smem_u32(bars + 2 * STAGES + 2); // [2]
+    const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);     // [1]
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+    volatile uint32_t* abort_flag = tmem_holder + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const WaitCtx wctx{abort_flag, p.wait_limit_ns};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar + 8 * b, 1);
+            mbar_init(acc_empty_bar + 8 * b, 4);   // one arrival per epilogue warp
+        }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0u;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            long long issued = 0;
+            bool ok = true;
+            bool first_tile = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                int bz, tm, tn;
+                decode_tile(tile, p, bz, tm, tn);
+                const int za = p.a_batched ? bz : 0;
+                const int zb = p.b_batched ? bz : 0;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (first_tile && kb == p.debug_skip_kblock) { ok = false; break; }
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u)) { ok = false; break; }
+                    const uint32_t fb = full_bar + 8 * stage;
+                    mbar_expect_tx(fb, STAGE_BYTES);
+                    const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint32_t b_dst = a_dst + A_BYTES;
+                    const int k0 = kb * BK;
+                    if (!p.a_mn_major) {
+                        tma_load_3d(a_dst, &tmap_a, fb, k0, tm * BM, za);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / EPB; ++j)
+                            tma_load_3d(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, tm * BM + j * EPB, k0, za);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_3d(b_dst, &tmap_b, fb, k0, tn * BN, zb);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / EPB; ++j)
+                            tma_load_3d(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, tn * BN + j * EPB, k0, zb);
+                    }
+                    ++issued;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                first_tile = false;
+            }
+            // Before leaving, wait (bounded) until every copy this thread issued has
+            // landed: immediate on the normal path, where the MMA role consumed them all.
+            {
+                const long long first = issued > STAGES ? issued - STAGES : 0;
+                for (long long i = first; i < issued; ++i) {
+                    const uint32_t s = static_cast<uint32_t>(i % STAGES);
+                    const uint32_t par = static_cast<uint32_t>((i / STAGES) & 1);
+                    mbar_wait(full_bar + 8 * s, par, wctx, 0x13000000u, false);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            bool issued_any = false;
+            int local = 0;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+                const uint32_t buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                if (!mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar + 8 * stage, phase, wctx, 0x22000000u)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_base = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint32_t b_base = a_base + A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t a_desc = p.a_mn_major
+                            ? make_smem_desc(a_base + kk * UMMA_K * 128, MN_BOX_BYTES, 1024)
+                            : make_smem_desc(a_base + kk * 32, 16, 1024);
+                        const uint64_t b_desc = p.b_mn_major
+                            ? make_smem_desc(b_base + kk * UMMA_K * 128, MN_BOX_BYTES, 1024)
+                            : make_smem_desc(b_base + kk * 32, 16, 1024);
+                        umma_ss<KIND>(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    issued_any = true;
+                    umma_commit(empty_bar + 8 * stage);     // frees the stage when these MMAs retire
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(acc_full_bar + 8 * buf);  // accumulator complete
+            }
+            if (*abort_flag != 0u && issued_any) {
+                umma_commit(drain_bar);
+                mbar_wait(drain_bar, 0u, wctx, 0x23000000u, false);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int lane_group = warp & 3;       // TMEM lanes [32*lane_group, +32) belong to this warp
+        float alpha = p.alpha;
+        if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
+        if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
+        bool ok = true;
+        int local = 0;
+        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+            int bz, tm, tn;
+            decode_tile(tile, p, bz, tm, tn);
+            const uint32_t buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const int row = tm * BM + lane_group * 32 + lane;
+            const bool row_ok = row < p.M;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = tn * BN + c * 32;
+                if (col0 >= p.N) break;          // warp-uniform
+                uint32_t acc[32];
+                __syncwarp();
+                tmem_ld_32x32(t_row + c * 32, acc);
+                tmem_ld_wait();
+                epilogue_row32(p, alpha, acc, bz, row, col0, row_ok);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buf);
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static std::atomic<EncodeTiledFn> cached{nullptr};
+    EncodeTiledFn fn = cached.load(std::memory_order_acquire);
+    if (fn != nullptr) return fn;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || sym == nullptr) {
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+    cached.store(fn, std::memory_order_release);
+    return fn;
+}
+
+static CUtensorMapDataType tmap_dtype(int dtype) {
+    switch (dtype) {
+        case SM120_DTYPE_FLOAT16:  return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        case SM120_DTYPE_BFLOAT16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        case SM120_DTYPE_FP8_E4M3: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+        default:                   return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    }
+}
+
+// 3-D map over a stored matrix: `inner` contiguous elements per row, `outer`
+// rows `pitch` elements apart, `nbatch` matrices `bstride` elements apart.
+static bool encode_operand(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch,
+                           int64_t pitch, int64_t bstride, uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const uint64_t es = static_cast<uint64_t>(dtype_size(dtype));
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), static_cast<cuuint64_t>(nbatch)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch) * es, static_cast<cuuint64_t>(bstride) * es};
+    cuuint32_t box[3] = {box_inner, box_outer, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, tmap_dtype(dtype), 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool tc_supported(const GemmProblem& p, const char** why) {
+    auto no = [&](const char* w) { if (why) *why = w; return false; };
+    if (p.in_dtype != SM120_DTYPE_FLOAT16 && p.in_dtype != SM120_DTYPE_BFLOAT16 && p.in_dtype != SM120_DTYPE_FP8_E4M3)
+        return no("input dtype has no tensor-core path");
+    const int64_t es = dtype_size(p.in_dtype);
+    if (p.K < 1) return no("K < 1");
+    if (!aligned16(p.A) || !aligned16(p.B)) return no("A or B is not 16-byte aligned");
+    if ((p.lda * es) % 16 != 0 || (p.ldb * es) % 16 != 0) return no("row pitch of A or B is not a multiple of 16 bytes");
+    if (p.batch > 1) {
+        if (p.stride_a != 0 && (p.stride_a * es) % 16 != 0) return no("batch stride of A is not a multiple of 16 bytes");
+        if (p.stride_b != 0 && (p.stride_b * es) % 16 != 0) return no("batch stride of B is not a multiple of 16 bytes");
+    }
+    if (p.M >= (1ll << 31) || p.N >= (1ll << 31) || p.K >= (1ll << 31) || p.batch >= (1ll << 31)) return no("extent >= 2^31");
+    const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + 63) / 64) * p.batch;
+    if (tiles >= (1ll << 31)) return no("too many tiles");
+    // TMA limits: strides below 2^40 bytes
+    if (p.lda * es >= (1ll << 40) || p.ldb * es >= (1ll << 40) || p.stride_a * es >= (1ll << 40) || p.stride_b * es >= (1ll << 40))
+        return no("stride >= 2^40 bytes");
+    return true;
+}
+
+template <int KIND, int BN, int STAGES>
+static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& tp, int grid, int device,
+                                  cudaStream_t stream) {
+    constexpr size_t SMEM = static_cast<size_t>(STAGES) * (BM * 128 + BN * 128) + 1024 /*align*/ + 256 /*barriers*/;
+    static_assert(SMEM <= 232448, "shared memory budget exceeded");
+    static_assert(SMEM > 116224, "one CTA per SM is assumed: shared memory must exceed half of an SM's");
+    static std::atomic<uint64_t> attr_done{0};   // one bit per device
+    auto kern = sm120_gemm_tcgen05_kernel<KIND, BN, STAGES>;
+    const uint64_t bit = 1ull << (device & 63);
+    if ((attr_done.load(std::memory_order_acquire) & bit) == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM));
+        if (e != cudaSuccess) return e;
+        attr_done.fetch_or(bit, std::memory_order_release);
+    }
+    kern<<<grid, NUM_THREADS, SMEM, stream>>>(ta, tb, tp);
+    return cudaGetLastError();
+}
+
+static std::atomic<int> g_debug_skip_kblock{-1};
+void tc_set_debug_skip_kblock(int kb) { g_debug_skip_kblock.store(kb); }
+
+cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char** kernel_name) {
+    const int es = dtype_size(p.in_dtype);
+    const int epb = 128 / es;
+    const int bk = epb;
+    const int kind = (p.in_dtype == SM120_DTYPE_FP8_E4M3) ? KIND_F8 : KIND_F16;
+
+    // Tile width: the widest BN that still gives every SM a tile; level 0 keeps 128.
+    const int64_t tiles_m = (p.M + BM - 1) / BM;
+    auto tiles_for = [&](int bn) { return tiles_m * ((p.N + bn - 1) / bn) * p.batch; };
+    int bn = 64;
+    if (p.optimization_level == 0) {
+        bn = p.N > 64 ? 128 : 64;
+    } else {
+        const int wide[2] = {256, 128};
+        for (int cand : wide) {
+            if (p.N > cand / 2 && tiles_for(cand) >= p.sm_count) { bn = cand; break; }
+        }
+    }
+
+    TcParams tp{};
+    tp.M = static_cast<int>(p.M); tp.N = static_cast<int>(p.N); tp.K = static_cast<int>(p.K);
+    tp.batch = static_cast<int>(p.batch);
+    tp.tiles_m = static_cast<int>(tiles_m);
+    tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
+    tp.k_blocks = static_cast<int>((p.K + bk - 1) / bk);
+    tp.num_tiles = static_cast<int>(tiles_for(bn));
+    tp.a_mn_major = p.transpose_a ? 1 : 0;     // stored [K,M]: M contiguous
+    tp.b_mn_major = p.transpose_b ? 0 : 1;     // stored [K,N]: N contiguous
+    tp.a_batched = (p.batch > 1 && p.stride_a != 0) ? 1 : 0;
+    tp.b_batched = (p.batch > 1 && p.stride_b != 0) ? 1 : 0;
+    tp.C = p.C; tp.ldc = p.ldc; tp.stride_c = p.stride_c; tp.out_dtype = p.out_dtype;
+    const int out_es = dtype_size(p.out_dtype);
+    tp.c_vec_ok = (aligned16(p.C) && (p.ldc * out_es) % 16 == 0 && (p.stride_c * out_es) % 16 == 0) ? 1 : 0;
+    tp.bias = p.bias; tp.bias_dtype = p.bias_dtype;
+    tp.bias_vec_ok = (p.bias != nullptr && p.bias_dtype == SM120_DTYPE_FLOAT32 && aligned16(p.bias)) ? 1 : 0;
+    tp.alpha = p.alpha * p.inv_scale; tp.beta = p.beta;
+    tp.scale_a_dev = p.scale_a_dev; tp.scale_b_dev = p.scale_b_dev;
+    tp.activation = p.activation;
+    tp.debug_skip_kblock = g_debug_skip_kblock.load();
+    tp.wait_limit_ns = wait_limit_ns;
+
+    // Instruction descriptor (tcgen05.mma kind::f16 / kind::f8f6f4):
+    //   bits 4..5 accumulator format (1 = f32), 7..9 A format, 10..12 B format
+    //   (kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3), 15 / 16 = A / B is
+    //   MN-major, 17..22 = N >> 3, 24..28 = M >> 4.
+    const uint32_t fmt = (p.in_dtype == SM120_DTYPE_BFLOAT16) ? 1u : 0u;
+    tp.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tp.a_mn_major) << 15) |
+               (static_cast<uint32_t>(tp.b_mn_major) << 16) | (static_cast<uint32_t>(bn >> 3) << 17) |
+               (static_cast<uint32_t>(BM >> 4) << 24);
+
+    CUtensorMap ta, tb;
+    const int64_t nb_a = tp.a_batched ? p.batch : 1;
+    const int64_t nb_b = tp.b_batched ? p.batch : 1;
+    bool ok;
+    if (!tp.a_mn_major) {
+        const int64_t bs = tp.a_batched ? p.stride_a : p.M * p.lda;
+        ok = encode_operand(&ta, p.A, p.in_dtype, p.K, p.M, nb_a, p.lda, bs, bk, BM);
+    } else {
+        const int64_t bs = tp.a_batched ? p.stride_a : p.K * p.lda;
+        ok = encode_operand(&ta, p.A, p.in_dtype, p.M, p.K, nb_a, p.lda, bs, epb, bk);
+    }
+    if (!ok) return cudaErrorInvalidValue;
+    if (!tp.b_mn_major) {
+        const int64_t bs = tp.b_batched ? p.stride_b : p.N * p.ldb;
+        ok = encode_operand(&tb, p.B, p.in_dtype, p.K, p.N, nb_b, p.ldb, bs, bk, bn);
+    } else {
+        const int64_t bs = tp.b_batched ? p.stride_b : p.K * p.ldb;
+        ok = encode_operand(&tb, p.B, p.in_dtype, p.N, p.K, nb_b, p.ldb, bs, epb, bk);
+    }
+    if (!ok) return cudaErrorInvalidValue;
+
+    const int grid = tp.num_tiles < p.sm_count ? tp.num_tiles : p.sm_count;
+
+#define SM120_TC_CASE(KIND_, BN_, ST_, NAME_)                                                   \
+    do {                                                                                        \
+        if (kernel_name) *kernel_name = NAME_;                                                  \
+        return launch_variant<KIND_, BN_, ST_>(ta, tb, tp, grid, p.device, p.stream);            \
+    } while (0)
+
+    if (kind == KIND_F16) {
+        const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
+        if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
+        if (bn == 128) SM120_TC_CASE(KIND_F16, 128, 6, bf ? "tc_bf16_128x128x64_s6" : "tc_f16_128x128x64_s6");
+        SM120_TC_CASE(KIND_F16, 64, 8, bf ? "tc_bf16_128x64x64_s8" : "tc_f16_128x64x64_s8");
+    } else {
+        if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, "tc_e4m3_128x256x128_s4");
+        if (bn == 128) SM120_TC_CASE(KIND_F8, 128, 6, "tc_e4m3_128x128x128_s6");
+        SM120_TC_CASE(KIND_F8, 64, 8, "tc_e4m3_128x64x128_s8");
+    }
+#undef SM120_TC_CASE
+}
+
+cudaError_t tc_read_status(unsigned int* status, int clear) {
+    unsigned int host[4] = {0, 0, 0, 0};
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpyFromSymbol(host, g_sm120_status, sizeof(host));
+    if (e != cudaSuccess) return e;
+    if (status) { status[0] = host[0]; }
+    if (clear && (host[0] != 0 || host[1] != 0)) {
+        unsigned int zero[4] = {0, 0, 0, 0};
+        e = cudaMemcpyToSymbol(g_sm120_status, zero, sizeof(zero));
+    }
+    return e;
+}
+
+}  // namespace sm120

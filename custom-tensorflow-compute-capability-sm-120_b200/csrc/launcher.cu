@@ -1,0 +1,269 @@
+// C ABI of the SM120 matmul op for B200: argument validation, defaults, choice
+// of kernel family, and the entry points declared in include/sm120_c_interface.h.
+// Mirrors the role of src/cuda_kernels/sm120_c_interface.cu:32-60 in the
+// reference (grid choice + dtype dispatch + cudaGetLastError()).
+//
+// The launchers hold no mutable global state except monotonic counters and
+// per-device caches of immutable device attributes, so they may be called
+// concurrently from any number of host threads.
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <atomic>
+
+#include "gemm_common.h"
+
+namespace sm120 {
+
+void tc_set_debug_skip_kblock(int kb);
+
+namespace {
+
+constexpr int MAX_DEVICES = 64;
+
+struct DeviceInfo {
+    std::atomic<int> state{0};   // 0 unknown, 1 supported, 2 unsupported
+    std::atomic<int> sm_count{0};
+};
+DeviceInfo g_devices[MAX_DEVICES];
+
+std::atomic<uint64_t> g_launch_count{0};
+std::atomic<uint64_t> g_wait_limit_ns{0};   // 0 = not initialised yet
+thread_local const char* t_last_kernel = "";
+
+uint64_t wait_limit_ns() {
+    uint64_t v = g_wait_limit_ns.load(std::memory_order_relaxed);
+    if (v != 0) return v;
+    uint64_t ms = 2000;
+    const char* env = getenv("SM120_WAIT_LIMIT_MS");
+    if (env != nullptr && env[0] != '\0') {
+        const long parsed = strtol(env, nullptr, 10);
+        if (parsed > 0) ms = static_cast<uint64_t>(parsed);
+    }
+    v = ms * 1000000ull;
+    g_wait_limit_ns.store(v, std::memory_order_relaxed);
+    return v;
+}
+
+// Returns cudaSuccess and fills sm_count when `device` is a compute-capability 10.x part.
+cudaError_t query_device(int device, int* sm_count) {
+    if (device < 0 || device >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    DeviceInfo& d = g_devices[device];
+    int st = d.state.load(std::memory_order_acquire);
+    if (st == 0) {
+        int major = 0, sms = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return e;
+        d.sm_count.store(sms, std::memory_order_relaxed);
+        st = (major == 10) ? 1 : 2;
+        d.state.store(st, std::memory_order_release);
+    }
+    if (st != 1) return cudaErrorInvalidDevice;
+    *sm_count = d.sm_count.load(std::memory_order_relaxed);
+    return cudaSuccess;
+}
+
+bool valid_dtype(int d) { return d >= SM120_DTYPE_FLOAT32 && d <= SM120_DTYPE_FP8_E4M3; }
+
+// Checks every field that can be checked without touching the device and
+// resolves defaults.  Returns cudaErrorInvalidValue for a rejected descriptor.
+cudaError_t resolve(const SM120GemmDesc* d, GemmProblem* out) {
+    if (d == nullptr) return cudaErrorInvalidValue;
+    if (d->struct_size != sizeof(SM120GemmDesc)) return cudaErrorInvalidValue;
+    if (!valid_dtype(d->in_dtype) || !valid_dtype(d->out_dtype)) return cudaErrorInvalidValue;
+    if (d->out_dtype == SM120_DTYPE_FP8_E4M3) return cudaErrorInvalidValue;
+    if (d->M < 0 || d->N < 0 || d->K < 0 || d->batch < 1) return cudaErrorInvalidValue;
+    if (d->activation < SM120_ACTIVATION_NONE || d->activation > SM120_ACTIVATION_GELU_ERF) return cudaErrorInvalidValue;
+    if (d->path < SM120_PATH_AUTO || d->path > SM120_PATH_SIMT) return cudaErrorInvalidValue;
+    if (d->optimization_level < 0 || d->optimization_level > 2) return cudaErrorInvalidValue;
+    if (d->bias != nullptr) {
+        if (d->bias_dtype != SM120_DTYPE_FLOAT32 && d->bias_dtype != SM120_DTYPE_FLOAT16 && d->bias_dtype != SM120_DTYPE_BFLOAT16)
+            return cudaErrorInvalidValue;
+    }
+    if (d->scale_a < 0.0f || d->scale_b < 0.0f) return cudaErrorInvalidValue;
+
+    GemmProblem p{};
+    p.M = d->M; p.N = d->N; p.K = d->K; p.batch = d->batch;
+    p.transpose_a = d->transpose_a != 0; p.transpose_b = d->transpose_b != 0;
+    const int64_t a_row = p.transpose_a ? p.M : p.K;     // stored row length of A
+    const int64_t a_rows = p.transpose_a ? p.K : p.M;
+    const int64_t b_row = p.transpose_b ? p.K : p.N;
+    const int64_t b_rows = p.transpose_b ? p.N : p.K;
+    p.lda = d->lda != 0 ? d->lda : a_row;
+    p.ldb = d->ldb != 0 ? d->ldb : b_row;
+    p.ldc = d->ldc != 0 ? d->ldc : p.N;
+    if (p.lda < a_row || p.ldb < b_row || p.ldc < p.N) return cudaErrorInvalidValue;
+    if (d->stride_a < 0 || d->stride_b < 0 || d->stride_c < 0) return cudaErrorInvalidValue;
+    p.stride_a = d->stride_a; p.stride_b = d->stride_b; p.stride_c = d->stride_c;
+    if (p.batch > 1) {
+        // C entries must not overlap; A and B may broadcast with stride 0
+        if (p.stride_c < (p.M > 0 ? (p.M - 1) * p.ldc + p.N : 0)) return cudaErrorInvalidValue;
+        if (p.stride_a != 0 && p.stride_a < (a_rows > 0 ? (a_rows - 1) * p.lda + a_row : 0)) return cudaErrorInvalidValue;
+        if (p.stride_b != 0 && p.stride_b < (b_rows > 0 ? (b_rows - 1) * p.ldb + b_row : 0)) return cudaErrorInvalidValue;
+    }
+    const bool empty_out = (p.M == 0 || p.N == 0);
+    if (!empty_out) {
+        if (d->C == nullptr) return cudaErrorInvalidValue;
+        if (p.K > 0 && (d->A == nullptr || d->B == nullptr)) return cudaErrorInvalidValue;
+    }
+    p.A = d->A; p.B = d->B; p.C = d->C; p.bias = d->bias;
+    p.in_dtype = d->in_dtype; p.out_dtype = d->out_dtype; p.bias_dtype = d->bias_dtype;
+    p.alpha = d->alpha; p.beta = d->beta;
+    const float sa = d->scale_a == 0.0f ? 1.0f : d->scale_a;
+    const float sb = d->scale_b == 0.0f ? 1.0f : d->scale_b;
+    p.inv_scale = 1.0f / (sa * sb);
+    p.scale_a_dev = d->scale_a_dev; p.scale_b_dev = d->scale_b_dev;
+    p.activation = d->activation;
+    p.optimization_level = d->optimization_level;
+    p.stream = d->stream;
+    *out = p;
+    return cudaSuccess;
+}
+
+cudaError_t launch_resolved(GemmProblem& p, int path) {
+    if (p.M == 0 || p.N == 0) return cudaSuccess;    // nothing to write
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    int sms = 0;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    p.device = device;
+    p.sm_count = sms;
+
+    const char* why = nullptr;
+    const bool tc_ok = tc_supported(p, &why);
+    const char* name = "";
+    if (path == SM120_PATH_TENSOR_CORE && !tc_ok) return cudaErrorInvalidValue;
+    if (path != SM120_PATH_SIMT && tc_ok) {
+        e = tc_launch(p, wait_limit_ns(), &name);
+    } else {
+        e = simt_launch(p, &name);
+    }
+    if (e == cudaSuccess) {
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+        t_last_kernel = name;
+    }
+    return e;
+}
+
+}  // namespace
+}  // namespace sm120
+
+using namespace sm120;
+
+extern "C" {
+
+void sm120_gemm_desc_init(SM120GemmDesc* desc) {
+    if (desc == nullptr) return;
+    memset(desc, 0, sizeof(*desc));
+    desc->struct_size = sizeof(SM120GemmDesc);
+    desc->batch = 1;
+    desc->alpha = 1.0f;
+    desc->beta = 0.0f;
+    desc->scale_a = 1.0f;
+    desc->scale_b = 1.0f;
+    desc->activation = SM120_ACTIVATION_NONE;
+    desc->path = SM120_PATH_AUTO;
+    desc->optimization_level = 1;
+}
+
+cudaError_t sm120_launch_matmul_ex(const SM120GemmDesc* desc) {
+    GemmProblem p;
+    cudaError_t e = resolve(desc, &p);
+    if (e != cudaSuccess) return e;
+    return launch_resolved(p, desc->path);
+}
+
+cudaError_t sm120_launch_matmul(const void* A, const void* B, void* C, int M, int N, int K, float alpha, float beta,
+                                SM120DataType dtype, cudaStream_t stream) {
+    // the reference launcher knows FLOAT32 and FLOAT16 and rejects the rest; BFLOAT16 is added, FP8 has no
+    // same-type output and is rejected here
+    if (dtype != SM120_DTYPE_FLOAT32 && dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    SM120GemmDesc d;
+    sm120_gemm_desc_init(&d);
+    d.A = A; d.B = B; d.C = C;
+    d.M = M; d.N = N; d.K = K;
+    d.alpha = alpha; d.beta = beta;
+    d.in_dtype = dtype; d.out_dtype = dtype;
+    d.stream = stream;
+    return sm120_launch_matmul_ex(&d);
+}
+
+void launch_sm120_matmul(const float* A, const float* B, float* C, int M, int N, int K, cudaStream_t stream) {
+    (void)sm120_launch_matmul(A, B, C, M, N, K, 1.0f, 0.0f, SM120_DTYPE_FLOAT32, stream);
+}
+
+cudaError_t sm120_launch_matmul_grad_a(const void* grad_c, const void* B, void* grad_a, int M, int N, int K, float alpha,
+                                       SM120DataType dtype, cudaStream_t stream) {
+    if (dtype != SM120_DTYPE_FLOAT32 && dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    // grad_a[M,K] = grad_c[M,N] * B[K,N]^T : a GEMM with inner dimension N and B read transposed
+    SM120GemmDesc d;
+    sm120_gemm_desc_init(&d);
+    d.A = grad_c; d.B = B; d.C = grad_a;
+    d.M = M; d.N = K; d.K = N;
+    d.transpose_b = 1;
+    d.alpha = alpha;
+    d.in_dtype = dtype; d.out_dtype = dtype;
+    d.stream = stream;
+    return sm120_launch_matmul_ex(&d);
+}
+
+cudaError_t sm120_launch_matmul_grad_b(const void* A, const void* grad_c, void* grad_b, int M, int N, int K, float alpha,
+                                       SM120DataType dtype, cudaStream_t stream) {
+    if (dtype != SM120_DTYPE_FLOAT32 && dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    // grad_b[K,N] = A[M,K]^T * grad_c[M,N] : a GEMM with inner dimension M and A read transposed
+    SM120GemmDesc d;
+    sm120_gemm_desc_init(&d);
+    d.A = A; d.B = grad_c; d.C = grad_b;
+    d.M = K; d.N = N; d.K = M;
+    d.transpose_a = 1;
+    d.alpha = alpha;
+    d.in_dtype = dtype; d.out_dtype = dtype;
+    d.stream = stream;
+    return sm120_launch_matmul_ex(&d);
+}
+
+bool sm120_is_supported(int device_id) {
+    int sms = 0;
+    return query_device(device_id, &sms) == cudaSuccess;
+}
+
+const char* sm120_get_error_string(cudaError_t error) { return cudaGetErrorString(error); }
+
+cudaError_t sm120_get_kernel_status(int device_id, unsigned int* status, int clear) {
+    if (status == nullptr) return cudaErrorInvalidValue;
+    int prev = 0;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev != device_id) {
+        e = cudaSetDevice(device_id);
+        if (e != cudaSuccess) return e;
+    }
+    e = tc_read_status(status, clear);
+    if (prev != device_id) cudaSetDevice(prev);
+    return e;
+}
+
+void sm120_set_wait_limit_ms(unsigned int ms) {
+    if (ms == 0) ms = 1;
+    g_wait_limit_ns.store(static_cast<uint64_t>(ms) * 1000000ull, std::memory_order_relaxed);
+}
+
+uint64_t sm120_get_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+
+const char* sm120_get_last_kernel_name(void) { return t_last_kernel; }
+
+// Test hook, not declared in the public header: the TMA producer of every CTA
+// stops before filling k-block `kb` of its first tile, so the consumer's bounded
+// wait runs out and the status word is set.  kb < 0 switches the hook off.
+void sm120_debug_skip_kblock(int kb) { tc_set_debug_skip_kblock(kb); }
+
+}  // extern "C"

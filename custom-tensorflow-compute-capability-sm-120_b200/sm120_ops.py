@@ -1,0 +1,519 @@
+"""Python API of the SM120 matmul op, B200 build.
+
+Same public names, arguments and error behaviour as the reference's
+``python/sm120_ops.py`` for the matmul path (``advanced_matmul`` :142-217,
+``SM120Config`` :108-139, ``is_sm120_available`` :41-63, ``benchmark_operation``
+:448-490, ``optimized_dense`` :494-552), with two deliberate differences:
+
+* tensors are ``torch`` CUDA tensors (TensorFlow is not part of this build);
+  host arrays (numpy or CPU torch tensors) are also accepted and are copied to
+  the device, multiplied there and copied back;
+* there is NO fallback to a stock or CPU matmul.  Where the reference warns and
+  calls ``tf.linalg.matmul`` (:203-213) this module raises.
+
+The computation itself happens in ``_sm120_ops.so`` through the C ABI
+(``sm120_launch_matmul_ex``); this file only validates, allocates the output
+with the caller's framework allocator (torch) and passes pointers and the
+current CUDA stream, which is what ``SM120MatMulOp<T>::Compute`` does in the
+reference (src/tensorflow_ops/sm120_ops_fixed.cc:111-150).
+"""
+from __future__ import annotations
+
+import ctypes
+import time
+import warnings
+from typing import Any, Callable, Dict, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from . import _binding as _b
+
+try:
+    import ml_dtypes as _ml
+except Exception:  # pragma: no cover - ml_dtypes ships with the image
+    _ml = None
+
+
+class InvalidArgumentError(ValueError):
+    """Stands in for ``tf.errors.InvalidArgumentError`` (incompatible shapes)."""
+
+
+class UnimplementedError(RuntimeError):
+    """Stands in for ``tf.errors.UnimplementedError``
+    (python/sm120_ops.py:215-217: SM120 operations not available)."""
+
+
+class InternalError(RuntimeError):
+    """Stands in for ``errors::Internal`` raised by the OpKernel when the launcher
+    fails (src/tensorflow_ops/sm120_ops_fixed.cc:145-146)."""
+
+
+try:
+    _b.load_library()
+    _SM120_AVAILABLE = True
+except Exception as _e:  # same warning site as python/sm120_ops.py:33-38, but nothing falls back later
+    warnings.warn(f"SM120 operations library not found: {_e}. SM120 operations will raise.")
+    _SM120_AVAILABLE = False
+
+
+_TORCH_TO_SM120 = {
+    torch.float32: _b.DTYPE_FLOAT32,
+    torch.float16: _b.DTYPE_FLOAT16,
+    torch.bfloat16: _b.DTYPE_BFLOAT16,
+    torch.float8_e4m3fn: _b.DTYPE_FP8_E4M3,
+}
+
+_ACTIVATIONS = {
+    None: _b.ACT_NONE, "linear": _b.ACT_NONE, "none": _b.ACT_NONE,
+    "relu": _b.ACT_RELU, "leaky_relu": _b.ACT_LEAKY_RELU, "elu": _b.ACT_ELU, "selu": _b.ACT_SELU,
+    "gelu": _b.ACT_GELU_ERF, "gelu_erf": _b.ACT_GELU_ERF, "gelu_tanh": _b.ACT_GELU_TANH,
+    "swish": _b.ACT_SWISH, "silu": _b.ACT_SWISH, "mish": _b.ACT_MISH, "tanh": _b.ACT_TANH,
+    "sigmoid": _b.ACT_SIGMOID,
+}
+
+
+def activation_code(activation: Union[None, str, int]) -> int:
+    """Epilogue code for a Keras-style activation name.  ``"gelu"`` is the exact
+    (erf) GELU, as in Keras; ``"gelu_tanh"`` is the reference's C-interface GELU."""
+    if isinstance(activation, int):
+        if not (-1 <= activation <= 9):
+            raise ValueError(f"unknown activation code {activation}")
+        return activation
+    key = activation.lower() if isinstance(activation, str) else activation
+    if key not in _ACTIVATIONS:
+        raise ValueError(f"activation {activation!r} is not implemented by the fused epilogue")
+    return _ACTIVATIONS[key]
+
+
+def is_sm120_available() -> bool:
+    """True when the library is loaded and a supported GPU is visible.  The
+    reference requires compute capability >= (12, 0) (python/sm120_ops.py:56);
+    this build requires 10.x (B200)."""
+    if not _SM120_AVAILABLE:
+        return False
+    try:
+        if not torch.cuda.is_available():
+            return False
+        lib = _b.load_library()
+        return any(bool(lib.sm120_is_supported(i)) for i in range(torch.cuda.device_count()))
+    except Exception:
+        return False
+
+
+def get_sm120_device_info() -> Dict[str, Any]:
+    """Same keys as python/sm120_ops.py:66-105."""
+    info: Dict[str, Any] = {"available": False, "devices": [], "library_loaded": _SM120_AVAILABLE}
+    if not _SM120_AVAILABLE or not torch.cuda.is_available():
+        return info
+    lib = _b.load_library()
+    for i in range(torch.cuda.device_count()):
+        try:
+            props = torch.cuda.get_device_properties(i)
+            cc = (props.major, props.minor)
+            ok = bool(lib.sm120_is_supported(i))
+            info["devices"].append({
+                "index": i, "name": props.name, "compute_capability": cc, "sm120_compatible": ok,
+                "details": {"multi_processor_count": props.multi_processor_count, "total_memory": props.total_memory},
+            })
+            info["available"] = info["available"] or ok
+        except Exception as e:  # pragma: no cover
+            info["devices"].append({"index": i, "error": str(e)})
+    return info
+
+
+class SM120Config:
+    """Configuration class for SM120 operations (python/sm120_ops.py:108-135).
+
+    ``fallback_to_standard`` is kept for source compatibility; this build has no
+    standard implementation to fall back to, so the flag has no effect."""
+
+    def __init__(self):
+        self.optimization_level = 1  # 0 = conservative tile, 1/2 = tuned tile choice
+        self.use_tensor_cores = True
+        self.enable_profiling = False
+        self.memory_optimization = True
+        self.fallback_to_standard = True
+
+    def set_optimization_level(self, level: int) -> None:
+        if level not in [0, 1, 2]:
+            raise ValueError("Optimization level must be 0, 1, or 2")
+        self.optimization_level = level
+
+    def enable_tensor_cores(self, enable: bool = True) -> None:
+        self.use_tensor_cores = enable
+
+    def enable_memory_optimization(self, enable: bool = True) -> None:
+        self.memory_optimization = enable
+
+
+_config = SM120Config()
+
+
+def get_config() -> SM120Config:
+    return _config
+
+
+# ---------------------------------------------------------------------------
+# host <-> device plumbing
+# ---------------------------------------------------------------------------
+def _numpy_to_torch(x: np.ndarray) -> torch.Tensor:
+    """Zero-copy view of a numpy array as a CPU torch tensor, including the
+    ml_dtypes types torch.from_numpy does not know."""
+    x = np.ascontiguousarray(x)
+    if _ml is not None and x.dtype == np.dtype(_ml.bfloat16):
+        return torch.from_numpy(x.view(np.uint16)).view(torch.bfloat16)
+    if _ml is not None and x.dtype == np.dtype(_ml.float8_e4m3fn):
+        return torch.from_numpy(x.view(np.uint8)).view(torch.float8_e4m3fn)
+    return torch.from_numpy(x)
+
+
+def _torch_to_numpy(t: torch.Tensor) -> np.ndarray:
+    t = t.contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.uint16).numpy().view(_ml.bfloat16)
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).numpy().view(_ml.float8_e4m3fn)
+    return t.numpy()
+
+
+def _require_available() -> None:
+    if not _SM120_AVAILABLE:
+        raise UnimplementedError("SM120 operations library is not loaded and there is no fallback")
+    if not torch.cuda.is_available():
+        raise UnimplementedError("SM120 operations need a CUDA device (compute capability 10.x); there is no CPU fallback")
+
+
+def _row_major_2d(t: torch.Tensor) -> bool:
+    return t.stride(-1) == 1 and (t.shape[-2] == 1 or t.stride(-2) >= t.shape[-1])
+
+
+def fused_matmul(
+    a, b, *,
+    transpose_a: bool = False,
+    transpose_b: bool = False,
+    bias=None,
+    activation: Union[None, str, int] = None,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    out: Optional[torch.Tensor] = None,
+    out_dtype: Optional[torch.dtype] = None,
+    scale_a: Union[float, torch.Tensor, None] = None,
+    scale_b: Union[float, torch.Tensor, None] = None,
+    use_tensor_cores: Optional[bool] = None,
+    optimization_level: Optional[int] = None,
+):
+    """out = act(alpha / (scale_a * scale_b) * op(a) @ op(b) + beta * out + bias).
+
+    The full form of the op (``sm120_launch_matmul_ex``).  ``a`` and ``b`` are
+    rank-2, or rank-3 with a leading batch dimension (a rank-2 operand is
+    broadcast over the batch).  FP8 inputs (``torch.float8_e4m3fn``) produce
+    bfloat16 unless ``out_dtype`` says otherwise.  ``scale_a`` / ``scale_b`` are the
+    per-tensor quantisation scales (floats, or one-element CUDA float32 tensors
+    that a producer kernel wrote).
+
+    Inputs on the host (numpy arrays or CPU tensors) are copied to the current
+    CUDA device, and the result is copied back and returned in the same form.
+    """
+    host_kind = None
+    if isinstance(a, np.ndarray) or isinstance(b, np.ndarray):
+        host_kind = "numpy"
+        a = _numpy_to_torch(a) if isinstance(a, np.ndarray) else a
+        b = _numpy_to_torch(b) if isinstance(b, np.ndarray) else b
+        if isinstance(bias, np.ndarray):
+            bias = _numpy_to_torch(bias)
+    if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
+        raise TypeError("a and b must be torch tensors or numpy arrays")
+    if a.dtype != b.dtype:
+        raise ValueError(f"Input tensors must have the same dtype, got {a.dtype} and {b.dtype}")
+    if a.dtype not in _TORCH_TO_SM120:
+        raise ValueError(f"dtype {a.dtype} is not supported (float32, float16, bfloat16, float8_e4m3fn)")
+    if a.dim() not in (2, 3) or b.dim() not in (2, 3):
+        raise ValueError("Input tensors must be 2-dimensional (or 3-dimensional with a leading batch dimension)")
+    if not a.is_cuda and host_kind is None:
+        host_kind = "torch"
+
+    # shapes under the transposes (src/tensorflow_ops/sm120_ops_fixed.cc:121-127)
+    M, Ka = (a.shape[-1], a.shape[-2]) if transpose_a else (a.shape[-2], a.shape[-1])
+    Kb, N = (b.shape[-1], b.shape[-2]) if transpose_b else (b.shape[-2], b.shape[-1])
+    if Ka != Kb:
+        raise InvalidArgumentError(f"Matrix dimensions must be compatible: inner dimensions {Ka} and {Kb}")
+    K = Ka
+    batch = 1
+    if a.dim() == 3 or b.dim() == 3:
+        ba = a.shape[0] if a.dim() == 3 else None
+        bb = b.shape[0] if b.dim() == 3 else None
+        if ba is not None and bb is not None and ba != bb:
+            raise InvalidArgumentError(f"batch dimensions differ: {ba} and {bb}")
+        batch = ba if ba is not None else bb
+        if batch < 1:
+            raise InvalidArgumentError("empty batch")
+
+    # everything above is pure validation; from here on a device is needed
+    _require_available()
+    if host_kind is not None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+        a = a.to(dev, non_blocking=True)
+        b = b.to(dev, non_blocking=True)
+        if isinstance(bias, torch.Tensor) and not bias.is_cuda:
+            bias = bias.to(dev, non_blocking=True)
+    if a.device != b.device:
+        raise ValueError(f"a and b are on different devices: {a.device} and {b.device}")
+
+    if not _row_major_2d(a):
+        a = a.contiguous()
+    if not _row_major_2d(b):
+        b = b.contiguous()
+
+    in_code = _TORCH_TO_SM120[a.dtype]
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else (torch.bfloat16 if a.dtype == torch.float8_e4m3fn else a.dtype)
+    if out_dtype not in _TORCH_TO_SM120 or out_dtype == torch.float8_e4m3fn:
+        raise ValueError(f"output dtype {out_dtype} is not supported")
+    out_shape = (batch, M, N) if (a.dim() == 3 or b.dim() == 3) else (M, N)
+    if out is None:
+        if beta != 0.0:
+            raise ValueError("beta != 0 needs `out` to hold the matrix to accumulate into")
+        out = torch.empty(out_shape, dtype=out_dtype, device=a.device)
+    else:
+        if tuple(out.shape) != tuple(out_shape) or out.dtype != out_dtype or out.device != a.device:
+            raise ValueError(f"`out` must be a {out_dtype} tensor of shape {out_shape} on {a.device}")
+        if not _row_major_2d(out) or (out.dim() == 3 and out.stride(0) < M * out.stride(-2)):
+            raise ValueError("`out` must be row-major")
+
+    d = _b.new_desc()
+    d.in_dtype = in_code
+    d.out_dtype = _TORCH_TO_SM120[out_dtype]
+    d.A, d.B, d.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    d.M, d.N, d.K = M, N, K
+    d.lda = a.stride(-2) if a.shape[-2] > 1 else a.shape[-1]
+    d.ldb = b.stride(-2) if b.shape[-2] > 1 else b.shape[-1]
+    d.ldc = out.stride(-2) if out.shape[-2] > 1 else out.shape[-1]
+    d.batch = batch
+    d.stride_a = a.stride(0) if a.dim() == 3 and batch > 1 else 0
+    d.stride_b = b.stride(0) if b.dim() == 3 and batch > 1 else 0
+    d.stride_c = out.stride(0) if out.dim() == 3 and batch > 1 else 0
+    d.transpose_a, d.transpose_b = int(bool(transpose_a)), int(bool(transpose_b))
+    d.alpha, d.beta = float(alpha), float(beta)
+    keep = [a, b, out]
+    for name, s in (("a", scale_a), ("b", scale_b)):
+        if s is None:
+            continue
+        if isinstance(s, torch.Tensor):
+            if not s.is_cuda or s.dtype != torch.float32 or s.numel() != 1:
+                raise ValueError("a tensor scale must be a one-element float32 CUDA tensor")
+            keep.append(s)
+            setattr(d, f"scale_{name}_dev", s.data_ptr())
+        else:
+            if not (float(s) > 0.0):
+                raise ValueError("scales must be positive")
+            setattr(d, f"scale_{name}", float(s))
+    if bias is not None:
+        if not isinstance(bias, torch.Tensor):
+            raise TypeError("bias must be a tensor")
+        if bias.dim() != 1 or bias.shape[0] != N:
+            raise InvalidArgumentError(f"bias must have shape [{N}], got {tuple(bias.shape)}")
+        if bias.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            raise ValueError(f"bias dtype {bias.dtype} is not supported")
+        bias = bias.to(a.device).contiguous()
+        keep.append(bias)
+        d.bias = bias.data_ptr()
+        d.bias_dtype = _TORCH_TO_SM120[bias.dtype]
+    d.activation = activation_code(activation)
+    if use_tensor_cores is None:
+        use_tensor_cores = _config.use_tensor_cores
+    if optimization_level is None:
+        optimization_level = _config.optimization_level
+    if optimization_level not in (0, 1, 2):
+        raise ValueError("Optimization level must be 0, 1, or 2")
+    d.optimization_level = int(optimization_level)
+    d.path = _b.PATH_AUTO if use_tensor_cores else _b.PATH_SIMT
+    d.stream = torch.cuda.current_stream(a.device).cuda_stream
+
+    with torch.cuda.device(a.device):
+        rc = _b.load_library().sm120_launch_matmul_ex(ctypes.byref(d))
+    if rc == _b.CUDA_ERROR_INVALID_VALUE:
+        raise InvalidArgumentError("SM120MatMul rejected its arguments (cudaErrorInvalidValue)")
+    if rc != _b.CUDA_SUCCESS:
+        raise InternalError(f"SM120MatMul failed: {_b.error_string(rc)}")
+
+    if host_kind is None:
+        return out
+    host = out.to("cpu")      # synchronises with the launch stream
+    return _torch_to_numpy(host) if host_kind == "numpy" else host
+
+
+def advanced_matmul(
+    a,
+    b,
+    transpose_a: bool = False,
+    transpose_b: bool = False,
+    use_tensor_cores: Optional[bool] = None,
+    optimization_level: Optional[int] = None,
+    name: Optional[str] = None,
+):
+    """Matrix product of two rank-2 tensors: the op ``SM120AdvancedMatMul`` /
+    ``SM120MatMul``.  Signature, defaults and the two ``ValueError`` checks are
+    those of python/sm120_ops.py:142-184.  ``a`` is [M, K] (or [K, M] with
+    ``transpose_a``), ``b`` is [K, N] (or [N, K] with ``transpose_b``); the result
+    is [M, N] in the inputs' dtype (bfloat16 for FP8 inputs).
+
+    Raises ``ValueError`` for mixed dtypes or rank != 2, ``InvalidArgumentError``
+    for incompatible inner dimensions, ``UnimplementedError`` when no supported
+    GPU or library is present (there is no fallback)."""
+    del name
+    if hasattr(a, "dtype") and hasattr(b, "dtype") and a.dtype != b.dtype:
+        raise ValueError(f"Input tensors must have the same dtype, got {a.dtype} and {b.dtype}")
+    if len(a.shape) != 2 or len(b.shape) != 2:
+        raise ValueError("Input tensors must be 2-dimensional")
+    return fused_matmul(a, b, transpose_a=transpose_a, transpose_b=transpose_b, use_tensor_cores=use_tensor_cores,
+                        optimization_level=optimization_level)
+
+
+# names other files of the reference call (python/benchmark.py:65, python/validate.py:158)
+sm120_matmul = advanced_matmul
+
+
+def batched_matmul(a, b, transpose_a: bool = False, transpose_b: bool = False, **kwargs):
+    """Strided-batch product C[i] = op(a[i]) @ op(b[i]) for rank-3 operands: the
+    semantics of LaunchSM120DynamicMatMul
+    (src/cuda_kernels/sm120_dynamic_shapes.cu:107-183,323-383)."""
+    if len(a.shape) != 3 and len(b.shape) != 3:
+        raise ValueError("batched_matmul needs at least one rank-3 operand")
+    return fused_matmul(a, b, transpose_a=transpose_a, transpose_b=transpose_b, **kwargs)
+
+
+def matmul_grad(grad_c, a, b):
+    """Gradients of C = a @ b (no transposes): (grad_c @ b^T, a^T @ grad_c), the
+    two products of SM120MatMulGradA / SM120MatMulGradB
+    (src/tensorflow_ops/sm120_gradients.cc:22-55)."""
+    return (fused_matmul(grad_c, b, transpose_b=True), fused_matmul(a, grad_c, transpose_a=True))
+
+
+def quantize_fp8(x: torch.Tensor):
+    """Per-tensor FP8 quantisation used with FP8 matmuls: returns
+    (x * s rounded to e4m3 with saturation, s) with s = 448 / amax(x)
+    (type and conversion: src/cuda_kernels/sm120_datatype_support.h:71-82,168-171)."""
+    amax = x.abs().amax().float().clamp_min(1e-30)
+    s = 448.0 / amax
+    q = (x.float() * s).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q, s.reshape(1)
+
+
+class SM120Profiler:
+    """Same interface as python/sm120_ops.py:415-445; times with a device
+    synchronisation on both sides instead of ``tf.timestamp``."""
+
+    def __init__(self, enabled: bool = True):
+        self.enabled = enabled
+        self.metrics: Dict[str, Dict[str, Any]] = {}
+
+    def profile_operation(self, operation_name: str, operation_fn, *args, **kwargs):
+        if not self.enabled:
+            return operation_fn(*args, **kwargs)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        start = time.perf_counter()
+        result = operation_fn(*args, **kwargs)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.metrics[operation_name] = {"execution_time": time.perf_counter() - start, "timestamp": start}
+        return result
+
+    def get_metrics(self) -> Dict[str, Any]:
+        return self.metrics.copy()
+
+    def clear_metrics(self) -> None:
+        self.metrics.clear()
+
+
+def benchmark_operation(operation_fn: Callable, *args, num_iterations: int = 100, warmup_iterations: int = 10,
+                        **kwargs) -> Dict[str, float]:
+    """Same arguments and result keys as python/sm120_ops.py:448-490.  Each
+    iteration is timed on the device with CUDA events (the reference reads
+    ``tf.timestamp`` without synchronising); times are in seconds."""
+    for _ in range(warmup_iterations):
+        operation_fn(*args, **kwargs)
+    times: List[float] = []
+    use_events = torch.cuda.is_available()
+    for _ in range(num_iterations):
+        if use_events:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            operation_fn(*args, **kwargs)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e-3)
+        else:
+            t0 = time.perf_counter()
+            operation_fn(*args, **kwargs)
+            times.append(time.perf_counter() - t0)
+    arr = np.asarray(times, dtype=np.float64)
+    return {
+        "mean_time": float(arr.mean()),
+        "std_time": float(arr.std()),
+        "min_time": float(arr.min()),
+        "max_time": float(arr.max()),
+        "median_time": float(np.median(arr)),
+    }
+
+
+def _initializer(name: str, shape: Sequence[int], dtype: torch.dtype, device, generator=None) -> torch.Tensor:
+    name = (name or "zeros").lower()
+    if name == "zeros":
+        return torch.zeros(*shape, dtype=dtype, device=device)
+    if name == "ones":
+        return torch.ones(*shape, dtype=dtype, device=device)
+    fan_in = shape[0] if len(shape) > 1 else shape[0]
+    fan_out = shape[-1]
+    if name == "glorot_uniform":
+        limit = (6.0 / (fan_in + fan_out)) ** 0.5
+        return ((torch.rand(*shape, generator=generator, device="cpu") * 2 - 1) * limit).to(device=device, dtype=dtype)
+    if name == "glorot_normal":
+        std = (2.0 / (fan_in + fan_out)) ** 0.5
+        return (torch.randn(*shape, generator=generator, device="cpu") * std).to(device=device, dtype=dtype)
+    if name == "he_normal":
+        std = (2.0 / fan_in) ** 0.5
+        return (torch.randn(*shape, generator=generator, device="cpu") * std).to(device=device, dtype=dtype)
+    if name == "random_normal":
+        return (torch.randn(*shape, generator=generator, device="cpu") * 0.05).to(device=device, dtype=dtype)
+    raise ValueError(f"unknown initializer {name!r}")
+
+
+def optimized_dense(inputs, units: int, use_bias: bool = True, activation: Optional[str] = None,
+                    kernel_initializer: str = "glorot_uniform", bias_initializer: str = "zeros",
+                    name: Optional[str] = None):
+    """Stateless dense helper with the signature of python/sm120_ops.py:494-552:
+    flattens leading dimensions, draws a fresh kernel [in, units] and bias [units]
+    on every call (as the reference does), and computes
+    act(inputs @ kernel + bias) in one fused launch."""
+    del name
+    if len(inputs.shape) < 2:
+        raise ValueError("Input must have at least 2 dimensions")
+    in_shape = tuple(inputs.shape)
+    x = inputs.reshape(-1, in_shape[-1])
+    kernel = _initializer(kernel_initializer, (in_shape[-1], units), x.dtype, x.device)
+    bias = _initializer(bias_initializer, (units,), x.dtype, x.device) if use_bias else None
+    y = fused_matmul(x, kernel, bias=bias, activation=activation)
+    return y.reshape(*in_shape[:-1], units)
+
+
+__all__ = [
+    "is_sm120_available",
+    "get_sm120_device_info",
+    "SM120Config",
+    "get_config",
+    "advanced_matmul",
+    "sm120_matmul",
+    "batched_matmul",
+    "fused_matmul",
+    "matmul_grad",
+    "quantize_fp8",
+    "SM120Profiler",
+    "benchmark_operation",
+    "optimized_dense",
+    "activation_code",
+    "InvalidArgumentError",
+    "UnimplementedError",
+    "InternalError",
+]

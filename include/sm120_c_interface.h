@@ -1,0 +1,217 @@
+/*
+ * C ABI of the B200 (sm_100a) build of the SM120 mixed-precision matmul op.
+ *
+ * This is the drop-in boundary: the entry points below are what the
+ * TensorFlow OpKernel (SM120MatMulOp<T>::Compute) and any other foreign
+ * caller (ctypes, cgo, JNI ...) bind.  Every signature uses plain pointers and
+ * sizes; no C++ or framework type crosses it.  The library is built as
+ * `_sm120_ops.so`, the artefact name the reference loads
+ * (python/sm120_ops.py:29-31).
+ *
+ * Contract shared by every launcher here (same as the reference launcher,
+ * src/cuda_kernels/sm120_c_interface.cu:32-60):
+ *   - all matrix pointers are DEVICE pointers owned by the caller;
+ *   - the launcher never allocates, frees or synchronises; work is enqueued on
+ *     the caller's stream (0 = the default stream);
+ *   - the return value is a cudaError_t: cudaSuccess when the kernel was
+ *     enqueued, cudaErrorInvalidValue for a rejected argument (nothing is
+ *     launched), otherwise the launch error;
+ *   - the launchers are re-entrant and may be called from several host threads
+ *     and for several devices at once.
+ *   - there is no CPU fallback: on a device that is not compute capability
+ *     10.x the launchers return cudaErrorInvalidDevice.
+ */
+#ifndef SM120_C_INTERFACE_H
+#define SM120_C_INTERFACE_H
+
+#include <stdbool.h>
+#include <stdint.h>
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Activation codes 0..8 keep the reference's numbering
+ * (src/cuda_kernels/sm120_c_interface.h:21-31) and formulas
+ * (src/cuda_kernels/sm120_pure_kernels.cu:141-171; code 4 is the tanh GELU
+ * with constants 0.7978845608 / 0.044715).  Two codes are appended for the
+ * fused GEMM epilogue: NONE (identity) and GELU_ERF, the exact erf GELU that
+ * the Keras path computes (python/sm120_keras_layers.py:105,172). */
+typedef enum {
+    SM120_ACTIVATION_NONE = -1,
+    SM120_ACTIVATION_RELU = 0,
+    SM120_ACTIVATION_LEAKY_RELU = 1,
+    SM120_ACTIVATION_ELU = 2,
+    SM120_ACTIVATION_SELU = 3,
+    SM120_ACTIVATION_GELU = 4,
+    SM120_ACTIVATION_SWISH = 5,
+    SM120_ACTIVATION_MISH = 6,
+    SM120_ACTIVATION_TANH = 7,
+    SM120_ACTIVATION_SIGMOID = 8,
+    SM120_ACTIVATION_GELU_ERF = 9
+} SM120ActivationType;
+
+/* Values 0 and 1 are the reference's (src/cuda_kernels/sm120_c_interface.h:40-43).
+ * BFLOAT16 and FP8_E4M3 are types the reference declares
+ * (src/cuda_kernels/sm120_datatype_support.h:49-58,71-82) but never feeds to a
+ * GEMM; they are appended here.  FP8_E4M3 is an input type only. */
+typedef enum {
+    SM120_DTYPE_FLOAT32 = 0,
+    SM120_DTYPE_FLOAT16 = 1,
+    SM120_DTYPE_BFLOAT16 = 2,
+    SM120_DTYPE_FP8_E4M3 = 3
+} SM120DataType;
+
+/* Which kernel family a launch may use.  AUTO picks the tcgen05 tensor-core
+ * kernel whenever the operands satisfy TMA's alignment rules and otherwise the
+ * SIMT kernel; the other two values force one family (a forced tensor-core
+ * launch of operands that cannot be described to TMA is rejected). */
+typedef enum {
+    SM120_PATH_AUTO = 0,
+    SM120_PATH_TENSOR_CORE = 1,
+    SM120_PATH_SIMT = 2
+} SM120KernelPath;
+
+/*
+ * Replaces sm120_launch_matmul (src/cuda_kernels/sm120_c_interface.h:53-58,
+ * body src/cuda_kernels/sm120_c_interface.cu:32-60) with the same signature:
+ * C[M,N] = alpha * A[M,K] * B[K,N] + beta * C, all three row-major and dense,
+ * inputs and output of type `dtype`, fp32 accumulation, C read only when
+ * beta != 0 (src/cuda_kernels/sm120_pure_kernels.cu:58-63).
+ * dtype FLOAT32 runs the exact FFMA kernel; FLOAT16 / BFLOAT16 run the tcgen05
+ * kernel.  An unknown dtype returns cudaErrorInvalidValue as the reference does.
+ */
+cudaError_t sm120_launch_matmul(
+    const void* A, const void* B, void* C,
+    int M, int N, int K,
+    float alpha, float beta,
+    SM120DataType dtype,
+    cudaStream_t stream);
+
+/*
+ * Replaces launch_sm120_matmul
+ * (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:788-798): fp32
+ * C[M,N] = A[M,K] * B[K,N], row-major.  Returns nothing, as the reference's
+ * does; a failure is left in cudaGetLastError().
+ */
+void launch_sm120_matmul(
+    const float* A, const float* B, float* C,
+    int M, int N, int K,
+    cudaStream_t stream);
+
+/*
+ * Superset descriptor.  It carries what the three competing OpKernel bodies
+ * pass or need (transposes: src/tensorflow_ops/sm120_ops_fixed.cc:137-143;
+ * alpha/beta: src/tensorflow_ops/sm120_tensorflow_ops.cc:93), the strided-batch
+ * form of LaunchSM120DynamicMatMul
+ * (src/cuda_kernels/sm120_dynamic_shapes.cu:107-183,323-383), and the fused
+ * Dense epilogue (bias add + activation + cast) that the reference runs as
+ * separate ops (python/sm120_keras_layers.py:159-174).
+ *
+ *   C[b] = act( alpha * inv_scale * op(A[b]) * op(B[b]) + beta * C[b] + bias )
+ *
+ * op(A) is [M,K]: A is stored row-major [M,K] with row pitch lda, or, when
+ * transpose_a != 0, as [K,M].  op(B) is [K,N]: B is stored [K,N] with pitch
+ * ldb, or [N,K] when transpose_b != 0.  C is [M,N] with pitch ldc.  A pitch of
+ * 0 means "tight" (the stored row length).  Pitches and batch strides are in
+ * elements.  inv_scale = 1 / (scale_a * scale_b): the per-tensor quantisation
+ * scales of FP8 inputs (q = saturate_e4m3(x * scale)); both default to 1 when
+ * given as 0.  When scale_a_dev / scale_b_dev are non-null they are device
+ * pointers to one float each and override the by-value scales, so a producer
+ * kernel can write them without a host round trip.
+ * bias has N entries of bias_dtype (FLOAT32, FLOAT16 or BFLOAT16) or is null.
+ */
+typedef struct SM120GemmDesc {
+    uint32_t struct_size;      /* sizeof(SM120GemmDesc); checked */
+    int32_t  in_dtype;         /* SM120DataType of A and B */
+    int32_t  out_dtype;        /* SM120DataType of C; FP8 is rejected */
+    int32_t  bias_dtype;       /* SM120DataType of bias (ignored when bias is null) */
+    const void* A;
+    const void* B;
+    void*       C;
+    const void* bias;
+    int64_t M, N, K;
+    int64_t lda, ldb, ldc;
+    int64_t batch;             /* >= 1 */
+    int64_t stride_a, stride_b, stride_c;   /* elements between batch entries; 0 with batch > 1 broadcasts A or B */
+    int32_t transpose_a, transpose_b;
+    float   alpha, beta;
+    float   scale_a, scale_b;
+    const float* scale_a_dev;
+    const float* scale_b_dev;
+    int32_t activation;        /* SM120ActivationType */
+    int32_t path;              /* SM120KernelPath */
+    int32_t optimization_level;/* 0..2 as SM120Config.optimization_level (python/sm120_ops.py:108-122); 0 = conservative tile, 1/2 = tuned */
+    int32_t reserved;
+    cudaStream_t stream;
+} SM120GemmDesc;
+
+/* Fills *desc with defaults: struct_size, batch = 1, alpha = 1, beta = 0,
+ * scales = 1, activation NONE, path AUTO, optimization_level = 1, all else 0. */
+void sm120_gemm_desc_init(SM120GemmDesc* desc);
+
+/* No counterpart in the reference: the launcher its OpKernels need
+ * (see SM120GemmDesc above).  Same contract as sm120_launch_matmul. */
+cudaError_t sm120_launch_matmul_ex(const SM120GemmDesc* desc);
+
+/*
+ * Replaces LaunchSM120MatMulGradA / LaunchSM120MatMulGradB
+ * (src/cuda_kernels/sm120_backward_kernels.cu:360-388; ops at
+ * src/tensorflow_ops/sm120_gradients.cc:22-212), for an op
+ * C = A[M,K] * B[K,N] without transposes:
+ *   grad_a[M,K] = alpha * grad_c[M,N] * B[K,N]^T
+ *   grad_b[K,N] = alpha * A[M,K]^T * grad_c[M,N]
+ * All matrices row-major and dense, of type dtype.
+ */
+cudaError_t sm120_launch_matmul_grad_a(
+    const void* grad_c, const void* B, void* grad_a,
+    int M, int N, int K, float alpha,
+    SM120DataType dtype, cudaStream_t stream);
+cudaError_t sm120_launch_matmul_grad_b(
+    const void* A, const void* grad_c, void* grad_b,
+    int M, int N, int K, float alpha,
+    SM120DataType dtype, cudaStream_t stream);
+
+/*
+ * Replaces sm120_is_supported (src/cuda_kernels/sm120_c_interface.h:153, body
+ * src/cuda_kernels/sm120_c_interface.cu:285-293, which accepts only compute
+ * capability 12.0).  This build accepts compute capability 10.x (B200).
+ */
+bool sm120_is_supported(int device_id);
+
+/* Replaces sm120_get_error_string (src/cuda_kernels/sm120_c_interface.h:209). */
+const char* sm120_get_error_string(cudaError_t error);
+
+/*
+ * Device-side wait status.  Every wait inside the tcgen05 kernel (on a TMA
+ * arrival, a free shared-memory stage or a TMEM accumulator) is bounded by a
+ * wall-clock limit; a kernel that gives up records a non-zero code in a
+ * per-device status word, drains and returns normally.  This call copies the
+ * word for `device_id` to *status (0 = no timeout seen) and, when `clear` is
+ * non-zero, resets it.  It synchronises the device.  The reference has no
+ * counterpart; its closest relative is SM120ErrorHandler
+ * (src/cuda_kernels/sm120_error_handling.cu:48-94), which only logs.
+ */
+cudaError_t sm120_get_kernel_status(int device_id, unsigned int* status, int clear);
+
+/* Wait limit, in milliseconds, used by launches made after the call
+ * (default 2000; also read once from the environment variable
+ * SM120_WAIT_LIMIT_MS).  No counterpart in the reference. */
+void sm120_set_wait_limit_ms(unsigned int ms);
+
+/* Number of kernels this library has enqueued since it was loaded
+ * (both families).  No counterpart in the reference; used to count launches
+ * inside a timed region. */
+uint64_t sm120_get_launch_count(void);
+
+/* Name of the kernel variant the last launch on this host thread used, e.g.
+ * "tc_bf16_128x256x64_s4" or "simt_f32_64x64"; "" before any launch.
+ * No counterpart in the reference. */
+const char* sm120_get_last_kernel_name(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SM120_C_INTERFACE_H */

@@ -1,0 +1,90 @@
+"""CPU tests of the M-sharding logic: slab arithmetic, and the local / gathered
+product with two gloo ranks, where the per-slab product is supplied by the test
+(the oracle) because no GPU kernel can run here."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.conftest import PACKAGE_NAME
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_slab_arithmetic(pkg):
+    ms = pkg.mshard
+    assert ms.slab_rows(65536, 8) == 8192 and ms.slab_bounds(65536, 8, 7) == (57344, 65536)
+    assert ms.slab_rows(1000, 4) == 256            # ceil(1000/4) = 250 -> next multiple of 128
+    bounds = [ms.slab_bounds(1000, 4, r) for r in range(4)]
+    assert bounds == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    assert [ms.slab_bounds(130, 4, r) for r in range(4)] == [(0, 128), (128, 130), (130, 130), (130, 130)]
+    assert ms.slab_rows(0, 4) == 0 and ms.slab_bounds(0, 4, 2) == (0, 0)
+    # slabs tile [0, M) exactly, for a sweep of sizes
+    for M in (1, 127, 128, 129, 4096, 65536, 100003):
+        for G in (1, 2, 4, 8):
+            cover = [ms.slab_bounds(M, G, r) for r in range(G)]
+            assert cover[0][0] == 0 and cover[-1][1] == M
+            assert all(cover[i][1] == cover[i + 1][0] for i in range(G - 1))
+    assert ms.chunk_bounds(8192, 4) == [(0, 2048), (2048, 4096), (4096, 6144), (6144, 8192)]
+    assert ms.chunk_bounds(300, 2) == [(0, 256), (256, 300)]
+    assert ms.chunk_bounds(0, 3) == []
+    with pytest.raises(ValueError):
+        ms.slab_bounds(10, 2, 2)
+
+
+def _cpu_matmul(a, b, out=None, **kwargs):
+    """Stand-in for the GPU op inside the gloo test: float64 product, fp32 result."""
+    r = (a.double() @ b.double()).float()
+    if kwargs.get("bias") is not None:
+        r = r + kwargs["bias"]
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
+
+
+def _worker(rank, world, port, M, N, K, chunks, ret):
+    import importlib
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ms = importlib.import_module(PACKAGE_NAME).mshard
+        g = torch.Generator().manual_seed(0)
+        a = torch.randn(M, K, generator=g)
+        b_src = torch.randn(K, N, generator=g)
+        sh = ms.MShardedMatmul(M, N, matmul_fn=_cpu_matmul)
+        b = b_src.clone() if rank == 0 else torch.zeros(K, N)
+        sh.replicate_b(b)
+        a_slab = a[sh.start:sh.stop]
+        local = sh.local(a_slab, b)
+        full = sh.gathered(a_slab, b, out_dtype=torch.float32, chunks=chunks)
+        want = (a.double() @ b_src.double()).float()
+        ok = (torch.equal(b, b_src) and torch.equal(local, want[sh.start:sh.stop]) and tuple(full.shape) == (M, N)
+              and torch.equal(full, want))
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("M,N,K,chunks", [(512, 96, 64, 1), (512, 96, 64, 2), (300, 40, 32, 1), (300, 40, 32, 3), (100, 16, 8, 1)])
+def test_two_gloo_ranks_local_and_gathered(M, N, K, chunks):
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, M, N, K, chunks, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert dict(ret) == {0: True, 1: True}
