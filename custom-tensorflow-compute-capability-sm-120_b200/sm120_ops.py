@@ -213,7 +213,8 @@ def fused_matmul(
     that a producer kernel wrote).
 
     Inputs on the host (numpy arrays or CPU tensors) are copied to the current
-    CUDA device, and the result is copied back and returned in the same form.
+    CUDA device, and the result is copied back and returned in the same form;
+    `out` may then be a host buffer (ideally pinned) that receives the result.
     """
     host_kind = None
     if isinstance(a, np.ndarray) or isinstance(b, np.ndarray):
@@ -251,6 +252,14 @@ def fused_matmul(
 
     # everything above is pure validation; from here on a device is needed
     _require_available()
+    host_out = None
+    if host_kind is not None and isinstance(out, np.ndarray):
+        out = _numpy_to_torch(out)
+    if host_kind is not None and isinstance(out, torch.Tensor) and not out.is_cuda:
+        # a host result buffer (pinned for an asynchronous copy): the device result is copied into it
+        if beta != 0.0:
+            raise ValueError("beta != 0 is not supported with host operands")
+        host_out, out = out, None
     if host_kind is not None:
         dev = torch.device("cuda", torch.cuda.current_device())
         a = a.to(dev, non_blocking=True)
@@ -339,7 +348,14 @@ def fused_matmul(
 
     if host_kind is None:
         return out
-    host = out.to("cpu")      # synchronises with the launch stream
+    if host_out is not None:
+        if tuple(host_out.shape) != tuple(out.shape) or host_out.dtype != out.dtype:
+            raise ValueError(f"host `out` must be a {out.dtype} tensor of shape {tuple(out.shape)}")
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(a.device).synchronize()
+        host = host_out
+    else:
+        host = out.to("cpu")      # synchronises with the launch stream
     return _torch_to_numpy(host) if host_kind == "numpy" else host
 
 

@@ -1,0 +1,441 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (ctypes, via the
+package's host code), against the CPU oracle on identical seeded inputs.
+
+Shapes, dtypes and tolerances of the first groups restate the reference's own
+tests (tests/test_sm120_operations.py:47-214,
+tests/integration/test_comprehensive_validation.py:145-193); the BASELINE groups
+use the five configurations of BASELINE.json with its relative-Frobenius gates
+(1e-5 fp32, 1e-2 fp16/bf16, 5e-2 fp8)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import reference as ref
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+TOL = ref.TOLERANCE
+
+
+def run(ops, a, b, *, ta=False, tb=False, bias=None, act=-1, alpha=1.0, beta=0.0, c_in=None, out_dtype=None,
+        sa=None, sb=None, use_tensor_cores=None, optimization_level=None):
+    """numpy operands -> CUDA -> fused_matmul -> numpy result (+ kernel name)."""
+    ta_, tb_ = U.to_cuda(a), U.to_cuda(b)
+    out = U.to_cuda(c_in) if c_in is not None else None
+    r = ops.fused_matmul(ta_, tb_, transpose_a=ta, transpose_b=tb, bias=None if bias is None else U.to_cuda(bias),
+                         activation=act, alpha=alpha, beta=beta, out=out,
+                         out_dtype=None if out_dtype is None else U.torch_dtype(out_dtype), scale_a=sa, scale_b=sb,
+                         use_tensor_cores=use_tensor_cores, optimization_level=optimization_level)
+    torch.cuda.synchronize()
+    return U.to_numpy(r)
+
+
+def check(got, want, dtype_name, what=""):
+    err = ref.rel_frobenius(got, want)
+    assert np.isfinite(np.asarray(got).astype(np.float32)).all(), f"{what}: non-finite output"
+    assert err <= TOL[dtype_name], f"{what}: rel Frobenius {err:.3e} > {TOL[dtype_name]:.0e}"
+    return err
+
+
+def test_device_is_supported(ops, binding):
+    assert ops.is_sm120_available()
+    assert binding.load_library().sm120_is_supported(0)
+    info = ops.get_sm120_device_info()
+    assert info["available"] and info["devices"][0]["compute_capability"][0] == 10
+
+
+def test_known_answer_2x2(ops):
+    # scripts/validate-installation.py:381-388
+    a = np.array([[1.0, 2.0], [3.0, 4.0]], dtype=np.float32)
+    b = np.array([[2.0, 0.0], [0.0, 2.0]], dtype=np.float32)
+    assert run(ops, a, b).tolist() == [[2.0, 4.0], [6.0, 8.0]]
+
+
+def test_golden_vectors(ops, binding):
+    for name, g in U.load_golden().items():
+        got = run(ops, g["a"], g["b"], ta=g["ta"], tb=g["tb"], bias=g["bias"], act=g["act"], alpha=g["alpha"],
+                  beta=g["beta"], c_in=g["c_in"], out_dtype=g["out_dtype"],
+                  sa=g["sa"] if g["in_dtype"] == "fp8_e4m3" else None, sb=g["sb"] if g["in_dtype"] == "fp8_e4m3" else None)
+        assert got.dtype == g["c"].dtype and got.shape == g["c"].shape, name
+        tol_name = g["in_dtype"] if g["in_dtype"] != "fp8_e4m3" else "bfloat16"   # vs the dequantised product: 1e-2
+        check(got, g["c"], tol_name, name)
+        if g["in_dtype"] != "float32":
+            assert binding.last_kernel_name().startswith("tc_"), (name, binding.last_kernel_name())
+
+
+# ----- the reference's own test shapes (tests/test_sm120_operations.py:47,71-72) -----
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("M,K", [(32, 64), (64, 32), (128, 256)])
+def test_reference_shapes(ops, dtype, M, K):
+    rng = np.random.default_rng(M * 131 + K)
+    a = ref.quantize(0.1 * rng.standard_normal((M, K), dtype=np.float32), dtype)
+    b = ref.quantize(0.1 * rng.standard_normal((K, K), dtype=np.float32), dtype)
+    got = run(ops, a, b)
+    want = ref.matmul_oracle(a, b, out_dtype=dtype)
+    check(got, want, dtype, f"{dtype} {M}x{K}")
+    # and the reference's own criterion: max|d| <= atol + rtol*max|ref| with 1e-3 (1e-2 for fp16)
+    t = 1e-2 if dtype != "float32" else 1e-3
+    assert ref.max_abs_tolerance_ok(got, want, rtol=t, atol=t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_transposes(ops, dtype, ta, tb):
+    # tests/test_sm120_operations.py:124-145, with shapes that are valid for every combination
+    M, N, K = 128, 256, 192
+    rng = np.random.default_rng(11 + 2 * ta + tb)
+    a, b, _, _ = U.random_operands(rng, M, N, K, 1, ta, tb, dtype, scale=0.1)
+    got = run(ops, a, b, ta=ta, tb=tb)
+    check(got, ref.matmul_oracle(a, b, transpose_a=ta, transpose_b=tb, out_dtype=dtype), dtype, f"{dtype} ta={ta} tb={tb}")
+
+
+@pytest.mark.parametrize("level", [0, 1, 2])
+def test_optimization_levels_and_tensor_core_switch(ops, binding, level):
+    # tests/test_sm120_operations.py:147-173
+    rng = np.random.default_rng(5)
+    a, b, _, _ = U.random_operands(rng, 256, 384, 128, 1, False, False, "float16", scale=0.1)
+    want = ref.matmul_oracle(a, b, out_dtype="float16")
+    check(run(ops, a, b, optimization_level=level), want, "float16", f"level {level}")
+    assert binding.last_kernel_name().startswith("tc_f16")
+    check(run(ops, a, b, optimization_level=level, use_tensor_cores=False), want, "float16", f"level {level} simt")
+    assert binding.last_kernel_name().startswith("simt_f16")
+
+
+@pytest.mark.parametrize("dtype,size", [("float32", 512), ("float16", 512), ("bfloat16", 2048), ("float16", 2048)])
+def test_square_sizes(ops, dtype, size):
+    # tests/test_sm120_operations.py:175-198 (2048^2) and :479-516 (512..4096)
+    rng = np.random.default_rng(size)
+    a, b, _, _ = U.random_operands(rng, size, size, size, 1, False, False, dtype, scale=0.1)
+    check(run(ops, a, b), ref.matmul_oracle(a, b, out_dtype=dtype), dtype, f"{dtype} {size}^2")
+
+
+def test_batch_flattened_projection(ops):
+    # tests/integration/test_comprehensive_validation.py:145-184: A[batch,512,768] . B[768,256], f32 and f16
+    for dtype in ("float32", "float16"):
+        rng = np.random.default_rng(9)
+        a = ref.quantize(0.1 * rng.standard_normal((4, 512, 768), dtype=np.float32), dtype)
+        b = ref.quantize(0.1 * rng.standard_normal((768, 256), dtype=np.float32), dtype)
+        want = ref.matmul_oracle(a, b, out_dtype=dtype)
+        got3 = run(ops, a, b)                                   # rank-3 A, B broadcast over the batch
+        got2 = run(ops, a.reshape(-1, 768), b).reshape(4, 512, 256)
+        check(got3, want, dtype, f"{dtype} batched-broadcast")
+        check(got2, want, dtype, f"{dtype} flattened")
+        assert np.array_equal(got3.view(np.uint8), got2.view(np.uint8))
+
+
+# ----- edge shapes: every extent off the tile grid, operands TMA cannot describe -----
+EDGE = [1, 7, 16, 17, 127, 129, 255]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
+def test_edge_shapes(ops, binding, dtype):
+    rng = np.random.default_rng(21)
+    seen = set()
+    for M in EDGE:
+        for N, K in ((1, 129), (7, 16), (16, 7), (17, 255), (127, 1), (129, 17), (255, 127), (264, 72), (136, 4104)):
+            for ta, tb in ((False, False), (False, True), (True, False)):
+                a, b, _, _ = U.random_operands(rng, M, N, K, 1, ta, tb, dtype, scale=0.25)
+                got = run(ops, a, b, ta=ta, tb=tb)
+                check(got, ref.matmul_oracle(a, b, transpose_a=ta, transpose_b=tb, out_dtype=dtype), dtype,
+                      f"{dtype} M={M} N={N} K={K} ta={ta} tb={tb}")
+                seen.add(binding.last_kernel_name().split("_")[0])
+    if dtype != "float32":
+        assert seen == {"tc", "simt"}     # aligned shapes ran on tensor cores, the rest on the SIMT kernel
+
+
+def test_ragged_tensor_core_tiles(ops, binding):
+    # extents that are multiples of 8 (so TMA applies) but of no tile size: M, N, K tails are zero-filled by TMA
+    rng = np.random.default_rng(33)
+    for (M, N, K) in ((136, 264, 72), (8, 8, 8), (120, 1000, 40), (392, 136, 520), (1, 512, 64)):
+        for tb in (False, True):
+            a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, tb, "bfloat16", scale=0.25)
+            got = run(ops, a, b, tb=tb)
+            assert binding.last_kernel_name().startswith("tc_bf16"), binding.last_kernel_name()
+            check(got, ref.matmul_oracle(a, b, transpose_b=tb, out_dtype="bfloat16"), "bfloat16", f"{M}x{N}x{K} tb={tb}")
+
+
+def test_guard_bands_are_untouched(ops):
+    # C with a pitch wider than N and spare rows: everything outside [M, N] must keep its sentinel
+    rng = np.random.default_rng(4)
+    for dtype, (M, N, K) in (("bfloat16", (200, 328, 136)), ("float32", (77, 90, 33))):
+        a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, False, dtype)
+        ta_, tb_ = U.to_cuda(a), U.to_cuda(b)
+        pitch, rows = N + 24, M + 5
+        big = torch.full((rows, pitch), 777.0, dtype=U.torch_dtype(dtype), device="cuda")
+        view = big[:M, :N]
+        ops.fused_matmul(ta_, tb_, out=view)
+        torch.cuda.synchronize()
+        host = U.to_numpy(big).astype(np.float32)
+        check(host[:M, :N], ref.matmul_oracle(a, b, out_dtype=dtype), dtype, f"{dtype} guarded")
+        assert (host[M:, :] == 777.0).all() and (host[:, N:] == 777.0).all()
+
+
+# ----- epilogue -----
+@pytest.mark.parametrize("act", list(range(-1, 10)))
+def test_activations_fused(ops, act):
+    rng = np.random.default_rng(100 + act)
+    M, N, K = 160, 192, 64
+    a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, False, "bfloat16", scale=0.3)
+    bias = rng.standard_normal((N,), dtype=np.float32)
+    want = ref.matmul_oracle(a, b, bias=bias, act=act, out_dtype="float32")
+    got_tc = run(ops, a, b, bias=bias, act=act, out_dtype="float32")
+    got_simt = run(ops, a, b, bias=bias, act=act, out_dtype="float32", use_tensor_cores=False)
+    assert ref.rel_frobenius(got_tc, want) <= 2e-5, act      # fp32 out of exact bf16 products: only fp32 rounding
+    assert ref.rel_frobenius(got_simt, want) <= 2e-5, act
+    assert ref.max_abs_tolerance_ok(got_tc, want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("bias_dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("out_dtype", ["float32", "float16", "bfloat16"])
+def test_bias_and_output_dtypes(ops, bias_dtype, out_dtype):
+    rng = np.random.default_rng(17)
+    M, N, K = 130, 200, 96
+    a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, True, "float16", scale=0.2)
+    bias = ref.quantize(rng.standard_normal((N,), dtype=np.float32), bias_dtype)
+    got = run(ops, a, b, tb=True, bias=bias, act=0, out_dtype=out_dtype)
+    want = ref.matmul_oracle(a, b, transpose_b=True, bias=bias, act=0, out_dtype=out_dtype)
+    check(got, want, "float16" if out_dtype == "float32" else out_dtype, f"bias {bias_dtype} out {out_dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_alpha_beta(ops, dtype):
+    # src/cuda_kernels/sm120_pure_kernels.cu:58-63
+    rng = np.random.default_rng(8)
+    M, N, K = 96, 136, 64
+    a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, False, dtype, scale=0.3)
+    c0 = ref.quantize(rng.standard_normal((M, N), dtype=np.float32), dtype)
+    got = run(ops, a, b, alpha=0.5, beta=2.0, c_in=c0)
+    check(got, ref.matmul_oracle(a, b, alpha=0.5, beta=2.0, c_in=c0, out_dtype=dtype), dtype, f"{dtype} alpha/beta")
+    # beta == 0 never reads C: a NaN-filled output buffer is simply overwritten
+    nan_c = np.full((M, N), np.nan, dtype=np.float32).astype(ref.NP_DTYPES[dtype])
+    got = run(ops, a, b, alpha=1.0, beta=0.0, c_in=nan_c)
+    check(got, ref.matmul_oracle(a, b, out_dtype=dtype), dtype, f"{dtype} beta=0")
+
+
+# ----- strided batch (src/cuda_kernels/sm120_dynamic_shapes.cu:107-183) -----
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_strided_batch(ops, dtype):
+    rng = np.random.default_rng(12)
+    batch, M, N, K = 5, 136, 264, 128
+    for ta, tb in ((False, False), (False, True), (True, False)):
+        a, b, _, _ = U.random_operands(rng, M, N, K, batch, ta, tb, dtype, scale=0.3)
+        got = run(ops, a, b, ta=ta, tb=tb)
+        check(got, ref.matmul_oracle(a, b, transpose_a=ta, transpose_b=tb, out_dtype=dtype), dtype, f"{dtype} batch ta={ta} tb={tb}")
+    # padded batch stride and pitch on A; B broadcast (stride 0)
+    a_full = torch.zeros(batch, M + 8, K + 16, dtype=U.torch_dtype(dtype), device="cuda")
+    a_np, b_np, _, _ = U.random_operands(rng, M, N, K, batch, False, False, dtype, scale=0.3)
+    a_full[:, :M, :K] = U.to_cuda(a_np)
+    got = U.to_numpy(ops.fused_matmul(a_full[:, :M, :K], U.to_cuda(b_np[0])))
+    check(got, ref.matmul_oracle(a_np, b_np[0], out_dtype=dtype), dtype, f"{dtype} strided A, broadcast B")
+
+
+# ----- FP8 -----
+def test_fp8_scaled(ops, binding):
+    rng = np.random.default_rng(40)
+    M, N, K = 256, 384, 512
+    a32 = rng.standard_normal((M, K), dtype=np.float32)
+    b32 = rng.standard_normal((N, K), dtype=np.float32)
+    sa, sb = float(np.float32(ref.fp8_scale(a32))), float(np.float32(ref.fp8_scale(b32)))
+    a, b = ref.quantize(a32 * np.float32(sa), "fp8_e4m3"), ref.quantize(b32 * np.float32(sb), "fp8_e4m3")
+    want_deq = ref.matmul_oracle(a, b, transpose_b=True, scale_a=sa, scale_b=sb, out_dtype="bfloat16")
+    want_true = ref.matmul_oracle(a32, b32, transpose_b=True, round_output=False)
+    got = run(ops, a, b, tb=True, sa=sa, sb=sb)
+    assert binding.last_kernel_name().startswith("tc_e4m3")
+    assert got.dtype == ref.NP_DTYPES["bfloat16"]
+    assert ref.rel_frobenius(got, want_deq) <= 1e-2          # kernel error alone
+    assert ref.rel_frobenius(got, want_true) <= TOL["fp8_e4m3"]   # BASELINE gate: vs the unquantised product
+    # scales supplied as device scalars give the same bits
+    r2 = ops.fused_matmul(U.to_cuda(a), U.to_cuda(b), transpose_b=True,
+                          scale_a=torch.tensor([sa], device="cuda"), scale_b=torch.tensor([sb], device="cuda"))
+    assert ref.rel_frobenius(U.to_numpy(r2), got) <= 1e-2
+    # the helper quantiser agrees with the oracle's
+    q, s = ops.quantize_fp8(torch.from_numpy(a32).cuda())
+    assert abs(float(s) - sa) / sa < 1e-6
+    assert np.mean(U.to_numpy(q).view(np.uint8) == a.view(np.uint8)) > 0.999
+    # SIMT path on the same FP8 operands
+    got_simt = run(ops, a, b, tb=True, sa=sa, sb=sb, use_tensor_cores=False)
+    assert ref.rel_frobenius(got_simt, want_deq) <= 1e-2
+
+
+# ----- BASELINE configurations at oracle-friendly size -----
+@pytest.mark.parametrize("idx,shrink", [(1, 1), (2, 4), (3, 8), (4, 4), (5, 16)])
+def test_baseline_configs_reduced(ops, idx, shrink):
+    cfg = ref.make_config(idx, shrink)
+    fp8 = cfg["in_dtype"] == "fp8_e4m3"
+    got = run(ops, cfg["a"], cfg["b"], ta=cfg["transpose_a"], tb=cfg["transpose_b"], bias=cfg["bias"], act=cfg["act"],
+              out_dtype=cfg["out_dtype"], sa=cfg["scale_a"] if fp8 else None, sb=cfg["scale_b"] if fp8 else None)
+    want = ref.oracle_for_config(cfg)
+    if fp8:
+        assert ref.rel_frobenius(got, want) <= 1e-2
+        exact = ref.matmul_oracle(cfg["a_unquantized"], cfg["b_unquantized"], transpose_b=True, round_output=False)
+        check(got, exact, "fp8_e4m3", cfg["name"])
+    else:
+        check(got, want, cfg["in_dtype"], cfg["name"])
+
+
+def _sampled_rows_check(ops, a_t, b_t, got_t, rows, *, tb, bias_t=None, act=-1, inv_scale=1.0, tol=1e-2):
+    """Full-size parity without a full-size CPU product: the oracle recomputes a sample of rows."""
+    a_rows = U.to_numpy(a_t[rows]).astype(np.float64)
+    b_np = U.to_numpy(b_t).astype(np.float64)
+    acc = a_rows @ (b_np.T if tb else b_np)
+    v = acc * inv_scale
+    if bias_t is not None:
+        v = v + U.to_numpy(bias_t).astype(np.float64)
+    v = ref.activation(v, act)
+    return ref.rel_frobenius(U.to_numpy(got_t[rows]), v) <= tol
+
+
+def test_baseline_config2_full_size(ops, binding):
+    torch.manual_seed(1)
+    n = 4096
+    a = (torch.randn(n, n, device="cuda") / 64).half()
+    b = (torch.randn(n, n, device="cuda") / 64).half()          # stored [N, K]
+    c = ops.advanced_matmul(a, b, transpose_b=True)
+    assert binding.last_kernel_name().startswith("tc_f16")
+    rows = torch.randint(0, n, (48,), device="cuda")
+    assert _sampled_rows_check(ops, a, b, c, rows, tb=True)
+    # linearity in A: (2A) B == 2 (A B) exactly in fp16 (scaling by 2 is exact)
+    c2 = ops.advanced_matmul(a * 2, b, transpose_b=True)
+    assert torch.equal(c2, c * 2)
+    # run-to-run determinism (DEPLOYMENT_GUIDE.md:498-519)
+    assert torch.equal(ops.advanced_matmul(a, b, transpose_b=True), c)
+    # same shape in bf16 (the north-star headline size)
+    cb = ops.advanced_matmul(a.bfloat16(), b.bfloat16(), transpose_b=True)
+    assert _sampled_rows_check(ops, a.bfloat16(), b.bfloat16(), cb, rows, tb=True)
+
+
+def test_baseline_config3_full_size(ops, binding):
+    torch.manual_seed(2)
+    x = torch.randn(8192, 4096, device="cuda").bfloat16()
+    w = (0.02 * torch.randn(4096, 11008, device="cuda")).bfloat16()
+    bias = (0.02 * torch.randn(11008, device="cuda")).bfloat16()
+    y = ops.fused_matmul(x, w, bias=bias, activation="gelu")
+    assert binding.last_kernel_name().startswith("tc_bf16") and tuple(y.shape) == (8192, 11008)
+    rows = torch.randint(0, 8192, (32,), device="cuda")
+    assert _sampled_rows_check(ops, x, w, y, rows, tb=False, bias_t=bias, act=9)
+    assert torch.equal(ops.fused_matmul(x, w, bias=bias, activation="gelu"), y)
+
+
+def test_baseline_config4_full_size(ops):
+    torch.manual_seed(3)
+    q = torch.randn(64, 2048, 128, device="cuda").bfloat16()
+    k = torch.randn(64, 128, 2048, device="cuda").bfloat16()
+    s = ops.batched_matmul(q, k)
+    assert tuple(s.shape) == (64, 2048, 2048)
+    for bz in (0, 31, 63):
+        rows = torch.randint(0, 2048, (16,), device="cuda")
+        assert _sampled_rows_check(ops, q[bz], k[bz], s[bz], rows, tb=False)
+    assert torch.equal(ops.batched_matmul(q, k), s)
+
+
+def test_baseline_config5_slab(ops, binding):
+    # one rank's slab of the 8-way M-sharded FP8 config: 8192 x 8192 x 8192
+    torch.manual_seed(4)
+    a32 = torch.randn(8192, 8192, device="cuda")
+    b32 = torch.randn(8192, 8192, device="cuda")
+    qa, sa = ops.quantize_fp8(a32)
+    qb, sb = ops.quantize_fp8(b32)
+    c = ops.fused_matmul(qa, qb, transpose_b=True, scale_a=sa, scale_b=sb)
+    assert binding.last_kernel_name().startswith("tc_e4m3") and c.dtype == torch.bfloat16
+    rows = torch.randint(0, 8192, (32,), device="cuda")
+    inv = 1.0 / (float(sa) * float(sb))
+    assert _sampled_rows_check(ops, qa, qb, c, rows, tb=True, inv_scale=inv, tol=1e-2)
+    # BASELINE gate against the unquantised product on the sampled rows
+    exact = a32[rows].double() @ b32.double().T
+    assert ref.rel_frobenius(U.to_numpy(c[rows]), exact.cpu().numpy()) <= TOL["fp8_e4m3"]
+
+
+def test_determinism_small_and_ragged(ops):
+    rng = np.random.default_rng(77)
+    for dtype, shape in (("bfloat16", (392, 520, 264)), ("float32", (300, 200, 100))):
+        a, b, _, _ = U.random_operands(rng, *shape, 1, False, False, dtype)
+        r1, r2 = run(ops, a, b), run(ops, a, b)
+        assert np.array_equal(r1.view(np.uint8), r2.view(np.uint8))
+
+
+# ----- the C entry points with the reference's own signatures -----
+def test_reference_signature_entry_points(binding):
+    lib = binding.load_library()
+    rng = np.random.default_rng(55)
+    M, N, K = 96, 72, 40
+    stream = torch.cuda.current_stream().cuda_stream
+    for dtype, code in (("float32", 0), ("float16", 1), ("bfloat16", 2)):
+        a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, False, dtype, scale=0.3)
+        c0 = ref.quantize(rng.standard_normal((M, N), dtype=np.float32), dtype)
+        ta_, tb_, tc_ = U.to_cuda(a), U.to_cuda(b), U.to_cuda(c0)
+        rc = lib.sm120_launch_matmul(ta_.data_ptr(), tb_.data_ptr(), tc_.data_ptr(), M, N, K, 1.5, 0.5, code, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        check(U.to_numpy(tc_), ref.matmul_oracle(a, b, alpha=1.5, beta=0.5, c_in=c0, out_dtype=dtype), dtype, f"launch_matmul {dtype}")
+    # launch_sm120_matmul: fp32, void return (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:788-798)
+    a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, False, "float32")
+    ta_, tb_ = U.to_cuda(a), U.to_cuda(b)
+    out = torch.empty(M, N, device="cuda")
+    lib.launch_sm120_matmul(ta_.data_ptr(), tb_.data_ptr(), out.data_ptr(), M, N, K, stream)
+    torch.cuda.synchronize()
+    check(U.to_numpy(out), ref.matmul_oracle(a, b), "float32", "launch_sm120_matmul")
+
+
+@pytest.mark.parametrize("dtype,code", [("float32", 0), ("bfloat16", 2)])
+def test_gradient_entry_points(binding, ops, dtype, code):
+    # dA = dC . B^T, dB = A^T . dC (src/tensorflow_ops/sm120_gradients.cc:22-55)
+    lib = binding.load_library()
+    rng = np.random.default_rng(66)
+    M, N, K = 136, 264, 72
+    a, b, _, _ = U.random_operands(rng, M, N, K, 1, False, False, dtype, scale=0.3)
+    g = ref.quantize(0.3 * rng.standard_normal((M, N), dtype=np.float32), dtype)
+    ta_, tb_, tg_ = U.to_cuda(a), U.to_cuda(b), U.to_cuda(g)
+    da = torch.empty(M, K, dtype=ta_.dtype, device="cuda")
+    db = torch.empty(K, N, dtype=ta_.dtype, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.sm120_launch_matmul_grad_a(tg_.data_ptr(), tb_.data_ptr(), da.data_ptr(), M, N, K, 1.0, code, stream) == 0
+    assert lib.sm120_launch_matmul_grad_b(ta_.data_ptr(), tg_.data_ptr(), db.data_ptr(), M, N, K, 1.0, code, stream) == 0
+    torch.cuda.synchronize()
+    check(U.to_numpy(da), ref.matmul_oracle(g, b, transpose_b=True, out_dtype=dtype), dtype, "grad_a")
+    check(U.to_numpy(db), ref.matmul_oracle(a, g, transpose_a=True, out_dtype=dtype), dtype, "grad_b")
+    ga, gb = ops.matmul_grad(tg_, ta_, tb_)
+    assert torch.equal(ga, da) and torch.equal(gb, db)
+
+
+# ----- the layer and the host-array path -----
+def test_dense_layer_forward(pkg):
+    layers, ops = pkg.sm120_keras_layers, pkg.sm120_ops
+    for act in (None, "relu", "gelu", "tanh"):
+        layer = layers.SM120Dense(264, activation=act, dtype="bfloat16")
+        x = torch.randn(4, 50, 136, device="cuda").bfloat16()      # rank-3 input is flattened and restored
+        layer.build(tuple(x.shape), seed=1)
+        layer.set_weights([layer.kernel, (0.1 * torch.randn(264, device="cuda")).bfloat16()])
+        y = layer(x)
+        assert tuple(y.shape) == (4, 50, 264) and y.dtype == torch.bfloat16
+        want = ref.matmul_oracle(U.to_numpy(x).reshape(-1, 136), U.to_numpy(layer.kernel), bias=U.to_numpy(layer.bias),
+                                 act=ops.activation_code(act), out_dtype="bfloat16").reshape(4, 50, 264)
+        check(U.to_numpy(y), want, "bfloat16", f"SM120Dense {act}")
+    # a callable activation is applied after the fused matmul + bias
+    layer = layers.SM120Dense(64, activation=torch.sigmoid, dtype="float32")
+    x = torch.randn(32, 48, device="cuda")
+    y = layer(x)
+    want = ref.matmul_oracle(U.to_numpy(x), U.to_numpy(layer.kernel), bias=U.to_numpy(layer.bias), act=8)
+    check(U.to_numpy(y), want, "float32", "SM120Dense callable")
+    out = ops.optimized_dense(torch.randn(8, 16, 32, device="cuda"), 24, activation="relu")
+    assert tuple(out.shape) == (8, 16, 24) and float(out.min()) >= 0.0
+
+
+def test_host_arrays_round_trip(ops):
+    rng = np.random.default_rng(91)
+    for dtype in ("float32", "bfloat16"):
+        a, b, _, _ = U.random_operands(rng, 200, 136, 72, 1, False, False, dtype, scale=0.3)
+        got = ops.advanced_matmul(a, b)                       # numpy in -> numpy out
+        assert isinstance(got, np.ndarray) and got.dtype == a.dtype
+        check(got, ref.matmul_oracle(a, b, out_dtype=dtype), dtype, f"host {dtype}")
+    a = torch.randn(64, 32)
+    got = ops.advanced_matmul(a, torch.randn(32, 16))         # CPU tensors in -> CPU tensor out
+    assert isinstance(got, torch.Tensor) and not got.is_cuda
+
+
+def test_kernel_status_is_clean(binding):
+    status = ctypes.c_uint(123)
+    assert binding.load_library().sm120_get_kernel_status(0, ctypes.byref(status), 0) == 0
+    assert status.value == 0
