@@ -597,9 +597,12 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     // Tile width: the widest BN that still gives every SM a tile; level 0 keeps 128.
     const int64_t tiles_m = (p.M + BM - 1) / BM;
     auto tiles_for = [&](int bn) { return tiles_m * ((p.N + bn - 1) / bn) * p.batch; };
-    int bn = 64;
+    // An MN-major operand is loaded in boxes of 128 bytes of M/N, so BN cannot be
+    // narrower than one box: 128 elements for 1-byte types.
+    const int min_bn = (!p.transpose_b && es == 1) ? 128 : 64;
+    int bn = min_bn;
     if (p.optimization_level == 0) {
-        bn = p.N > 64 ? 128 : 64;
+        bn = p.N > 64 ? 128 : min_bn;
     } else {
         const int wide[2] = {256, 128};
         for (int cand : wide) {
