@@ -95,6 +95,8 @@ def load_library() -> ctypes.CDLL:
         # test hook, not part of the public header
         lib.sm120_debug_skip_kblock.restype = None
         lib.sm120_debug_skip_kblock.argtypes = [c_int]
+        lib.sm120_debug_force_cta_group.restype = None
+        lib.sm120_debug_force_cta_group.argtypes = [c_int]
     except Exception as e:  # remember and re-raise on every later call
         _load_error = e
         raise

@@ -1,6 +1,7 @@
 // Tensor-core GEMM for B200 (sm_100a): tcgen05.mma with fp32 accumulators in
 // tensor memory (TMEM), operands staged in shared memory by TMA through a
-// multi-stage mbarrier ring, warp-specialised roles, persistent CTAs.
+// multi-stage mbarrier ring, warp-specialised roles, persistent CTAs, and an
+// epilogue that goes TMEM -> registers -> swizzled shared memory -> TMA store.
 //
 // It replaces the reference's WMMA-tiled GEMM family
 // (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:133-286 and :458-509) and
@@ -9,16 +10,26 @@
 // form of src/cuda_kernels/sm120_dynamic_shapes.cu:107-183 and the fused
 // bias + activation + cast epilogue.
 //
-// One CTA = 6 warps:
+// One CTA = 10 warps:
 //   warp 0      TMA producer (one lane): fills the shared-memory ring
 //   warp 1      TMEM allocator; one lane issues tcgen05.mma and the commits
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (32 TMEM lanes per warp),
-//               alpha/scale, beta*C, bias, activation, cast, 16-byte stores
-// The CTA tile is 128 x BN (BN = 64, 128 or 256) and the accumulator is double
-// buffered in TMEM (2*BN columns), so the epilogue of one tile overlaps the
-// main loop of the next.  Tiles are handed out statically (tile = blockIdx.x +
-// i*gridDim.x); there is no split-K and no atomic, so results are bitwise
-// reproducible from run to run.
+//   warps 2..9  epilogue.  Warp w reads TMEM lanes [32*(w%4), +32) (the hardware
+//               ties a warp to that quarter) and the column half (w-2)/4 of the
+//               tile, 32 columns at a time: tcgen05.ld, alpha/scale, bias,
+//               activation, cast, swizzled st.shared, one TMA store per 32x32 block.
+//
+// Two flavours, chosen by the template parameter CG:
+//   CG = 1  one CTA per tile of 128 x BN (BN = 64, 128, 256).
+//   CG = 2  a cluster of two CTAs per tile of 256 x 256 (tcgen05 cta_group::2).
+//           CTA r of the pair loads rows [128r, 128r+128) of the A tile and columns
+//           [128r, 128r+128) of the B tile into its own shared memory; the MMA
+//           issued by CTA 0 reads both CTAs' shared memory and writes both CTAs'
+//           TMEM (each CTA ends up with its 128 rows x 256 columns).  Per CTA this
+//           moves 32 KB per k-block from L2 instead of 48 KB for the same math.
+//           The TMA loads use no cluster multicast.
+// The accumulator is double buffered in TMEM, so the epilogue of one tile overlaps
+// the main loop of the next.  Tiles are handed out statically; there is no
+// split-K and no atomic, so results are bitwise reproducible from run to run.
 //
 // Operand layouts.  Each operand tile in shared memory is a sequence of
 // 128-byte-swizzled atoms exactly as TMA writes them:
@@ -27,14 +38,13 @@
 //   MN-major operand (M or N contiguous: A transposed, B not transposed):
 //     rows*es/128 boxes {128/es, BK}: box j covers 128 bytes of M/N; inside a box
 //     k-row k is at k*128 B.
-// BK is always 128 bytes of K (64 bf16/fp16, 128 fp8, 32 tf32), i.e. 4 MMA
-// K-steps of 32 bytes.
+// BK is always 128 bytes of K (64 bf16/fp16, 128 fp8), i.e. 4 MMA K-steps of 32 B.
 //
 // Every wait on an mbarrier is bounded by a wall-clock limit.  A role whose
 // wait runs out records a code in g_sm120_status, raises the CTA's abort flag
-// and leaves; the other roles see the flag in their own wait loops; the CTA then
-// waits (bounded) for its TMA copies and MMAs in flight, frees its TMEM and
-// returns normally.
+// (and its peer's) and leaves; the other roles see the flag in their own wait
+// loops; the CTA then waits (bounded) for its TMA copies and MMAs in flight,
+// frees its TMEM and returns normally.
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -46,18 +56,21 @@
 namespace sm120 {
 
 // status word 0: first timeout code seen (role<<28 | barrier kind<<24 | CTA),
-// word 1: number of CTAs that aborted.
+// word 1: number of waits that ran out.
 __device__ unsigned int g_sm120_status[4];
 
-enum : int { KIND_F16 = 0, KIND_F8 = 1, KIND_TF32 = 2 };
+enum : int { KIND_F16 = 0, KIND_F8 = 1 };
+enum : int { ACTC_NONE = 0, ACTC_RELU = 1, ACTC_GELU_ERF = 2, ACTC_DYNAMIC = 3 };
 
-constexpr int BM = 128;
-constexpr int NUM_THREADS = 192;
+constexpr int BM = 128;                 // rows per CTA
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int GROUP_M = 8;
+constexpr uint32_t EPI_STAGE_BYTES = 4096;   // per epilogue warp: 32 rows x 128 B
 
 struct TcParams {
     int M, N, K, batch;
-    int tiles_m, tiles_n, k_blocks, num_tiles;
+    int tiles_m, tiles_n, k_blocks, num_tiles;   // tiles are (CG*128) x BN
     uint32_t idesc;
     int a_mn_major, b_mn_major;
     int a_batched, b_batched;
@@ -65,9 +78,10 @@ struct TcParams {
     long long ldc, stride_c;
     int out_dtype;
     int c_vec_ok;                   // C rows may be written with 16-byte stores
+    int use_tma_store;              // epilogue goes through shared memory and TMA (needs beta == 0, aligned C)
     const void* bias;
     int bias_dtype;
-    int bias_vec_ok;                // bias is fp32 and 16-byte aligned
+    int bias_vec_ok;                // bias is 16-byte aligned
     float alpha, beta;
     const float* scale_a_dev;
     const float* scale_b_dev;
@@ -87,6 +101,23 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -96,12 +127,30 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// arrive on a barrier given by a shared::cluster address (own or peer CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// same with cluster-scope acquire: used where the arrivals come from the peer CTA
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
@@ -121,47 +170,91 @@ __device__ __forceinline__ void tcgen05_fence_before() {
 __device__ __forceinline__ void tcgen05_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
-// Tiled TMA load of one 3-D box into this CTA's shared memory; completion is
-// signalled as transaction bytes on `bar`.  No cluster multicast.
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int x, int y, int z) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
+
+template <int CG>
+__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t ncols) {
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(ncols) : "memory");
+    else
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(ncols) : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tmem_relinquish() {
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    else
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+    else
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrive on the mbarrier at shared::cluster address `bar` once every tcgen05.mma
+// issued so far by this thread has retired.
+template <int CG>
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    else
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-template <int KIND>
+// Tiled TMA load of one 3-D box into this CTA's shared memory; completion is
+// signalled as transaction bytes on `bar`.  With CG == 2 `bar` may be the
+// shared::cluster address of the pair leader's barrier.  No cluster multicast.
+template <int CG>
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int x, int y, int z) {
+    if constexpr (CG == 1)
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
+            : "memory");
+}
+// Tiled TMA store of one 3-D box from shared memory; out-of-range rows and
+// columns of the box are clipped by the hardware.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+template <int KIND, int CG>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (KIND == KIND_F16) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-    } else if constexpr (KIND == KIND_F8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    if constexpr (KIND == KIND_F16 && CG == 1) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (KIND == KIND_F16 && CG == 2) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (KIND == KIND_F8 && CG == 1) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
     } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
     }
 }
 
@@ -203,28 +296,36 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 // Bounded wait.  `code` identifies role and barrier for the status word.
 // ---------------------------------------------------------------------------
 struct WaitCtx {
-    volatile uint32_t* abort_flag;
+    volatile uint32_t* abort_flag;      // this CTA's flag
+    uint32_t peer_abort_addr;           // shared::cluster address of the peer CTA's flag, 0 without a peer
     unsigned long long limit_ns;
 };
+
+__device__ __forceinline__ void raise_abort(const WaitCtx& w, uint32_t code) {
+    *w.abort_flag = 1u;
+    if (w.peer_abort_addr != 0u)
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(w.peer_abort_addr), "r"(1u) : "memory");
+    atomicCAS(&g_sm120_status[0], 0u, code | (blockIdx.x & 0xFFFFFFu));
+    atomicAdd(&g_sm120_status[1], 1u);
+}
 
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code, bool watch_abort) {
     const unsigned long long t0 = global_timer_ns();
     uint32_t spins = 0;
+    const bool paired = w.peer_abort_addr != 0u;
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (paired ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if ((++spins & 31u) == 0u) {
             if (watch_abort && *w.abort_flag != 0u) return false;
             if (global_timer_ns() - t0 > w.limit_ns) {
-                *w.abort_flag = 1u;
-                atomicCAS(&g_sm120_status[0], 0u, code | (blockIdx.x & 0xFFFFFFu));
-                atomicAdd(&g_sm120_status[1], 1u);
+                raise_abort(w, code);
                 return false;
             }
         }
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code, bool watch_abort = true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (w.peer_abort_addr != 0u ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, w, code, watch_abort);
 }
 
@@ -241,20 +342,23 @@ __device__ __forceinline__ void decode_tile(int tile, const TcParams& p, int& bz
     tn = r / gm;
 }
 
-// Epilogue for 32 consecutive columns of one row held in registers.
-__device__ __forceinline__ void epilogue_row32(const TcParams& p, float alpha, uint32_t (&acc)[32], int bz, int row, int col0, bool row_ok) {
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[j]);
+// ---------------------------------------------------------------------------
+// Epilogue helpers.  Everything is fully unrolled over compile-time indices so
+// that the 32 values of a row segment stay in registers.
+// ---------------------------------------------------------------------------
+template <int ACTC>
+__device__ __forceinline__ float act_apply(float x, int act) {
+    if constexpr (ACTC == ACTC_NONE) return x;
+    else if constexpr (ACTC == ACTC_RELU) return fmaxf(0.0f, x);
+    else if constexpr (ACTC == ACTC_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    else return apply_activation(x, act);
+}
 
-    const int ncols = min(32, p.N - col0);
-    const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
-
-    if (p.beta != 0.0f && row_ok) {
-        for (int j = 0; j < ncols; ++j) v[j] += p.beta * load_as_float(p.C, off + j, p.out_dtype);
-    }
-    if (p.bias != nullptr) {
-        if (ncols == 32 && p.bias_vec_ok) {
+// v[j] += bias[col0 + j] for j < ncols
+__device__ __forceinline__ void add_bias32(const TcParams& p, int col0, int ncols, float (&v)[32]) {
+    if (p.bias == nullptr) return;
+    if (ncols == 32 && p.bias_vec_ok) {
+        if (p.bias_dtype == SM120_DTYPE_FLOAT32) {
             const float4* b4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + col0);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -262,16 +366,79 @@ __device__ __forceinline__ void epilogue_row32(const TcParams& p, float alpha, u
                 v[4 * j + 0] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
             }
         } else {
-            for (int j = 0; j < ncols; ++j) v[j] += load_as_float(p.bias, col0 + j, p.bias_dtype);
+            const uint4* b4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + col0);
+            const bool is_bf16 = p.bias_dtype == SM120_DTYPE_BFLOAT16;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 b = __ldg(b4 + j);
+                const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float lo, hi;
+                    if (is_bf16) {
+                        lo = __uint_as_float(w[k] << 16);
+                        hi = __uint_as_float(w[k] & 0xFFFF0000u);
+                    } else {
+                        const __half2 h = *reinterpret_cast<const __half2*>(&w[k]);
+                        lo = __low2float(h);
+                        hi = __high2float(h);
+                    }
+                    v[8 * j + 2 * k] += lo;
+                    v[8 * j + 2 * k + 1] += hi;
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < ncols) v[j] += load_as_float(p.bias, col0 + j, p.bias_dtype);
+    }
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ void pack16(const float (&v)[32], bool bf16, uint32_t (&packed)[16]) {
+    if (bf16) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
         }
     }
-    if (p.activation != SM120_ACTIVATION_NONE) {
-        const int act = p.activation;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = apply_activation(v[j], act);
-    }
-    if (!row_ok) return;
+}
 
+// Write this lane's 32 values as row `lane` of a 32 x 32 staging block laid out
+// as the TMA store expects it: rows of 128 B with the 128-byte swizzle for fp32
+// (16-byte chunk c of row r at chunk c ^ (r & 7)), rows of 64 B with the 64-byte
+// swizzle for 16-bit types (chunk c at c ^ ((r >> 1) & 3)).
+__device__ __forceinline__ void stage_row32(uint32_t block_addr, int lane, const float (&v)[32], int out_dtype) {
+    if (out_dtype == SM120_DTYPE_FLOAT32) {
+        const uint32_t row = block_addr + lane * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            st_shared_v4(row + ((c ^ (lane & 7)) << 4), __float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]),
+                         __float_as_uint(v[4 * c + 2]), __float_as_uint(v[4 * c + 3]));
+    } else {
+        uint32_t packed[16];
+        pack16(v, out_dtype == SM120_DTYPE_BFLOAT16, packed);
+        const uint32_t row = block_addr + lane * 64;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            st_shared_v4(row + ((c ^ ((lane >> 1) & 3)) << 4), packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+    }
+}
+
+// Direct path: this lane writes its row segment to global memory itself (used
+// when beta != 0 or when C cannot be described to TMA).
+__device__ __forceinline__ void store_row32_direct(const TcParams& p, long long off, int ncols, const float (&v)[32]) {
     if (ncols == 32 && p.c_vec_ok) {
         if (p.out_dtype == SM120_DTYPE_FLOAT32) {
             float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.C) + off);
@@ -279,51 +446,144 @@ __device__ __forceinline__ void epilogue_row32(const TcParams& p, float alpha, u
             for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         } else {
             uint32_t packed[16];
-            if (p.out_dtype == SM120_DTYPE_BFLOAT16) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                    packed[j] = *reinterpret_cast<uint32_t*>(&h);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                    packed[j] = *reinterpret_cast<uint32_t*>(&h);
-                }
-            }
+            pack16(v, p.out_dtype == SM120_DTYPE_BFLOAT16, packed);
             uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.C) + off);
 #pragma unroll
             for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
         }
     } else {
-        for (int j = 0; j < ncols; ++j) store_from_float(p.C, off + j, p.out_dtype, v[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < ncols) store_from_float(p.C, off + j, p.out_dtype, v[j]);
     }
 }
 
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int KIND, int BN, int STAGES>
+template <int KIND, int BN, int STAGES, int CG>
+struct TileCfg {
+    static constexpr int ES = (KIND == KIND_F16) ? 2 : 1;
+    static constexpr int EPB = 128 / ES;            // elements per 128 bytes
+    static constexpr int BK = EPB;                  // K elements per stage
+    static constexpr int UMMA_K = 32 / ES;          // K elements per tcgen05.mma
+    static constexpr int BN_CTA = BN / CG;          // columns of the B tile this CTA loads
+    static constexpr uint32_t A_BYTES = BM * 128;
+    static constexpr uint32_t B_BYTES = BN_CTA * 128;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t MN_BOX_BYTES = BK * 128;   // one {128 B of M/N, BK} box
+    static constexpr uint32_t TMEM_COLS = 2 * BN;        // 128, 256 or 512: a power of two >= 32
+    static constexpr uint32_t EPI_BYTES = EPI_WARPS * EPI_STAGE_BYTES;
+    static constexpr uint32_t BAR_BYTES = 256;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024 /* alignment slack */;
+    static_assert(BN_CTA % 64 == 0 && BN % 64 == 0, "tile width");
+    static_assert((2 * STAGES + 5) * 8 + 8 <= BAR_BYTES, "barrier block");
+    static_assert(SMEM <= 232448, "shared memory budget exceeded");
+    static_assert(SMEM > 116224, "one CTA per SM is assumed: shared memory must exceed half of an SM's");
+};
+
+template <int KIND, int BN, int STAGES, int CG, int ACTC>
+__device__ __forceinline__ void epilogue_role(const TcParams& p, const CUtensorMap* tmap_c, const WaitCtx& wctx,
+                                              uint32_t tmem_base, uint32_t acc_full_bar, uint32_t acc_empty_addr,
+                                              uint32_t stage_addr, int warp, int lane, uint32_t cta_rank, int first_tile,
+                                              int tile_step) {
+    const int lane_group = warp & 3;          // TMEM lanes [32*lane_group, +32) belong to this warp
+    const int half = (warp - 2) >> 2;         // which half of the tile's columns
+    constexpr int COLS_PER_WARP = BN / 2;
+    constexpr int CHUNKS = COLS_PER_WARP / 32;
+    float alpha = p.alpha;
+    if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
+    if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
+    const bool two_buffers = p.out_dtype != SM120_DTYPE_FLOAT32;   // 2 KB blocks: two fit in the warp's 4 KB
+    uint32_t stores = 0;
+    int local = 0;
+    for (int tile = first_tile; tile < p.num_tiles; tile += tile_step, ++local) {
+        int bz, tm, tn;
+        decode_tile(tile, p, bz, tm, tn);
+        const uint32_t buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
+        const int row = row0 + lane;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * COLS_PER_WARP;
+        const int colbase = tn * BN + half * COLS_PER_WARP;
+        bool released = false;
+#pragma unroll 1
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int col0 = colbase + c * 32;
+            if (col0 >= p.N) break;                        // warp-uniform
+            uint32_t acc[32];
+            __syncwarp();
+            tmem_ld_32x32(t_row + c * 32, acc);
+            tmem_ld_wait();
+            if (c == CHUNKS - 1 || col0 + 32 >= p.N) {
+                // the last columns of this warp are in registers: hand the TMEM buffer back early
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+                released = true;
+            }
+            const int ncols = min(32, p.N - col0);
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[j]);
+            const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
+            if (p.beta != 0.0f && row < p.M) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < ncols) v[j] += p.beta * load_as_float(p.C, off + j, p.out_dtype);
+            }
+            add_bias32(p, col0, ncols, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = act_apply<ACTC>(v[j], p.activation);
+
+            if (p.use_tma_store) {
+                const uint32_t block = stage_addr + ((two_buffers && (stores & 1u)) ? 2048u : 0u);
+                if (lane == 0) {
+                    // the block about to be overwritten must have been read by its TMA store
+                    if (two_buffers) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+                }
+                __syncwarp();
+                stage_row32(block, lane, v, p.out_dtype);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && row0 < p.M) {
+                    tma_store_3d(tmap_c, block, col0, row0, bz);
+                    bulk_commit_group();
+                }
+                ++stores;
+            } else if (row < p.M) {
+                store_row32_direct(p, off, ncols, v);
+            }
+        }
+        if (!released) {
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+        }
+    }
+    if (lane == 0) bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
+}
+
+template <int KIND, int BN, int STAGES, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                           const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_c,
                           const TcParams p) {
-    constexpr int ES = (KIND == KIND_F16) ? 2 : (KIND == KIND_F8 ? 1 : 4);
-    constexpr int EPB = 128 / ES;          // elements per 128 bytes
-    constexpr int BK = EPB;                // K elements per stage
-    constexpr int UMMA_K = 32 / ES;        // K elements per tcgen05.mma
-    constexpr uint32_t A_BYTES = BM * 128;
-    constexpr uint32_t B_BYTES = BN * 128;
-    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t MN_BOX_BYTES = BK * 128;   // one {128 B of M/N, BK} box
-    constexpr uint32_t TMEM_COLS = 2 * BN;        // 128, 256 or 512: a power of two >= 32
+    using Cfg = TileCfg<KIND, BN, STAGES, CG>;
+    constexpr int EPB = Cfg::EPB, BK = Cfg::BK, UMMA_K = Cfg::UMMA_K, BN_CTA = Cfg::BN_CTA;
+    constexpr uint32_t A_BYTES = Cfg::A_BYTES, STAGE_BYTES = Cfg::STAGE_BYTES, MN_BOX_BYTES = Cfg::MN_BOX_BYTES;
+    constexpr uint32_t TMEM_COLS = Cfg::TMEM_COLS;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;                       // 1024-byte aligned
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
     const uint32_t full_bar = smem_u32(bars);                       // [STAGES]
     const uint32_t empty_bar = smem_u32(bars + STAGES);             // [STAGES]
     const uint32_t acc_full_bar = smem_u32(bars + 2 * STAGES);      // [2]
@@ -334,7 +594,12 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const WaitCtx wctx{abort_flag, p.wait_limit_ns};
+    const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+    const bool leader = cta_rank == 0u;
+    const int first_tile = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = (CG == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    WaitCtx wctx{abort_flag, 0u, p.wait_limit_ns};
+    if constexpr (CG == 2) wctx.peer_abort_addr = map_to_cta(smem_u32(const_cast<uint32_t*>(abort_flag)), cta_rank ^ 1u);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -343,7 +608,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar + 8 * b, 1);
-            mbar_init(acc_empty_bar + 8 * b, 4);   // one arrival per epilogue warp
+            mbar_init(acc_empty_bar + 8 * b, EPI_WARPS * CG);   // one arrival per epilogue warp of every CTA of the pair
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0u;
@@ -351,13 +616,18 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fence_proxy_async_smem();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        prefetch_tmap(&tmap_c);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
-        tmem_relinquish();
+        tmem_alloc<CG>(smem_u32(tmem_holder), TMEM_COLS);
+        tmem_relinquish<CG>();
     }
     tcgen05_fence_before();
     __syncthreads();
+    if constexpr (CG == 2) {       // the peer's barriers must exist before anything signals them
+        cluster_arrive();
+        cluster_wait();
+    }
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
@@ -367,44 +637,49 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t stage = 0, phase = 0;
             long long issued = 0;
             bool ok = true;
-            bool first_tile = true;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+            bool first = true;
+            for (int tile = first_tile; ok && tile < p.num_tiles; tile += tile_step) {
                 int bz, tm, tn;
                 decode_tile(tile, p, bz, tm, tn);
                 const int za = p.a_batched ? bz : 0;
                 const int zb = p.b_batched ? bz : 0;
+                const int m0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
+                const int n0 = tn * BN + static_cast<int>(cta_rank) * BN_CTA;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (first_tile && kb == p.debug_skip_kblock) { ok = false; break; }
+                    if (first && kb == p.debug_skip_kblock) { ok = false; break; }
                     if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u)) { ok = false; break; }
-                    const uint32_t fb = full_bar + 8 * stage;
-                    mbar_expect_tx(fb, STAGE_BYTES);
+                    // transaction bytes of the whole pair are expected on the leader's barrier
+                    uint32_t fb = full_bar + 8 * stage;
+                    if (leader) mbar_expect_tx(fb, STAGE_BYTES * CG);
+                    if constexpr (CG == 2) fb = map_to_cta(fb, 0u);
                     const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
                     const uint32_t b_dst = a_dst + A_BYTES;
                     const int k0 = kb * BK;
                     if (!p.a_mn_major) {
-                        tma_load_3d(a_dst, &tmap_a, fb, k0, tm * BM, za);
+                        tma_load_3d<CG>(a_dst, &tmap_a, fb, k0, m0, za);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / EPB; ++j)
-                            tma_load_3d(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, tm * BM + j * EPB, k0, za);
+                            tma_load_3d<CG>(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, m0 + j * EPB, k0, za);
                     }
                     if (!p.b_mn_major) {
-                        tma_load_3d(b_dst, &tmap_b, fb, k0, tn * BN, zb);
+                        tma_load_3d<CG>(b_dst, &tmap_b, fb, k0, n0, zb);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / EPB; ++j)
-                            tma_load_3d(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, tn * BN + j * EPB, k0, zb);
+                        for (int j = 0; j < BN_CTA / EPB; ++j)
+                            tma_load_3d<CG>(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, n0 + j * EPB, k0, zb);
                     }
                     ++issued;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                first_tile = false;
+                first = false;
             }
-            // Before leaving, wait (bounded) until every copy this thread issued has
-            // landed: immediate on the normal path, where the MMA role consumed them all.
-            {
-                const long long first = issued > STAGES ? issued - STAGES : 0;
-                for (long long i = first; i < issued; ++i) {
+            // Before leaving, wait (bounded) until every copy issued has landed:
+            // immediate on the normal path, where the MMA role consumed them all.
+            // (Only the leader's barriers count transaction bytes.)
+            if (leader) {
+                const long long from = issued > STAGES ? issued - STAGES : 0;
+                for (long long i = from; i < issued; ++i) {
                     const uint32_t s = static_cast<uint32_t>(i % STAGES);
                     const uint32_t par = static_cast<uint32_t>((i / STAGES) & 1);
                     mbar_wait(full_bar + 8 * s, par, wctx, 0x13000000u, false);
@@ -412,13 +687,13 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
         }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+        if (lane == 0 && leader) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             bool issued_any = false;
             int local = 0;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+            for (int tile = first_tile; ok && tile < p.num_tiles; tile += tile_step, ++local) {
                 const uint32_t buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 if (!mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u)) { ok = false; break; }
@@ -437,62 +712,56 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const uint64_t b_desc = p.b_mn_major
                             ? make_smem_desc(b_base + kk * UMMA_K * 128, MN_BOX_BYTES, 1024)
                             : make_smem_desc(b_base + kk * 32, 16, 1024);
-                        umma_ss<KIND>(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+                        umma_ss<KIND, CG>(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
                     issued_any = true;
-                    umma_commit(empty_bar + 8 * stage);     // frees the stage when these MMAs retire
+                    // free the stage, in both CTAs of a pair, when these MMAs retire
+                    umma_commit<CG>(empty_bar + 8 * stage);
+                    if constexpr (CG == 2) umma_commit<CG>(map_to_cta(empty_bar + 8 * stage, 1u));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) umma_commit(acc_full_bar + 8 * buf);  // accumulator complete
+                if (ok) {                                   // accumulator complete, in both CTAs of a pair
+                    umma_commit<CG>(acc_full_bar + 8 * buf);
+                    if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
+                }
             }
             if (*abort_flag != 0u && issued_any) {
-                umma_commit(drain_bar);
+                umma_commit<CG>(drain_bar);
                 mbar_wait(drain_bar, 0u, wctx, 0x23000000u, false);
             }
         }
     } else {
         // ------------------------------ epilogue ------------------------------
-        const int lane_group = warp & 3;       // TMEM lanes [32*lane_group, +32) belong to this warp
-        float alpha = p.alpha;
-        if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
-        if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
-        bool ok = true;
-        int local = 0;
-        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
-            int bz, tm, tn;
-            decode_tile(tile, p, bz, tm, tn);
-            const uint32_t buf = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1;
-            ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
-            ok = __all_sync(0xFFFFFFFFu, ok);
-            if (!ok) break;
-            tcgen05_fence_after();
-            const int row = tm * BM + lane_group * 32 + lane;
-            const bool row_ok = row < p.M;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int col0 = tn * BN + c * 32;
-                if (col0 >= p.N) break;          // warp-uniform
-                uint32_t acc[32];
-                __syncwarp();
-                tmem_ld_32x32(t_row + c * 32, acc);
-                tmem_ld_wait();
-                epilogue_row32(p, alpha, acc, bz, row, col0, row_ok);
-            }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buf);
+        uint32_t acc_empty_addr = acc_empty_bar;                       // the leader's barrier collects every arrival
+        if constexpr (CG == 2) acc_empty_addr = map_to_cta(acc_empty_bar, 0u);
+        const uint32_t stage_addr = smem_u32(epi_smem) + (warp - 2) * EPI_STAGE_BYTES;
+        switch (p.activation) {
+            case SM120_ACTIVATION_NONE:
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_NONE>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                break;
+            case SM120_ACTIVATION_RELU:
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_RELU>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                break;
+            case SM120_ACTIVATION_GELU_ERF:
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_GELU_ERF>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                break;
+            default:
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_DYNAMIC>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                break;
         }
     }
 
     // ------------------------------ teardown ------------------------------
     tcgen05_fence_before();
     __syncthreads();
+    if constexpr (CG == 2) {       // neither CTA may leave while its peer can still touch its shared memory or TMEM
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
         __syncwarp();
         tcgen05_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -529,8 +798,8 @@ static CUtensorMapDataType tmap_dtype(int dtype) {
 
 // 3-D map over a stored matrix: `inner` contiguous elements per row, `outer`
 // rows `pitch` elements apart, `nbatch` matrices `bstride` elements apart.
-static bool encode_operand(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch,
-                           int64_t pitch, int64_t bstride, uint32_t box_inner, uint32_t box_outer) {
+static bool encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch,
+                      int64_t pitch, int64_t bstride, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = get_encode_fn();
     if (fn == nullptr) return false;
     const uint64_t es = static_cast<uint64_t>(dtype_size(dtype));
@@ -539,7 +808,7 @@ static bool encode_operand(CUtensorMap* map, const void* ptr, int dtype, int64_t
     cuuint32_t box[3] = {box_inner, box_outer, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, tmap_dtype(dtype), 3, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -567,65 +836,101 @@ bool tc_supported(const GemmProblem& p, const char** why) {
     return true;
 }
 
-template <int KIND, int BN, int STAGES>
-static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& tp, int grid, int device,
-                                  cudaStream_t stream) {
-    constexpr size_t SMEM = static_cast<size_t>(STAGES) * (BM * 128 + BN * 128) + 1024 /*align*/ + 256 /*barriers*/;
-    static_assert(SMEM <= 232448, "shared memory budget exceeded");
-    static_assert(SMEM > 116224, "one CTA per SM is assumed: shared memory must exceed half of an SM's");
-    static std::atomic<uint64_t> attr_done{0};   // one bit per device
-    auto kern = sm120_gemm_tcgen05_kernel<KIND, BN, STAGES>;
+static std::atomic<int> g_debug_skip_kblock{-1};
+void tc_set_debug_skip_kblock(int kb) { g_debug_skip_kblock.store(kb); }
+static std::atomic<int> g_force_cta_group{0};     // 0 = choose, 1 / 2 = force (tests and tuning)
+void tc_set_force_cta_group(int cg) { g_force_cta_group.store(cg); }
+
+template <int KIND, int BN, int STAGES, int CG>
+static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcParams& tp,
+                                  int sm_count, int device, cudaStream_t stream) {
+    using Cfg = TileCfg<KIND, BN, STAGES, CG>;
+    static std::atomic<uint64_t> attr_done{0};     // one bit per device
+    static std::atomic<int> max_clusters[64];      // CG == 2: co-resident clusters per device (0 = not asked yet)
+    auto kern = sm120_gemm_tcgen05_kernel<KIND, BN, STAGES, CG>;
     const uint64_t bit = 1ull << (device & 63);
     if ((attr_done.load(std::memory_order_acquire) & bit) == 0) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::SMEM));
         if (e != cudaSuccess) return e;
         attr_done.fetch_or(bit, std::memory_order_release);
     }
-    kern<<<grid, NUM_THREADS, SMEM, stream>>>(ta, tb, tp);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = max_clusters[device & 63].load(std::memory_order_acquire);
+        if (clusters == 0) {
+            cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1), 1, 1);
+            int n = 0;
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+            if (e != cudaSuccess) return e;
+            if (n < 1) return cudaErrorInvalidConfiguration;
+            clusters = n;
+            max_clusters[device & 63].store(n, std::memory_order_release);
+        }
+        const int want = tp.num_tiles < clusters ? tp.num_tiles : clusters;
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * want), 1, 1);
+    } else {
+        const int want = tp.num_tiles < sm_count ? tp.num_tiles : sm_count;
+        cfg.gridDim = dim3(static_cast<unsigned>(want), 1, 1);
+    }
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp);
 }
-
-static std::atomic<int> g_debug_skip_kblock{-1};
-void tc_set_debug_skip_kblock(int kb) { g_debug_skip_kblock.store(kb); }
 
 cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char** kernel_name) {
     const int es = dtype_size(p.in_dtype);
     const int epb = 128 / es;
     const int bk = epb;
-    const int kind = (p.in_dtype == SM120_DTYPE_FP8_E4M3) ? KIND_F8 : KIND_F16;
+    const bool fp8 = p.in_dtype == SM120_DTYPE_FP8_E4M3;
+    const bool a_mn = p.transpose_a != 0;       // stored [K,M]: M contiguous
+    const bool b_mn = p.transpose_b == 0;       // stored [K,N]: N contiguous
 
-    // Tile width: the widest BN that still gives every SM a tile; level 0 keeps 128.
-    const int64_t tiles_m = (p.M + BM - 1) / BM;
-    auto tiles_for = [&](int bn) { return tiles_m * ((p.N + bn - 1) / bn) * p.batch; };
-    // An MN-major operand is loaded in boxes of 128 bytes of M/N, so BN cannot be
-    // narrower than one box: 128 elements for 1-byte types.
-    const int min_bn = (!p.transpose_b && es == 1) ? 128 : 64;
-    int bn = min_bn;
+    // Tile choice.  A pair of CTAs on a 256 x 256 tile when that still gives every
+    // SM work; otherwise the widest single-CTA tile that does; level 0 keeps
+    // 128 x 128.  An MN-major operand is loaded in boxes of 128 bytes of M/N, so a
+    // CTA's share of the B tile cannot be narrower than one box (128 fp8 elements).
+    const int min_bn = (b_mn && es == 1) ? 128 : 64;
+    auto tiles_for = [&](int bm, int bn) { return ((p.M + bm - 1) / bm) * ((p.N + bn - 1) / bn) * p.batch; };
+    int cg = 1, bn = min_bn;
+    const int force = g_force_cta_group.load();
     if (p.optimization_level == 0) {
         bn = p.N > 64 ? 128 : min_bn;
     } else {
-        const int wide[2] = {256, 128};
-        for (int cand : wide) {
-            if (p.N > cand / 2 && tiles_for(cand) >= p.sm_count) { bn = cand; break; }
+        if (force != 1 && p.M > 128 && p.N > 128 && (force == 2 || tiles_for(256, 256) * 2 >= p.sm_count)) {
+            cg = 2; bn = 256;
+        } else {
+            const int wide[2] = {256, 128};
+            for (int cand : wide) {
+                if (p.N > cand / 2 && tiles_for(BM, cand) >= p.sm_count) { bn = cand; break; }
+            }
         }
     }
 
     TcParams tp{};
     tp.M = static_cast<int>(p.M); tp.N = static_cast<int>(p.N); tp.K = static_cast<int>(p.K);
     tp.batch = static_cast<int>(p.batch);
-    tp.tiles_m = static_cast<int>(tiles_m);
+    tp.tiles_m = static_cast<int>((p.M + BM * cg - 1) / (BM * cg));
     tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
     tp.k_blocks = static_cast<int>((p.K + bk - 1) / bk);
-    tp.num_tiles = static_cast<int>(tiles_for(bn));
-    tp.a_mn_major = p.transpose_a ? 1 : 0;     // stored [K,M]: M contiguous
-    tp.b_mn_major = p.transpose_b ? 0 : 1;     // stored [K,N]: N contiguous
+    tp.num_tiles = static_cast<int>(tiles_for(BM * cg, bn));
+    tp.a_mn_major = a_mn ? 1 : 0;
+    tp.b_mn_major = b_mn ? 1 : 0;
     tp.a_batched = (p.batch > 1 && p.stride_a != 0) ? 1 : 0;
     tp.b_batched = (p.batch > 1 && p.stride_b != 0) ? 1 : 0;
     tp.C = p.C; tp.ldc = p.ldc; tp.stride_c = p.stride_c; tp.out_dtype = p.out_dtype;
     const int out_es = dtype_size(p.out_dtype);
     tp.c_vec_ok = (aligned16(p.C) && (p.ldc * out_es) % 16 == 0 && (p.stride_c * out_es) % 16 == 0) ? 1 : 0;
+    tp.use_tma_store = (tp.c_vec_ok && p.beta == 0.0f && p.ldc * out_es < (1ll << 40) && p.stride_c * out_es < (1ll << 40)) ? 1 : 0;
     tp.bias = p.bias; tp.bias_dtype = p.bias_dtype;
-    tp.bias_vec_ok = (p.bias != nullptr && p.bias_dtype == SM120_DTYPE_FLOAT32 && aligned16(p.bias)) ? 1 : 0;
+    tp.bias_vec_ok = (p.bias != nullptr && aligned16(p.bias)) ? 1 : 0;
     tp.alpha = p.alpha * p.inv_scale; tp.beta = p.beta;
     tp.scale_a_dev = p.scale_a_dev; tp.scale_b_dev = p.scale_b_dev;
     tp.activation = p.activation;
@@ -635,50 +940,48 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     // Instruction descriptor (tcgen05.mma kind::f16 / kind::f8f6f4):
     //   bits 4..5 accumulator format (1 = f32), 7..9 A format, 10..12 B format
     //   (kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3), 15 / 16 = A / B is
-    //   MN-major, 17..22 = N >> 3, 24..28 = M >> 4.
+    //   MN-major, 17..22 = N >> 3, 24..28 = M >> 4 (M = 256 for a CTA pair).
     const uint32_t fmt = (p.in_dtype == SM120_DTYPE_BFLOAT16) ? 1u : 0u;
     tp.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tp.a_mn_major) << 15) |
                (static_cast<uint32_t>(tp.b_mn_major) << 16) | (static_cast<uint32_t>(bn >> 3) << 17) |
-               (static_cast<uint32_t>(BM >> 4) << 24);
+               (static_cast<uint32_t>((BM * cg) >> 4) << 24);
 
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     const int64_t nb_a = tp.a_batched ? p.batch : 1;
     const int64_t nb_b = tp.b_batched ? p.batch : 1;
+    const uint32_t bn_cta = static_cast<uint32_t>(bn / cg);
     bool ok;
-    if (!tp.a_mn_major) {
-        const int64_t bs = tp.a_batched ? p.stride_a : p.M * p.lda;
-        ok = encode_operand(&ta, p.A, p.in_dtype, p.K, p.M, nb_a, p.lda, bs, bk, BM);
-    } else {
-        const int64_t bs = tp.a_batched ? p.stride_a : p.K * p.lda;
-        ok = encode_operand(&ta, p.A, p.in_dtype, p.M, p.K, nb_a, p.lda, bs, epb, bk);
-    }
+    if (!a_mn) ok = encode_3d(&ta, p.A, p.in_dtype, p.K, p.M, nb_a, p.lda, tp.a_batched ? p.stride_a : p.M * p.lda, bk, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    else       ok = encode_3d(&ta, p.A, p.in_dtype, p.M, p.K, nb_a, p.lda, tp.a_batched ? p.stride_a : p.K * p.lda, epb, bk, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
-    if (!tp.b_mn_major) {
-        const int64_t bs = tp.b_batched ? p.stride_b : p.N * p.ldb;
-        ok = encode_operand(&tb, p.B, p.in_dtype, p.K, p.N, nb_b, p.ldb, bs, bk, bn);
-    } else {
-        const int64_t bs = tp.b_batched ? p.stride_b : p.K * p.ldb;
-        ok = encode_operand(&tb, p.B, p.in_dtype, p.N, p.K, nb_b, p.ldb, bs, epb, bk);
-    }
+    if (!b_mn) ok = encode_3d(&tb, p.B, p.in_dtype, p.K, p.N, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.N * p.ldb, bk, bn_cta, CU_TENSOR_MAP_SWIZZLE_128B);
+    else       ok = encode_3d(&tb, p.B, p.in_dtype, p.N, p.K, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.K * p.ldb, epb, bk, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
+    if (tp.use_tma_store) {
+        // 32 x 32 output blocks: rows of 128 B (fp32, 128-byte swizzle) or 64 B (16-bit, 64-byte swizzle)
+        ok = encode_3d(&tc, p.C, p.out_dtype, p.N, p.M, p.batch, p.ldc, p.batch > 1 ? p.stride_c : p.M * p.ldc, 32, 32,
+                       out_es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+        if (!ok) tp.use_tma_store = 0;
+    }
+    if (!tp.use_tma_store) tc = ta;      // never dereferenced by the kernel
 
-    const int grid = tp.num_tiles < p.sm_count ? tp.num_tiles : p.sm_count;
-
-#define SM120_TC_CASE(KIND_, BN_, ST_, NAME_)                                                   \
-    do {                                                                                        \
-        if (kernel_name) *kernel_name = NAME_;                                                  \
-        return launch_variant<KIND_, BN_, ST_>(ta, tb, tp, grid, p.device, p.stream);            \
+#define SM120_TC_CASE(KIND_, BN_, ST_, CG_, NAME_)                                                       \
+    do {                                                                                                 \
+        if (kernel_name) *kernel_name = NAME_;                                                           \
+        return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);       \
     } while (0)
 
-    if (kind == KIND_F16) {
+    if (!fp8) {
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
-        if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
-        if (bn == 128) SM120_TC_CASE(KIND_F16, 128, 6, bf ? "tc_bf16_128x128x64_s6" : "tc_f16_128x128x64_s6");
-        SM120_TC_CASE(KIND_F16, 64, 8, bf ? "tc_bf16_128x64x64_s8" : "tc_f16_128x64x64_s8");
+        if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 6, 2, bf ? "tc_bf16_2cta_256x256x64_s6" : "tc_f16_2cta_256x256x64_s6");
+        if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
+        if (bn == 128) SM120_TC_CASE(KIND_F16, 128, 6, 1, bf ? "tc_bf16_128x128x64_s6" : "tc_f16_128x128x64_s6");
+        SM120_TC_CASE(KIND_F16, 64, 8, 1, bf ? "tc_bf16_128x64x64_s8" : "tc_f16_128x64x64_s8");
     } else {
-        if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, "tc_e4m3_128x256x128_s4");
-        if (bn == 128) SM120_TC_CASE(KIND_F8, 128, 6, "tc_e4m3_128x128x128_s6");
-        SM120_TC_CASE(KIND_F8, 64, 8, "tc_e4m3_128x64x128_s8");
+        if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 6, 2, "tc_e4m3_2cta_256x256x128_s6");
+        if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, 1, "tc_e4m3_128x256x128_s4");
+        if (bn == 128) SM120_TC_CASE(KIND_F8, 128, 6, 1, "tc_e4m3_128x128x128_s6");
+        SM120_TC_CASE(KIND_F8, 64, 8, 1, "tc_e4m3_128x64x128_s8");
     }
 #undef SM120_TC_CASE
 }

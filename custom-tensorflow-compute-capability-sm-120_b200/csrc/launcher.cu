@@ -18,6 +18,7 @@
 namespace sm120 {
 
 void tc_set_debug_skip_kblock(int kb);
+void tc_set_force_cta_group(int cg);
 
 namespace {
 
@@ -265,5 +266,10 @@ const char* sm120_get_last_kernel_name(void) { return t_last_kernel; }
 // stops before filling k-block `kb` of its first tile, so the consumer's bounded
 // wait runs out and the status word is set.  kb < 0 switches the hook off.
 void sm120_debug_skip_kblock(int kb) { tc_set_debug_skip_kblock(kb); }
+
+// Tuning/test hook, not declared in the public header: 1 or 2 forces the
+// single-CTA or the CTA-pair flavour of the tensor-core kernel, 0 restores the
+// launcher's own choice.
+void sm120_debug_force_cta_group(int cg) { tc_set_force_cta_group(cg); }
 
 }  // extern "C"
