@@ -11,12 +11,13 @@
 // bias + activation + cast epilogue.
 //
 // One CTA = 10 warps:
-//   warp 0      TMA producer (one lane): fills the shared-memory ring
-//   warp 1      TMEM allocator; one lane issues tcgen05.mma and the commits
+//   warp 0      TMA producer (one elected lane issues): fills the shared-memory ring
+//   warp 1      TMEM allocator; one elected lane issues tcgen05.mma and the commits
 //   warps 2..9  epilogue.  Warp w reads TMEM lanes [32*(w%4), +32) (the hardware
 //               ties a warp to that quarter) and the column half (w-2)/4 of the
 //               tile, 32 columns at a time: tcgen05.ld, alpha/scale, bias,
-//               activation, cast, swizzled st.shared, one TMA store per 32x32 block.
+//               activation, cast, swizzled st.shared; the four warps of a column half
+//               share a 128-row staging block and one TMA store per 128 x 64 (or 32) block.
 //
 // Two flavours, chosen by the template parameter CG:
 //   CG = 1  one CTA per tile of 128 x BN (BN = 64, 128, 256).
@@ -58,6 +59,8 @@ namespace sm120 {
 // status word 0: first timeout code seen (role<<28 | barrier kind<<24 | CTA),
 // word 1: number of waits that ran out.
 __device__ unsigned int g_sm120_status[4];
+// [0] SM cycles and [1] nanoseconds that CTA 0 of the last launch was alive (clock probe for tuning)
+__device__ unsigned long long g_sm120_probe[2];
 
 enum : int { KIND_F16 = 0, KIND_F8 = 1 };
 enum : int { ACTC_NONE = 0, ACTC_RELU = 1, ACTC_GELU_ERF = 2, ACTC_DYNAMIC = 3 };
@@ -66,7 +69,7 @@ constexpr int BM = 128;                 // rows per CTA
 constexpr int EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int GROUP_M = 8;
-constexpr uint32_t EPI_STAGE_BYTES = 4096;   // per epilogue warp: 32 rows x 128 B
+constexpr uint32_t EPI_STAGE_BYTES = 4096;   // per epilogue warp: 32 rows x 128 B (four warps share 128 rows)
 
 struct TcParams {
     int M, N, K, batch;
@@ -79,6 +82,8 @@ struct TcParams {
     int out_dtype;
     int c_vec_ok;                   // C rows may be written with 16-byte stores
     int use_tma_store;              // epilogue goes through shared memory and TMA (needs beta == 0, aligned C)
+    int epi_cols;                   // columns per TMA store: 64 or 32 (one staging row of 128 or 64 bytes)
+    int epi_row_bytes;              // bytes per staging row: 128 or 64
     const void* bias;
     int bias_dtype;
     int bias_vec_ok;                // bias is 16-byte aligned
@@ -87,6 +92,7 @@ struct TcParams {
     const float* scale_b_dev;
     int activation;
     int debug_skip_kblock;          // >= 0: the producer never fills this k-block of its first tile (wait-limit test)
+    int debug_mode;                 // timing experiments only (results are garbage): 1 = no MMA issue, 2 = no TMA loads
     unsigned long long wait_limit_ns;
 };
 
@@ -111,6 +117,18 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
     return r;
+}
+// true in exactly one lane of a fully active warp
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "elect.sync _|P, 0xFFFFFFFF;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void cluster_arrive() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -346,53 +364,122 @@ __device__ __forceinline__ void decode_tile(int tile, const TcParams& p, int& bz
 // Epilogue helpers.  Everything is fully unrolled over compile-time indices so
 // that the 32 values of a row segment stay in registers.
 // ---------------------------------------------------------------------------
-template <int ACTC>
-__device__ __forceinline__ float act_apply(float x, int act) {
-    if constexpr (ACTC == ACTC_NONE) return x;
-    else if constexpr (ACTC == ACTC_RELU) return fmaxf(0.0f, x);
-    else if constexpr (ACTC == ACTC_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
-    else return apply_activation(x, act);
+// GELU with the exact (erf) definition, evaluated with the Abramowitz-Stegun
+// 7.1.26 rational approximation of erf (|error| <= 1.5e-7) and the hardware
+// exponential: about a third of the instructions of erff().  Measured against
+// the float64 definition the absolute error of the result stays below 5e-7.
+__device__ __forceinline__ float gelu_erf_fast(float x) {
+    const float z = x * 0.70710678118654752440f;
+    const float az = fabsf(z);
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, az, 1.0f));
+    float poly = 1.061405429f;
+    poly = fmaf(poly, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    poly *= t;
+    const float erf_abs = fmaf(-poly, __expf(-az * az), 1.0f);
+    return 0.5f * x * (1.0f + copysignf(erf_abs, z));
 }
 
-// v[j] += bias[col0 + j] for j < ncols
-__device__ __forceinline__ void add_bias32(const TcParams& p, int col0, int ncols, float (&v)[32]) {
-    if (p.bias == nullptr) return;
-    if (ncols == 32 && p.bias_vec_ok) {
-        if (p.bias_dtype == SM120_DTYPE_FLOAT32) {
-            const float4* b4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + col0);
+template <int ACT>
+__device__ __forceinline__ void act_loop(float (&v)[32]) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 b = __ldg(b4 + j);
-                v[4 * j + 0] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
-            }
-        } else {
-            const uint4* b4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + col0);
-            const bool is_bf16 = p.bias_dtype == SM120_DTYPE_BFLOAT16;
+    for (int j = 0; j < 32; ++j) v[j] = apply_activation(v[j], ACT);     // ACT is a constant: the switch folds
+}
+
+// Apply the activation to the 32 values.  The three common cases are compile-time
+// (ACTC); the rest dispatch ONCE per 32 values so that only one formula's code is
+// executed (a switch inside the unrolled loop would put every formula 32 times
+// into the instruction stream).
+template <int ACTC>
+__device__ __forceinline__ void act_apply32(float (&v)[32], int act) {
+    if constexpr (ACTC == ACTC_NONE) {
+        return;
+    } else if constexpr (ACTC == ACTC_RELU) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint4 b = __ldg(b4 + j);
-                const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+        for (int j = 0; j < 32; ++j) v[j] = fmaxf(0.0f, v[j]);
+    } else if constexpr (ACTC == ACTC_GELU_ERF) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float lo, hi;
-                    if (is_bf16) {
-                        lo = __uint_as_float(w[k] << 16);
-                        hi = __uint_as_float(w[k] & 0xFFFF0000u);
-                    } else {
-                        const __half2 h = *reinterpret_cast<const __half2*>(&w[k]);
-                        lo = __low2float(h);
-                        hi = __high2float(h);
-                    }
-                    v[8 * j + 2 * k] += lo;
-                    v[8 * j + 2 * k + 1] += hi;
-                }
-            }
+        for (int j = 0; j < 32; ++j) v[j] = gelu_erf_fast(v[j]);
+    } else {
+        switch (act) {
+            case SM120_ACTIVATION_LEAKY_RELU: act_loop<SM120_ACTIVATION_LEAKY_RELU>(v); break;
+            case SM120_ACTIVATION_ELU:        act_loop<SM120_ACTIVATION_ELU>(v); break;
+            case SM120_ACTIVATION_SELU:       act_loop<SM120_ACTIVATION_SELU>(v); break;
+            case SM120_ACTIVATION_GELU:       act_loop<SM120_ACTIVATION_GELU>(v); break;
+            case SM120_ACTIVATION_SWISH:      act_loop<SM120_ACTIVATION_SWISH>(v); break;
+            case SM120_ACTIVATION_MISH:       act_loop<SM120_ACTIVATION_MISH>(v); break;
+            case SM120_ACTIVATION_TANH:       act_loop<SM120_ACTIVATION_TANH>(v); break;
+            case SM120_ACTIVATION_SIGMOID:    act_loop<SM120_ACTIVATION_SIGMOID>(v); break;
+            default: break;
+        }
+    }
+}
+
+// Bias for 32 consecutive columns.  A 16-bit bias (64 bytes) is fetched early as
+// four raw 16-byte words (every lane reads the same addresses) and added later,
+// so that the load latency overlaps other work; an fp32 bias is read where it is
+// added (prefetching its 32 registers would spill).
+struct BiasRaw { uint4 q[4]; };
+
+__device__ __forceinline__ void bias_prefetch32(const TcParams& p, int col0, BiasRaw& r) {
+    if (p.bias_dtype != SM120_DTYPE_FLOAT32) {
+        const uint4* b = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r.q[j] = __ldg(b + j);
+    }
+}
+
+__device__ __forceinline__ void bias_add_raw32(const TcParams& p, int col0, const BiasRaw& r, float (&v)[32]) {
+    if (p.bias_dtype == SM120_DTYPE_FLOAT32) {
+        const float4* b4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + col0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 b = __ldg(b4 + j);
+            v[4 * j + 0] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
         }
     } else {
+        const bool is_bf16 = p.bias_dtype == SM120_DTYPE_BFLOAT16;
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (j < ncols) v[j] += load_as_float(p.bias, col0 + j, p.bias_dtype);
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t w[4] = {r.q[j].x, r.q[j].y, r.q[j].z, r.q[j].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float lo, hi;
+                if (is_bf16) {
+                    lo = __uint_as_float(w[k] << 16);
+                    hi = __uint_as_float(w[k] & 0xFFFF0000u);
+                } else {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&w[k]);
+                    lo = __low2float(h);
+                    hi = __high2float(h);
+                }
+                v[8 * j + 2 * k] += lo;
+                v[8 * j + 2 * k + 1] += hi;
+            }
+        }
     }
+}
+
+// v[j] += bias[col0 + j] for j < ncols, element by element (ragged or unaligned bias)
+__device__ __forceinline__ void bias_add_scalar32(const TcParams& p, int col0, int ncols, float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+        if (j < ncols) v[j] += load_as_float(p.bias, col0 + j, p.bias_dtype);
+}
+
+// tcgen05.wait::ld that also names the destination registers of the load, so
+// that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;"
+        : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+          "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+          "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+          "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+        :
+        : "memory");
 }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -415,25 +502,48 @@ __device__ __forceinline__ void pack16(const float (&v)[32], bool bf16, uint32_t
     }
 }
 
-// Write this lane's 32 values as row `lane` of a 32 x 32 staging block laid out
-// as the TMA store expects it: rows of 128 B with the 128-byte swizzle for fp32
-// (16-byte chunk c of row r at chunk c ^ (r & 7)), rows of 64 B with the 64-byte
-// swizzle for 16-bit types (chunk c at c ^ ((r >> 1) & 3)).
-__device__ __forceinline__ void stage_row32(uint32_t block_addr, int lane, const float (&v)[32], int out_dtype) {
+// Write this thread's 32 values into row `r` (0..127) of the staging block of its
+// column half, laid out as the TMA store expects it.  Rows are `row_bytes` long
+// (128 or 64); the 32 values fill 16-byte chunks [first_chunk, first_chunk + n)
+// of the row (n = 8 for fp32, 4 for 16-bit types); chunk c of row r is stored at
+// chunk c ^ (r & 7) under the 128-byte swizzle and at c ^ ((r >> 1) & 3) under the
+// 64-byte swizzle, which also keeps the st.shared free of bank conflicts.
+__device__ __forceinline__ void stage_row32(uint32_t block_addr, int r, int row_bytes, int first_chunk,
+                                            const float (&v)[32], int out_dtype) {
+    const uint32_t row = block_addr + r * row_bytes;
+    const int sw = (row_bytes == 128) ? (r & 7) : ((r >> 1) & 3);
     if (out_dtype == SM120_DTYPE_FLOAT32) {
-        const uint32_t row = block_addr + lane * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-            st_shared_v4(row + ((c ^ (lane & 7)) << 4), __float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]),
+            st_shared_v4(row + (((first_chunk + c) ^ sw) << 4), __float_as_uint(v[4 * c]), __float_as_uint(v[4 * c + 1]),
                          __float_as_uint(v[4 * c + 2]), __float_as_uint(v[4 * c + 3]));
     } else {
         uint32_t packed[16];
         pack16(v, out_dtype == SM120_DTYPE_BFLOAT16, packed);
-        const uint32_t row = block_addr + lane * 64;
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-            st_shared_v4(row + ((c ^ ((lane >> 1) & 3)) << 4), packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            st_shared_v4(row + (((first_chunk + c) ^ sw) << 4), packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
     }
+}
+
+// Named barrier among the 128 threads of one column half of the epilogue.
+__device__ __forceinline__ void half_barrier(int id) {
+    asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
+}
+// The same barrier with an AND vote: true when every participant passed true.
+__device__ __forceinline__ bool half_barrier_all(int id, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %2, 0;\n\t"
+        "bar.red.and.pred p, %1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(r)
+        : "r"(id), "r"(pred ? 1u : 0u)
+        : "memory");
+    return r != 0;
 }
 
 // Direct path: this lane writes its row segment to global memory itself (used
@@ -494,78 +604,98 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const CUtensorM
     float alpha = p.alpha;
     if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
     if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
-    const bool two_buffers = p.out_dtype != SM120_DTYPE_FLOAT32;   // 2 KB blocks: two fit in the warp's 4 KB
-    uint32_t stores = 0;
+    const bool has_bias = p.bias != nullptr;
     int local = 0;
     for (int tile = first_tile; tile < p.num_tiles; tile += tile_step, ++local) {
         int bz, tm, tn;
         decode_tile(tile, p, bz, tm, tn);
         const uint32_t buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
-        ok = __all_sync(0xFFFFFFFFu, ok);
-        if (!ok) break;
-        tcgen05_fence_after();
         const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
         const int row = row0 + lane;
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * COLS_PER_WARP;
         const int colbase = tn * BN + half * COLS_PER_WARP;
-        bool released = false;
-#pragma unroll 1
-        for (int c = 0; c < CHUNKS; ++c) {
-            const int col0 = colbase + c * 32;
-            if (col0 >= p.N) break;                        // warp-uniform
-            uint32_t acc[32];
-            __syncwarp();
-            tmem_ld_32x32(t_row + c * 32, acc);
-            tmem_ld_wait();
-            if (c == CHUNKS - 1 || col0 + 32 >= p.N) {
-                // the last columns of this warp are in registers: hand the TMEM buffer back early
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
-                released = true;
-            }
-            const int ncols = min(32, p.N - col0);
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[j]);
-            const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
-            if (p.beta != 0.0f && row < p.M) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (j < ncols) v[j] += p.beta * load_as_float(p.C, off + j, p.out_dtype);
-            }
-            add_bias32(p, col0, ncols, v);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = act_apply<ACTC>(v[j], p.activation);
+        // chunks of 32 columns this warp owns that start inside the matrix (warp-uniform)
+        const int nvalid = max(0, min(CHUNKS, (p.N - colbase + 31) / 32));
+        BiasRaw braw;
+        // the first chunk's bias is fetched before the wait for the accumulator
+        if (has_bias && p.bias_vec_ok && nvalid > 0 && colbase + 32 <= p.N) bias_prefetch32(p, colbase, braw);
 
-            if (p.use_tma_store) {
-                const uint32_t block = stage_addr + ((two_buffers && (stores & 1u)) ? 2048u : 0u);
-                if (lane == 0) {
-                    // the block about to be overwritten must have been read by its TMA store
-                    if (two_buffers) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+        bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        // the four warps of a column half share staging memory and named barriers: they go on, or leave, together
+        ok = half_barrier_all(1 + half, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * COLS_PER_WARP;
+        const int cta_row0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
+        const int spg = p.epi_cols >> 5;                    // 32-column chunks per TMA store: 1 or 2
+        const int chunk16_per_sub = (p.out_dtype == SM120_DTYPE_FLOAT32) ? 8 : 4;
+
+        uint32_t acc[2][32];
+        __syncwarp();
+        if (nvalid > 0) tmem_ld_32x32(t_row, acc[0]);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            if (c < nvalid) {                               // warp-uniform, and the same in the four warps of a half
+                const int col0 = colbase + c * 32;
+                const int ncols = min(32, p.N - col0);
+                tmem_ld_wait_regs(acc[c & 1]);
+                if (c + 1 < nvalid) {
+                    __syncwarp();
+                    tmem_ld_32x32(t_row + (c + 1) * 32, acc[(c + 1) & 1]);   // in flight while this chunk is processed
+                } else {
+                    // every column of this warp is in registers: hand the TMEM buffer back
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
                 }
-                __syncwarp();
-                stage_row32(block, lane, v, p.out_dtype);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0 && row0 < p.M) {
-                    tma_store_3d(tmap_c, block, col0, row0, bz);
-                    bulk_commit_group();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[c & 1][j]);
+                const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
+                if (p.beta != 0.0f && row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < ncols) v[j] += p.beta * load_as_float(p.C, off + j, p.out_dtype);
                 }
-                ++stores;
-            } else if (row < p.M) {
-                store_row32_direct(p, off, ncols, v);
+                if (has_bias) {
+                    if (p.bias_vec_ok && ncols == 32) bias_add_raw32(p, col0, braw, v);
+                    else bias_add_scalar32(p, col0, ncols, v);
+                    // fetch the next chunk's bias now; it is consumed one chunk later
+                    if (p.bias_vec_ok && c + 1 < nvalid && col0 + 64 <= p.N) bias_prefetch32(p, col0 + 32, braw);
+                }
+                act_apply32<ACTC>(v, p.activation);
+
+                if (p.use_tma_store) {
+                    const int sub = (spg == 2) ? (c & 1) : 0;           // position of this chunk in its store
+                    const bool first_of_store = sub == 0;
+                    const bool last_of_store = (sub == spg - 1) || (c == nvalid - 1);
+                    if (first_of_store) {
+                        // the staging block is about to be overwritten: its previous TMA store must have read it
+                        if (lane_group == 0 && lane == 0) bulk_wait_group_read<0>();
+                        half_barrier(1 + half);
+                    }
+                    stage_row32(stage_addr, lane_group * 32 + lane, p.epi_row_bytes, sub * chunk16_per_sub, v, p.out_dtype);
+                    if (last_of_store) {
+                        fence_proxy_async_smem();
+                        half_barrier(1 + half);
+                        if (lane_group == 0 && lane == 0 && cta_row0 < p.M) {
+                            tma_store_3d(tmap_c, stage_addr, col0 - sub * 32, cta_row0, bz);
+                            bulk_commit_group();
+                        }
+                    }
+                } else if (row < p.M) {
+                    store_row32_direct(p, off, ncols, v);
+                }
             }
         }
-        if (!released) {
+        if (nvalid == 0) {
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
         }
     }
-    if (lane == 0) bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
+    if (lane_group == 0 && lane == 0) bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
 }
 
 template <int KIND, int BN, int STAGES, int CG>
@@ -594,6 +724,8 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const long long probe_c0 = clock64();
+    const unsigned long long probe_t0 = global_timer_ns();
     const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
     const bool leader = cta_rank == 0u;
     const int first_tile = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
@@ -633,62 +765,81 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            long long issued = 0;
-            bool ok = true;
-            bool first = true;
-            for (int tile = first_tile; ok && tile < p.num_tiles; tile += tile_step) {
-                int bz, tm, tn;
-                decode_tile(tile, p, bz, tm, tn);
-                const int za = p.a_batched ? bz : 0;
-                const int zb = p.b_batched ? bz : 0;
-                const int m0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
-                const int n0 = tn * BN + static_cast<int>(cta_rank) * BN_CTA;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (first && kb == p.debug_skip_kblock) { ok = false; break; }
-                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u)) { ok = false; break; }
-                    // transaction bytes of the whole pair are expected on the leader's barrier
-                    uint32_t fb = full_bar + 8 * stage;
-                    if (leader) mbar_expect_tx(fb, STAGE_BYTES * CG);
-                    if constexpr (CG == 2) fb = map_to_cta(fb, 0u);
-                    const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
-                    const uint32_t b_dst = a_dst + A_BYTES;
-                    const int k0 = kb * BK;
-                    if (!p.a_mn_major) {
-                        tma_load_3d<CG>(a_dst, &tmap_a, fb, k0, m0, za);
+        // The whole warp runs the loop (so that its variables stay warp-uniform and
+        // can live in uniform registers); one elected lane issues the copies.
+        uint32_t stage = 0, phase = 0;
+        long long issued = 0;
+        bool ok = true;
+        bool first = true;
+        const uint32_t full_for_tma = (CG == 2) ? map_to_cta(full_bar, 0u) : full_bar;   // the pair leader's barriers
+        for (int tile = first_tile; ok && tile < p.num_tiles; tile += tile_step) {
+            int bz, tm, tn;
+            decode_tile(tile, p, bz, tm, tn);
+            const int za = p.a_batched ? bz : 0;
+            const int zb = p.b_batched ? bz : 0;
+            const int m0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
+            const int n0 = tn * BN + static_cast<int>(cta_rank) * BN_CTA;
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                if (first && kb == p.debug_skip_kblock) { ok = false; break; }
+                bool w = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u);
+                w = __all_sync(0xFFFFFFFFu, w);
+                if (!w) { ok = false; break; }
+                if (elect_one_sync()) {
+                    if (p.debug_mode == 2) {
+                        if (leader) mbar_arrive(full_bar + 8 * stage);
                     } else {
+                        // transaction bytes of the whole pair are expected on the leader's barrier
+                        if (leader) mbar_expect_tx(full_bar + 8 * stage, STAGE_BYTES * CG);
+                        const uint32_t fb = full_for_tma + 8 * stage;
+                        const uint32_t a_dst = smem_u32(smem) + stage * STAGE_BYTES;
+                        const uint32_t b_dst = a_dst + A_BYTES;
+                        const int k0 = kb * BK;
+                        if (!p.a_mn_major) {
+                            tma_load_3d<CG>(a_dst, &tmap_a, fb, k0, m0, za);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BM / EPB; ++j)
-                            tma_load_3d<CG>(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, m0 + j * EPB, k0, za);
-                    }
-                    if (!p.b_mn_major) {
-                        tma_load_3d<CG>(b_dst, &tmap_b, fb, k0, n0, zb);
-                    } else {
+                            for (int j = 0; j < BM / EPB; ++j)
+                                tma_load_3d<CG>(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, m0 + j * EPB, k0, za);
+                        }
+                        if (!p.b_mn_major) {
+                            tma_load_3d<CG>(b_dst, &tmap_b, fb, k0, n0, zb);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BN_CTA / EPB; ++j)
-                            tma_load_3d<CG>(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, n0 + j * EPB, k0, zb);
+                            for (int j = 0; j < BN_CTA / EPB; ++j)
+                                tma_load_3d<CG>(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, n0 + j * EPB, k0, zb);
+                        }
                     }
-                    ++issued;
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                first = false;
+                __syncwarp();
+                ++issued;
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
-            // Before leaving, wait (bounded) until every copy issued has landed:
-            // immediate on the normal path, where the MMA role consumed them all.
-            // (Only the leader's barriers count transaction bytes.)
-            if (leader) {
-                const long long from = issued > STAGES ? issued - STAGES : 0;
-                for (long long i = from; i < issued; ++i) {
-                    const uint32_t s = static_cast<uint32_t>(i % STAGES);
-                    const uint32_t par = static_cast<uint32_t>((i / STAGES) & 1);
-                    mbar_wait(full_bar + 8 * s, par, wctx, 0x13000000u, false);
-                }
+            first = false;
+        }
+        // Before leaving, wait (bounded) until every copy issued has landed:
+        // immediate on the normal path, where the MMA role consumed them all.
+        // (Only the leader's barriers count transaction bytes.)
+        if (leader) {
+            const long long from = issued > STAGES ? issued - STAGES : 0;
+            for (long long i = from; i < issued; ++i) {
+                const uint32_t s = static_cast<uint32_t>(i % STAGES);
+                const uint32_t par = static_cast<uint32_t>((i / STAGES) & 1);
+                mbar_wait(full_bar + 8 * s, par, wctx, 0x13000000u, false);
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer (leader CTA only) ------------------------------
-        if (lane == 0 && leader) {
+        // Warp-uniform loop, one elected lane issues.  The 64-bit shared-memory
+        // descriptors are kept as a constant high word and a low word that only
+        // advances by the stage and K-step offsets.
+        if (leader) {
+            const uint32_t a_kstep = (p.a_mn_major ? static_cast<uint32_t>(UMMA_K) * 128u : 32u) >> 4;
+            const uint32_t b_kstep = (p.b_mn_major ? static_cast<uint32_t>(UMMA_K) * 128u : 32u) >> 4;
+            const uint32_t a_lo0 = ((smem_u32(smem) >> 4) & 0x3FFFu) | (((p.a_mn_major ? MN_BOX_BYTES : 16u) >> 4) << 16);
+            const uint32_t b_lo0 = (((smem_u32(smem) + A_BYTES) >> 4) & 0x3FFFu) | (((p.b_mn_major ? MN_BOX_BYTES : 16u) >> 4) << 16);
+            // high word: stride offset 1024 B (bits 32..45), version 1 (bits 46..47), 128-byte swizzle (bits 61..63)
+            const uint64_t desc_hi = (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+            const uint32_t idesc = p.idesc;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             bool issued_any = false;
@@ -696,37 +847,51 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int tile = first_tile; ok && tile < p.num_tiles; tile += tile_step, ++local) {
                 const uint32_t buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
-                if (!mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u)) { ok = false; break; }
+                bool w = mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u);
+                w = __all_sync(0xFFFFFFFFu, w);
+                if (!w) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait(full_bar + 8 * stage, phase, wctx, 0x22000000u)) { ok = false; break; }
+                    w = mbar_wait(full_bar + 8 * stage, phase, wctx, 0x22000000u);
+                    w = __all_sync(0xFFFFFFFFu, w);
+                    if (!w) { ok = false; break; }
                     tcgen05_fence_after();
-                    const uint32_t a_base = smem_u32(smem + stage * STAGE_BYTES);
-                    const uint32_t b_base = a_base + A_BYTES;
+                    const uint32_t soff = stage * (STAGE_BYTES >> 4);
+                    if (elect_one_sync()) {
+                        if (p.debug_mode == 1) {
+                            mbar_arrive(empty_bar + 8 * stage);
+                            if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(empty_bar + 8 * stage, 1u));
+                        } else {
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        const uint64_t a_desc = p.a_mn_major
-                            ? make_smem_desc(a_base + kk * UMMA_K * 128, MN_BOX_BYTES, 1024)
-                            : make_smem_desc(a_base + kk * 32, 16, 1024);
-                        const uint64_t b_desc = p.b_mn_major
-                            ? make_smem_desc(b_base + kk * UMMA_K * 128, MN_BOX_BYTES, 1024)
-                            : make_smem_desc(b_base + kk * 32, 16, 1024);
-                        umma_ss<KIND, CG>(d_tmem, a_desc, b_desc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+                            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                                const uint64_t a_desc = desc_hi | (a_lo0 + soff + kk * a_kstep);
+                                const uint64_t b_desc = desc_hi | (b_lo0 + soff + kk * b_kstep);
+                                umma_ss<KIND, CG>(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            }
+                            // free the stage, in both CTAs of a pair, when these MMAs retire
+                            umma_commit<CG>(empty_bar + 8 * stage);
+                            if constexpr (CG == 2) umma_commit<CG>(map_to_cta(empty_bar + 8 * stage, 1u));
+                        }
                     }
+                    __syncwarp();
                     issued_any = true;
-                    // free the stage, in both CTAs of a pair, when these MMAs retire
-                    umma_commit<CG>(empty_bar + 8 * stage);
-                    if constexpr (CG == 2) umma_commit<CG>(map_to_cta(empty_bar + 8 * stage, 1u));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) {                                   // accumulator complete, in both CTAs of a pair
-                    umma_commit<CG>(acc_full_bar + 8 * buf);
-                    if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
+                if (ok && elect_one_sync()) {
+                    if (p.debug_mode == 1) {
+                        mbar_arrive(acc_full_bar + 8 * buf);
+                        if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(acc_full_bar + 8 * buf, 1u));
+                    } else {                                // accumulator complete, in both CTAs of a pair
+                        umma_commit<CG>(acc_full_bar + 8 * buf);
+                        if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
+                    }
                 }
+                __syncwarp();
             }
-            if (*abort_flag != 0u && issued_any) {
-                umma_commit<CG>(drain_bar);
+            if (*abort_flag != 0u && issued_any && p.debug_mode != 1) {
+                if (elect_one_sync()) umma_commit<CG>(drain_bar);
+                __syncwarp();
                 mbar_wait(drain_bar, 0u, wctx, 0x23000000u, false);
             }
         }
@@ -734,7 +899,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // ------------------------------ epilogue ------------------------------
         uint32_t acc_empty_addr = acc_empty_bar;                       // the leader's barrier collects every arrival
         if constexpr (CG == 2) acc_empty_addr = map_to_cta(acc_empty_bar, 0u);
-        const uint32_t stage_addr = smem_u32(epi_smem) + (warp - 2) * EPI_STAGE_BYTES;
+        const uint32_t stage_addr = smem_u32(epi_smem) + ((warp - 2) >> 2) * (4 * EPI_STAGE_BYTES);   // 16 KB per column half
         switch (p.activation) {
             case SM120_ACTIVATION_NONE:
                 epilogue_role<KIND, BN, STAGES, CG, ACTC_NONE>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
@@ -762,6 +927,10 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();
         tcgen05_fence_after();
         tmem_dealloc<CG>(tmem_base, TMEM_COLS);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        g_sm120_probe[0] = static_cast<unsigned long long>(clock64() - probe_c0);
+        g_sm120_probe[1] = global_timer_ns() - probe_t0;
     }
 }
 
@@ -838,6 +1007,8 @@ bool tc_supported(const GemmProblem& p, const char** why) {
 
 static std::atomic<int> g_debug_skip_kblock{-1};
 void tc_set_debug_skip_kblock(int kb) { g_debug_skip_kblock.store(kb); }
+static std::atomic<int> g_debug_mode{0};
+void tc_set_debug_mode(int m) { g_debug_mode.store(m); }
 static std::atomic<int> g_force_cta_group{0};     // 0 = choose, 1 / 2 = force (tests and tuning)
 void tc_set_force_cta_group(int cg) { g_force_cta_group.store(cg); }
 
@@ -935,6 +1106,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.scale_a_dev = p.scale_a_dev; tp.scale_b_dev = p.scale_b_dev;
     tp.activation = p.activation;
     tp.debug_skip_kblock = g_debug_skip_kblock.load();
+    tp.debug_mode = g_debug_mode.load();
     tp.wait_limit_ns = wait_limit_ns;
 
     // Instruction descriptor (tcgen05.mma kind::f16 / kind::f8f6f4):
@@ -957,10 +1129,14 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     if (!b_mn) ok = encode_3d(&tb, p.B, p.in_dtype, p.K, p.N, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.N * p.ldb, bk, bn_cta, CU_TENSOR_MAP_SWIZZLE_128B);
     else       ok = encode_3d(&tb, p.B, p.in_dtype, p.N, p.K, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.K * p.ldb, epb, bk, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
+    // One TMA store writes 128 rows x epi_cols columns: as many columns as fit a
+    // 128-byte staging row, but not more than one epilogue warp owns (bn / 2).
+    tp.epi_cols = (bn / 2 >= 64 && out_es == 2) ? 64 : 32;
+    tp.epi_row_bytes = tp.epi_cols * out_es;
     if (tp.use_tma_store) {
-        // 32 x 32 output blocks: rows of 128 B (fp32, 128-byte swizzle) or 64 B (16-bit, 64-byte swizzle)
-        ok = encode_3d(&tc, p.C, p.out_dtype, p.N, p.M, p.batch, p.ldc, p.batch > 1 ? p.stride_c : p.M * p.ldc, 32, 32,
-                       out_es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+        ok = encode_3d(&tc, p.C, p.out_dtype, p.N, p.M, p.batch, p.ldc, p.batch > 1 ? p.stride_c : p.M * p.ldc,
+                       static_cast<uint32_t>(tp.epi_cols), BM,
+                       tp.epi_row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
         if (!ok) tp.use_tma_store = 0;
     }
     if (!tp.use_tma_store) tc = ta;      // never dereferenced by the kernel
@@ -984,6 +1160,12 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         SM120_TC_CASE(KIND_F8, 64, 8, 1, "tc_e4m3_128x64x128_s8");
     }
 #undef SM120_TC_CASE
+}
+
+cudaError_t tc_read_probe(unsigned long long* cycles_ns) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    return cudaMemcpyFromSymbol(cycles_ns, g_sm120_probe, 2 * sizeof(unsigned long long));
 }
 
 cudaError_t tc_read_status(unsigned int* status, int clear) {

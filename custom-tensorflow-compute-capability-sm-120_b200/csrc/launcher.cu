@@ -19,6 +19,8 @@ namespace sm120 {
 
 void tc_set_debug_skip_kblock(int kb);
 void tc_set_force_cta_group(int cg);
+void tc_set_debug_mode(int m);
+cudaError_t tc_read_probe(unsigned long long* cycles_ns);
 
 namespace {
 
@@ -271,5 +273,14 @@ void sm120_debug_skip_kblock(int kb) { tc_set_debug_skip_kblock(kb); }
 // single-CTA or the CTA-pair flavour of the tensor-core kernel, 0 restores the
 // launcher's own choice.
 void sm120_debug_force_cta_group(int cg) { tc_set_force_cta_group(cg); }
+
+// Timing-experiment hook, not declared in the public header: 1 = the MMA role
+// issues no tcgen05.mma, 2 = the producer issues no TMA loads (results are
+// garbage in both), 0 = normal.
+void sm120_debug_mode(int m) { tc_set_debug_mode(m); }
+
+// Tuning hook, not declared in the public header: SM cycles and nanoseconds that
+// CTA 0 of the last tensor-core launch on the current device was alive.
+int sm120_debug_read_probe(unsigned long long* cycles_ns) { return static_cast<int>(tc_read_probe(cycles_ns)); }
 
 }  // extern "C"
