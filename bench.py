@@ -381,6 +381,13 @@ def run_gpu(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_secs = float(t.item())
 
+    # SM clock seen from inside the last launch (%clock64 over %globaltimer of CTA 0)
+    probe = (__import__("ctypes").c_ulonglong * 2)()
+    lib = binding.load_library()
+    lib.sm120_debug_read_probe.argtypes = [__import__("ctypes").c_void_p]
+    lib.sm120_debug_read_probe(probe)
+    kernel_mhz = 1e3 * probe[0] / probe[1] if probe[1] else None
+
     status = __import__("ctypes").c_uint(0)
     binding.load_library().sm120_get_kernel_status(local_rank, __import__("ctypes").byref(status), 0)
 
@@ -393,10 +400,15 @@ def run_gpu(args, rank, world, local_rank):
         if store_bound:
             roof = {"bound": "hbm", "achieved": spec["bytes"] / per_launch / 1e9, "peak": hbm, "unit": "GB/s"}
         else:
-            roof = {"bound": "tensor", "achieved": tf_gpu, "peak": peak, "unit": "TFLOP/s"}
+            # the e4m3 rate of the tensor pipe is twice the bf16 rate: scale the measured bf16 peak for the FP8 workload
+            tpeak = peak * (2.0 if spec["dtype"] == "f8e4m3" else 1.0)
+            roof = {"bound": "tensor", "achieved": tf_gpu, "peak": tpeak, "unit": "TFLOP/s"}
         roof["frac"] = roof["achieved"] / roof["peak"]
         roof["traffic"] = NCU_TRAFFIC_BYTES.get(spec["name"])
-        roof["peak_source"] = f"{peak_kind}: MEASURED_PEAKS.json " + ("hbm_gbs (copy)" if store_bound else "bf16_tflops (cuBLAS bf16 8192^3 burst)")
+        roof["peak_source"] = f"{peak_kind}: MEASURED_PEAKS.json " + (
+            "hbm_gbs (copy)" if store_bound else
+            ("2 x bf16_tflops (cuBLAS bf16 8192^3 burst; e4m3 runs at twice the bf16 rate)" if spec["dtype"] == "f8e4m3"
+             else "bf16_tflops (cuBLAS bf16 8192^3 burst)"))
         roof["kernel"] = kernel
         roof["algorithmic_flops_per_launch"] = spec["flops"]
         roof["algorithmic_bytes_per_launch"] = spec["bytes"]
@@ -424,7 +436,7 @@ def run_gpu(args, rank, world, local_rank):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_secs / e2e_steps,
                     "steps": e2e_steps},
             "gpu_launches": int(launches),
-            "clocks": sampler.summary() if sampler else None,
+            "clocks": dict(sampler.summary(), sm_mhz_in_kernel=kernel_mhz) if sampler else None,
             "kernel_status": int(status.value),
         }
         if world == 1 and not args.no_side_table:

@@ -74,7 +74,9 @@ constexpr uint32_t EPI_STAGE_BYTES = 4096;   // per epilogue warp: 32 rows x 128
 struct TcParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, k_blocks, num_tiles;   // tiles are (CG*128) x BN
+    int num_work, full_work;        // work items: [0, full_work) are whole tiles, the rest are half-width tiles (two per tile)
     uint32_t idesc;
+    uint32_t idesc_half;            // instruction descriptor of a half-width tile (N = BN / 2)
     int a_mn_major, b_mn_major;
     int a_batched, b_batched;
     void* C;
@@ -360,6 +362,24 @@ __device__ __forceinline__ void decode_tile(int tile, const TcParams& p, int& bz
     tn = r / gm;
 }
 
+// Work item -> batch entry, row tile, first column and width.  The last
+// num_work - full_work items are the two column halves of the last tiles: when the
+// tile count leaves the final wave less than half full, splitting those tiles
+// shortens the tail from one tile time to half a tile time.
+__device__ __forceinline__ void decode_work(int w, const TcParams& p, int bn, int& bz, int& tm, int& n0, int& width) {
+    int tile = w, sel = 0;
+    width = bn;
+    if (w >= p.full_work) {
+        const int h = w - p.full_work;
+        tile = p.full_work + (h >> 1);
+        sel = h & 1;
+        width = bn >> 1;
+    }
+    int tn;
+    decode_tile(tile, p, bz, tm, tn);
+    n0 = tn * bn + sel * width;
+}
+
 // ---------------------------------------------------------------------------
 // Epilogue helpers.  Everything is fully unrolled over compile-time indices so
 // that the 32 values of a row segment stay in registers.
@@ -599,23 +619,23 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const CUtensorM
                                               int tile_step) {
     const int lane_group = warp & 3;          // TMEM lanes [32*lane_group, +32) belong to this warp
     const int half = (warp - 2) >> 2;         // which half of the tile's columns
-    constexpr int COLS_PER_WARP = BN / 2;
-    constexpr int CHUNKS = COLS_PER_WARP / 32;
+    constexpr int CHUNKS = BN / 64;           // 32-column chunks per warp in a whole tile
     float alpha = p.alpha;
     if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
     if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
     const bool has_bias = p.bias != nullptr;
     int local = 0;
-    for (int tile = first_tile; tile < p.num_tiles; tile += tile_step, ++local) {
-        int bz, tm, tn;
-        decode_tile(tile, p, bz, tm, tn);
+    for (int tile = first_tile; tile < p.num_work; tile += tile_step, ++local) {
+        int bz, tm, n0, width;
+        decode_work(tile, p, BN, bz, tm, n0, width);
         const uint32_t buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
         const int row = row0 + lane;
-        const int colbase = tn * BN + half * COLS_PER_WARP;
+        const int cols_per_warp = width >> 1;
+        const int colbase = n0 + half * cols_per_warp;
         // chunks of 32 columns this warp owns that start inside the matrix (warp-uniform)
-        const int nvalid = max(0, min(CHUNKS, (p.N - colbase + 31) / 32));
+        const int nvalid = max(0, min(cols_per_warp >> 5, (p.N - colbase + 31) / 32));
         BiasRaw braw;
         // the first chunk's bias is fetched before the wait for the accumulator
         if (has_bias && p.bias_vec_ok && nvalid > 0 && colbase + 32 <= p.N) bias_prefetch32(p, colbase, braw);
@@ -626,7 +646,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const CUtensorM
         ok = half_barrier_all(1 + half, ok);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * COLS_PER_WARP;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * cols_per_warp;
         const int cta_row0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
         const int spg = p.epi_cols >> 5;                    // 32-column chunks per TMA store: 1 or 2
         const int chunk16_per_sub = (p.out_dtype == SM120_DTYPE_FLOAT32) ? 8 : 4;
@@ -772,13 +792,15 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         bool ok = true;
         bool first = true;
         const uint32_t full_for_tma = (CG == 2) ? map_to_cta(full_bar, 0u) : full_bar;   // the pair leader's barriers
-        for (int tile = first_tile; ok && tile < p.num_tiles; tile += tile_step) {
-            int bz, tm, tn;
-            decode_tile(tile, p, bz, tm, tn);
+        for (int tile = first_tile; ok && tile < p.num_work; tile += tile_step) {
+            int bz, tm, nt, width;
+            decode_work(tile, p, BN, bz, tm, nt, width);
             const int za = p.a_batched ? bz : 0;
             const int zb = p.b_batched ? bz : 0;
             const int m0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
-            const int n0 = tn * BN + static_cast<int>(cta_rank) * BN_CTA;
+            // this CTA's share of the tile's columns (a half-width tile still loads a full
+            // box of BN_CTA rows of B; the MMA reads only the first width / CG of them)
+            const int n0 = nt + static_cast<int>(cta_rank) * (width / CG);
             for (int kb = 0; kb < p.k_blocks; ++kb) {
                 if (first && kb == p.debug_skip_kblock) { ok = false; break; }
                 bool w = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u);
@@ -839,12 +861,12 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t b_lo0 = (((smem_u32(smem) + A_BYTES) >> 4) & 0x3FFFu) | (((p.b_mn_major ? MN_BOX_BYTES : 16u) >> 4) << 16);
             // high word: stride offset 1024 B (bits 32..45), version 1 (bits 46..47), 128-byte swizzle (bits 61..63)
             const uint64_t desc_hi = (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
-            const uint32_t idesc = p.idesc;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             bool issued_any = false;
             int local = 0;
-            for (int tile = first_tile; ok && tile < p.num_tiles; tile += tile_step, ++local) {
+            for (int tile = first_tile; ok && tile < p.num_work; tile += tile_step, ++local) {
+                const uint32_t idesc = tile < p.full_work ? p.idesc : p.idesc_half;
                 const uint32_t buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 bool w = mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u);
@@ -1009,6 +1031,8 @@ static std::atomic<int> g_debug_skip_kblock{-1};
 void tc_set_debug_skip_kblock(int kb) { g_debug_skip_kblock.store(kb); }
 static std::atomic<int> g_debug_mode{0};
 void tc_set_debug_mode(int m) { g_debug_mode.store(m); }
+static std::atomic<int> g_split_tail{1};           // 0 switches the half-width tail tiles off (tuning)
+void tc_set_split_tail(int on) { g_split_tail.store(on); }
 static std::atomic<int> g_force_cta_group{0};     // 0 = choose, 1 / 2 = force (tests and tuning)
 void tc_set_force_cta_group(int cg) { g_force_cta_group.store(cg); }
 
@@ -1049,6 +1073,14 @@ static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, 
         }
         const int want = tp.num_tiles < clusters ? tp.num_tiles : clusters;
         cfg.gridDim = dim3(static_cast<unsigned>(2 * want), 1, 1);
+        // A final wave that is less than half full is run as half-width tiles.
+        TcParams t = tp;
+        const int rest = tp.num_tiles % clusters;
+        if (tp.num_tiles > clusters && rest > 0 && 2 * rest <= clusters && g_split_tail.load() != 0) {
+            t.full_work = tp.num_tiles - rest;
+            t.num_work = t.full_work + 2 * rest;
+        }
+        return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, t);
     } else {
         const int want = tp.num_tiles < sm_count ? tp.num_tiles : sm_count;
         cfg.gridDim = dim3(static_cast<unsigned>(want), 1, 1);
@@ -1092,6 +1124,8 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
     tp.k_blocks = static_cast<int>((p.K + bk - 1) / bk);
     tp.num_tiles = static_cast<int>(tiles_for(BM * cg, bn));
+    tp.num_work = tp.num_tiles;
+    tp.full_work = tp.num_tiles;
     tp.a_mn_major = a_mn ? 1 : 0;
     tp.b_mn_major = b_mn ? 1 : 0;
     tp.a_batched = (p.batch > 1 && p.stride_a != 0) ? 1 : 0;
@@ -1117,6 +1151,8 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tp.a_mn_major) << 15) |
                (static_cast<uint32_t>(tp.b_mn_major) << 16) | (static_cast<uint32_t>(bn >> 3) << 17) |
                (static_cast<uint32_t>((BM * cg) >> 4) << 24);
+
+    tp.idesc_half = (tp.idesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>((bn / 2) >> 3) << 17);
 
     CUtensorMap ta, tb, tc;
     const int64_t nb_a = tp.a_batched ? p.batch : 1;

@@ -20,6 +20,7 @@ namespace sm120 {
 void tc_set_debug_skip_kblock(int kb);
 void tc_set_force_cta_group(int cg);
 void tc_set_debug_mode(int m);
+void tc_set_split_tail(int on);
 cudaError_t tc_read_probe(unsigned long long* cycles_ns);
 
 namespace {
@@ -278,6 +279,10 @@ void sm120_debug_force_cta_group(int cg) { tc_set_force_cta_group(cg); }
 // issues no tcgen05.mma, 2 = the producer issues no TMA loads (results are
 // garbage in both), 0 = normal.
 void sm120_debug_mode(int m) { tc_set_debug_mode(m); }
+
+// Tuning hook, not declared in the public header: 0 switches off the half-width
+// tiles that the CTA-pair kernel uses for a short final wave, 1 (default) on.
+void sm120_debug_split_tail(int on) { tc_set_split_tail(on); }
 
 // Tuning hook, not declared in the public header: SM cycles and nanoseconds that
 // CTA 0 of the last tensor-core launch on the current device was alive.
