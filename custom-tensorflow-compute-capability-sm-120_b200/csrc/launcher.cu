@@ -17,6 +17,8 @@
 
 namespace sm120 {
 
+long long quant_spans(long long n);
+cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, long long n, float* partial, cudaStream_t stream);
 void tc_set_debug_skip_kblock(int kb);
 void tc_set_force_cta_group(int cg);
 void tc_set_debug_mode(int m);
@@ -233,6 +235,33 @@ cudaError_t sm120_launch_matmul_grad_b(const void* A, const void* grad_c, void* 
     d.in_dtype = dtype; d.out_dtype = dtype;
     d.stream = stream;
     return sm120_launch_matmul_ex(&d);
+}
+
+size_t sm120_quantize_fp8_scratch_bytes(int64_t n) {
+    return n > 0 ? static_cast<size_t>(quant_spans(n)) * sizeof(float) : 0;
+}
+
+cudaError_t sm120_launch_quantize_fp8(const void* x, SM120DataType x_dtype, int64_t n, void* q, float* scale_out,
+                                      void* scratch, size_t scratch_bytes, cudaStream_t stream) {
+    if (n < 0 || scale_out == nullptr) return cudaErrorInvalidValue;
+    if (x_dtype != SM120_DTYPE_FLOAT32 && x_dtype != SM120_DTYPE_FLOAT16 && x_dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (n > 0 && (x == nullptr || q == nullptr || scratch == nullptr)) return cudaErrorInvalidValue;
+    if (scratch_bytes < sm120_quantize_fp8_scratch_bytes(n)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(scratch) & 3u) != 0 || (reinterpret_cast<uintptr_t>(scale_out) & 3u) != 0)
+        return cudaErrorInvalidValue;
+    if (n == 0) return cudaSuccess;
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    e = quant_launch(x, x_dtype, q, scale_out, n, static_cast<float*>(scratch), stream);
+    if (e == cudaSuccess) {
+        g_launch_count.fetch_add(3, std::memory_order_relaxed);
+        t_last_kernel = "quant_e4m3_amax_scale_cast";
+    }
+    return e;
 }
 
 bool sm120_is_supported(int device_id) {

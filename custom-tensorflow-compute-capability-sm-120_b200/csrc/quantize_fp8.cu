@@ -1,0 +1,141 @@
+// Per-tensor FP8 (e4m3) quantisation for the FP8 matmul path:
+//     scale = 448 / max|x|          (1 when the tensor is all zeros)
+//     q[i]  = saturate_e4m3(x[i] * scale)       round-to-nearest-even, finite
+// The reference declares the type and the conversion
+// (src/cuda_kernels/sm120_datatype_support.h:71-82,168-171;
+// python/sm120_datatype_manager.py:88-98) but has no kernel that produces FP8
+// operands; the matmul consumes `scale` through SM120GemmDesc::scale_a_dev /
+// scale_b_dev, so no host round trip is needed between the two.
+//
+// Three launches on the caller's stream, all HBM-bound (x is read twice, q
+// written once):
+//   1. amax_partial : one block per span of 65536 elements -> partial[b] = max|x| of the span
+//   2. amax_final   : one block reduces the partials -> *scale_out
+//   3. scale_cast   : q = sat(x * *scale_out), 16-byte loads where alignment allows
+// `partial` is scratch memory: one float per span.  Every slot that a call reads
+// is written by that call's first launch, so nothing has to be zero beforehand.
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+#include "gemm_common.h"
+
+namespace sm120 {
+
+constexpr int64_t QUANT_SPAN = 65536;       // elements per partial maximum
+constexpr int QUANT_THREADS = 256;
+
+template <typename T> __device__ __forceinline__ float q_to_float(T v);
+template <> __device__ __forceinline__ float q_to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float q_to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float q_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < (blockDim.x >> 5) ? red[lane] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+        if (lane == 0) red[0] = v;
+    }
+    __syncthreads();
+    return red[0];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QUANT_THREADS)
+sm120_quant_amax_partial_kernel(const T* __restrict__ x, long long n, float* __restrict__ partial) {
+    __shared__ float red[32];
+    constexpr int VEC = 16 / sizeof(T);
+    const long long begin = static_cast<long long>(blockIdx.x) * QUANT_SPAN;
+    const long long end = min(n, begin + QUANT_SPAN);
+    float m = 0.0f;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;     // spans start at multiples of 65536 elements
+    if (vec_ok) {
+        const long long nvec = (end - begin) / VEC;
+        const uint4* xv = reinterpret_cast<const uint4*>(x + begin);
+        for (long long i = threadIdx.x; i < nvec; i += QUANT_THREADS) {
+            const uint4 w = __ldg(xv + i);
+            const T* e = reinterpret_cast<const T*>(&w);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) m = fmaxf(m, fabsf(q_to_float<T>(e[k])));
+        }
+        for (long long i = begin + nvec * VEC + threadIdx.x; i < end; i += QUANT_THREADS) m = fmaxf(m, fabsf(q_to_float<T>(x[i])));
+    } else {
+        for (long long i = begin + threadIdx.x; i < end; i += QUANT_THREADS) m = fmaxf(m, fabsf(q_to_float<T>(x[i])));
+    }
+    m = block_max(m, red);
+    if (threadIdx.x == 0) partial[blockIdx.x] = m;
+}
+
+__global__ void __launch_bounds__(1024)
+sm120_quant_amax_final_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ scale_out) {
+    __shared__ float red[32];
+    float m = 0.0f;
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) m = fmaxf(m, partial[i]);
+    m = block_max(m, red);
+    if (threadIdx.x == 0) *scale_out = m > 0.0f ? 448.0f / m : 1.0f;
+}
+
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QUANT_THREADS)
+sm120_quant_scale_cast_kernel(const T* __restrict__ x, long long n, const float* __restrict__ scale, uint8_t* __restrict__ q) {
+    constexpr int VEC = 16 / sizeof(T);          // elements per 16-byte load
+    const float s = __ldg(scale);
+    const long long begin = static_cast<long long>(blockIdx.x) * QUANT_SPAN;
+    const long long end = min(n, begin + QUANT_SPAN);
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q) & 15u) == 0;
+    if (vec_ok) {
+        const long long nvec = (end - begin) / VEC;
+        const uint4* xv = reinterpret_cast<const uint4*>(x + begin);
+        for (long long i = threadIdx.x; i < nvec; i += QUANT_THREADS) {
+            const uint4 w = __ldg(xv + i);
+            const T* e = reinterpret_cast<const T*>(&w);
+            uint8_t out[VEC];
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) out[k] = to_e4m3(q_to_float<T>(e[k]) * s);
+            uint8_t* dst = q + begin + i * VEC;
+            if constexpr (VEC == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(out);
+            else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(out);
+        }
+        for (long long i = begin + nvec * VEC + threadIdx.x; i < end; i += QUANT_THREADS) q[i] = to_e4m3(q_to_float<T>(x[i]) * s);
+    } else {
+        for (long long i = begin + threadIdx.x; i < end; i += QUANT_THREADS) q[i] = to_e4m3(q_to_float<T>(x[i]) * s);
+    }
+}
+
+long long quant_spans(long long n) { return (n + QUANT_SPAN - 1) / QUANT_SPAN; }
+
+template <typename T>
+static cudaError_t quant_typed(const void* x, long long n, uint8_t* q, float* scale_out, float* partial, cudaStream_t stream) {
+    const long long spans = quant_spans(n);
+    const T* xt = static_cast<const T*>(x);
+    sm120_quant_amax_partial_kernel<T><<<static_cast<unsigned>(spans), QUANT_THREADS, 0, stream>>>(xt, n, partial);
+    sm120_quant_amax_final_kernel<<<1, 1024, 0, stream>>>(partial, static_cast<int>(spans), scale_out);
+    sm120_quant_scale_cast_kernel<T><<<static_cast<unsigned>(spans), QUANT_THREADS, 0, stream>>>(xt, n, scale_out, q);
+    return cudaGetLastError();
+}
+
+// Enqueue the three kernels.  `partial` must hold quant_spans(n) floats.
+cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, long long n, float* partial, cudaStream_t stream) {
+    if (quant_spans(n) > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+    switch (x_dtype) {
+        case SM120_DTYPE_FLOAT32:  return quant_typed<float>(x, n, static_cast<uint8_t*>(q), scale_out, partial, stream);
+        case SM120_DTYPE_FLOAT16:  return quant_typed<__half>(x, n, static_cast<uint8_t*>(q), scale_out, partial, stream);
+        case SM120_DTYPE_BFLOAT16: return quant_typed<__nv_bfloat16>(x, n, static_cast<uint8_t*>(q), scale_out, partial, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace sm120

@@ -407,13 +407,33 @@ def matmul_grad(grad_c, a, b):
 
 
 def quantize_fp8(x: torch.Tensor):
-    """Per-tensor FP8 quantisation used with FP8 matmuls: returns
-    (x * s rounded to e4m3 with saturation, s) with s = 448 / amax(x)
-    (type and conversion: src/cuda_kernels/sm120_datatype_support.h:71-82,168-171)."""
-    amax = x.abs().amax().float().clamp_min(1e-30)
-    s = 448.0 / amax
-    q = (x.float() * s).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn)
-    return q, s.reshape(1)
+    """Per-tensor FP8 quantisation for FP8 matmuls, on the device: returns
+    (q, scale) with scale = 448 / amax(x) as a one-element float32 CUDA tensor and
+    q = x * scale rounded to e4m3 with saturation
+    (type and conversion: src/cuda_kernels/sm120_datatype_support.h:71-82,168-171).
+    `scale` can be passed to ``fused_matmul(scale_a=...)`` as it is: nothing is
+    copied to the host."""
+    _require_available()
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise TypeError("quantize_fp8 needs a CUDA tensor")
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"dtype {x.dtype} cannot be quantised (float32, float16, bfloat16)")
+    x = x.contiguous()
+    lib = _b.load_library()
+    n = x.numel()
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    nbytes = int(lib.sm120_quantize_fp8_scratch_bytes(n))
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)     # the caller's allocator, not the library's
+    with torch.cuda.device(x.device):
+        rc = lib.sm120_launch_quantize_fp8(x.data_ptr(), _TORCH_TO_SM120[x.dtype], n, q.data_ptr(), scale.data_ptr(),
+                                           scratch.data_ptr(), scratch.numel(), torch.cuda.current_stream(x.device).cuda_stream)
+    if rc == _b.CUDA_ERROR_INVALID_VALUE:
+        raise InvalidArgumentError("quantize_fp8 rejected its arguments (cudaErrorInvalidValue)")
+    if rc != _b.CUDA_SUCCESS:
+        raise InternalError(f"quantize_fp8 failed: {_b.error_string(rc)}")
+    scratch.record_stream(torch.cuda.current_stream(x.device))
+    return q, scale
 
 
 class SM120Profiler:

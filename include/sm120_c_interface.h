@@ -25,6 +25,7 @@
 #define SM120_C_INTERFACE_H
 
 #include <stdbool.h>
+#include <stddef.h>
 #include <stdint.h>
 #include <cuda_runtime_api.h>
 
@@ -172,6 +173,28 @@ cudaError_t sm120_launch_matmul_grad_b(
     const void* A, const void* grad_c, void* grad_b,
     int M, int N, int K, float alpha,
     SM120DataType dtype, cudaStream_t stream);
+
+/*
+ * Per-tensor FP8 quantisation, the producer of FP8 matmul operands:
+ *   *scale_out = 448 / max|x|   (1 for an all-zero tensor)
+ *   q[i] = saturate_e4m3(x[i] * *scale_out)      (round-to-nearest-even, finite)
+ * x has n elements of x_dtype (FLOAT32, FLOAT16 or BFLOAT16); q receives n bytes;
+ * scale_out is one float in device memory and can be passed straight to
+ * SM120GemmDesc::scale_a_dev / scale_b_dev.  `scratch` is device memory of at
+ * least sm120_quantize_fp8_scratch_bytes(n) bytes (4 bytes per 65536 elements),
+ * 4-byte aligned, owned by the caller; its contents before the call do not
+ * matter and it may be reused by the next call on the same stream.
+ * The reference declares the FP8 type and its saturating conversion
+ * (src/cuda_kernels/sm120_datatype_support.h:71-82,168-171;
+ * python/sm120_datatype_manager.py:88-98) but has no launcher that produces
+ * FP8 tensors; this is that launcher.
+ */
+size_t sm120_quantize_fp8_scratch_bytes(int64_t n);
+cudaError_t sm120_launch_quantize_fp8(
+    const void* x, SM120DataType x_dtype, int64_t n,
+    void* q, float* scale_out,
+    void* scratch, size_t scratch_bytes,
+    cudaStream_t stream);
 
 /*
  * Replaces sm120_is_supported (src/cuda_kernels/sm120_c_interface.h:153, body
