@@ -25,6 +25,7 @@ PATH_AUTO, PATH_TENSOR_CORE, PATH_SIMT = 0, 1, 2
 
 CUDA_SUCCESS = 0
 CUDA_ERROR_INVALID_VALUE = 1
+QUANTIZE_FP8_STATIC_MAX_ELEMENTS = 268435456      # SM120_QUANTIZE_FP8_STATIC_MAX_ELEMENTS
 
 
 class SM120GemmDesc(Structure):
@@ -65,6 +66,7 @@ EXPORTS = {
     "sm120_launch_matmul_grad_b": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "sm120_quantize_fp8_scratch_bytes": (ctypes.c_size_t, [c_int64]),
     "sm120_launch_quantize_fp8": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
+    "sm120_launch_quantize_fp8_static": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "sm120_is_supported": (c_bool, [c_int]),
     "sm120_get_error_string": (c_char_p, [c_int]),
     "sm120_get_kernel_status": (c_int, [c_int, POINTER(c_uint), c_int]),

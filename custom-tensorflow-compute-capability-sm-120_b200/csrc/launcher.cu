@@ -19,6 +19,7 @@ namespace sm120 {
 
 long long quant_spans(long long n);
 cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, long long n, float* partial, cudaStream_t stream);
+cudaError_t quant_launch_static(const void* x, int x_dtype, void* q, float* scale_out, long long n, int device, cudaStream_t stream);
 void tc_set_debug_skip_kblock(int kb);
 void tc_set_force_cta_group(int cg);
 void tc_set_debug_mode(int m);
@@ -260,6 +261,31 @@ cudaError_t sm120_launch_quantize_fp8(const void* x, SM120DataType x_dtype, int6
     if (e == cudaSuccess) {
         g_launch_count.fetch_add(3, std::memory_order_relaxed);
         t_last_kernel = "quant_e4m3_amax_scale_cast";
+    }
+    return e;
+}
+
+// Quantisation without caller scratch and without any allocation: the partial
+// maxima go to a fixed array inside the library (see the header for who needs
+// this, the size limit, the first-call set-up and the sharing rule).
+cudaError_t sm120_launch_quantize_fp8_static(const void* x, SM120DataType x_dtype, int64_t n, void* q, float* scale_out,
+                                             cudaStream_t stream) {
+    if (n < 0 || scale_out == nullptr) return cudaErrorInvalidValue;
+    if (n > SM120_QUANTIZE_FP8_STATIC_MAX_ELEMENTS) return cudaErrorInvalidValue;     // beyond the built-in scratch
+    if (x_dtype != SM120_DTYPE_FLOAT32 && x_dtype != SM120_DTYPE_FLOAT16 && x_dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (n > 0 && (x == nullptr || q == nullptr)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(scale_out) & 3u) != 0) return cudaErrorInvalidValue;
+    if (n == 0) return cudaSuccess;
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    e = quant_launch_static(x, x_dtype, q, scale_out, n, device, stream);
+    if (e == cudaSuccess) {
+        g_launch_count.fetch_add(3, std::memory_order_relaxed);
+        t_last_kernel = "quant_e4m3_amax_scale_cast_static";
     }
     return e;
 }

@@ -20,6 +20,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+#include <atomic>
 
 #include "gemm_common.h"
 
@@ -136,6 +137,33 @@ cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, 
         case SM120_DTYPE_BFLOAT16: return quant_typed<__nv_bfloat16>(x, n, static_cast<uint8_t*>(q), scale_out, partial, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+// ---------------------------------------------------------------------------
+// Variant that allocates nothing: the partial maxima live in a fixed array in
+// this library's own device image.
+// ---------------------------------------------------------------------------
+// Every GPU that loads the library holds these 16 KB until the process exits.
+// One float per 65536-element span: 4096 spans cover 268 435 456 elements.
+static __device__ __align__(256) float g_quant_static_partial[SM120_QUANTIZE_FP8_STATIC_MAX_ELEMENTS / QUANT_SPAN];
+
+// In host code the array's name is only a handle: the device address has to be
+// asked for, once per device and with that device current.
+static std::atomic<float*> g_quant_static_addr[64];
+
+cudaError_t quant_launch_static(const void* x, int x_dtype, void* q, float* scale_out, long long n, int device,
+                                cudaStream_t stream) {
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    float* partial = g_quant_static_addr[device].load(std::memory_order_acquire);
+    if (partial == nullptr) {
+        void* addr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&addr, g_quant_static_partial);
+        if (e != cudaSuccess) return e;
+        if (addr == nullptr) return cudaErrorInvalidSymbol;
+        partial = static_cast<float*>(addr);
+        g_quant_static_addr[device].store(partial, std::memory_order_release);
+    }
+    return quant_launch(x, x_dtype, q, scale_out, n, partial, stream);
 }
 
 }  // namespace sm120

@@ -436,6 +436,42 @@ def quantize_fp8(x: torch.Tensor):
     return q, scale
 
 
+def quantize_fp8_into(x: torch.Tensor, q: torch.Tensor, scale: torch.Tensor) -> None:
+    """FP8 quantisation of `x` into buffers the caller already owns, with no
+    allocation anywhere on the way (``sm120_launch_quantize_fp8_static``).
+
+    For code that must not allocate device memory while it runs -- a callback
+    that may use only the tensors it was given, a serving loop whose memory was
+    fixed at start-up.  `q` (float8_e4m3fn, same number of elements as `x`) and
+    `scale` (one float32) are written; the intermediate partial maxima live in
+    a 16 KB array built into the library, which limits `x` to 268 435 456
+    elements and means that two calls running at the same time on one GPU would
+    disturb each other: keep them on one stream or order them.  The first call
+    on a device also looks up that array's address, so make it before any
+    stream capture starts."""
+    _require_available()
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and x.is_contiguous()):
+        raise TypeError("x must be a contiguous CUDA tensor")
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"dtype {x.dtype} cannot be quantised (float32, float16, bfloat16)")
+    if not (q.is_cuda and q.is_contiguous() and q.dtype == torch.float8_e4m3fn and q.numel() == x.numel() and q.device == x.device):
+        raise ValueError("q must be a contiguous float8_e4m3fn CUDA tensor with as many elements as x")
+    if not (scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == 1 and scale.device == x.device):
+        raise ValueError("scale must be a one-element float32 CUDA tensor on x's device")
+    if x.numel() > _b.QUANTIZE_FP8_STATIC_MAX_ELEMENTS:
+        raise InvalidArgumentError(
+            f"x has {x.numel()} elements; the allocation-free quantiser takes at most "
+            f"{_b.QUANTIZE_FP8_STATIC_MAX_ELEMENTS} (use quantize_fp8 for larger tensors)")
+    with torch.cuda.device(x.device):
+        rc = _b.load_library().sm120_launch_quantize_fp8_static(
+            x.data_ptr(), _TORCH_TO_SM120[x.dtype], x.numel(), q.data_ptr(), scale.data_ptr(),
+            torch.cuda.current_stream(x.device).cuda_stream)
+    if rc == _b.CUDA_ERROR_INVALID_VALUE:
+        raise InvalidArgumentError("quantize_fp8_into rejected its arguments (cudaErrorInvalidValue)")
+    if rc != _b.CUDA_SUCCESS:
+        raise InternalError(f"quantize_fp8_into failed: {_b.error_string(rc)}")
+
+
 class SM120Profiler:
     """Same interface as python/sm120_ops.py:415-445; times with a device
     synchronisation on both sides instead of ``tf.timestamp``."""
@@ -545,6 +581,7 @@ __all__ = [
     "fused_matmul",
     "matmul_grad",
     "quantize_fp8",
+    "quantize_fp8_into",
     "SM120Profiler",
     "benchmark_operation",
     "optimized_dense",

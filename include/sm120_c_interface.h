@@ -197,6 +197,41 @@ cudaError_t sm120_launch_quantize_fp8(
     cudaStream_t stream);
 
 /*
+ * The same quantisation for callers that cannot hand over scratch memory.
+ * It has no counterpart in the reference.
+ *
+ * Who needs it: code that runs where asking the device for memory is off the
+ * table -- a framework callback that may touch only the tensors the framework
+ * passed in, a serving loop that fixed its memory pool at start-up, a
+ * foreign-language binding that owns no device buffers.  Such a caller still
+ * passes its input, its output and the float that receives the scale; the
+ * partial maxima that sm120_launch_quantize_fp8 keeps in `scratch` go into a
+ * 16 KB array that is part of this library's device image instead (every GPU
+ * that loads the library carries it until the process ends).  The call itself
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ * Limit: n <= SM120_QUANTIZE_FP8_STATIC_MAX_ELEMENTS (268 435 456); a larger n
+ * is rejected with cudaErrorInvalidValue before anything is launched -- use
+ * sm120_launch_quantize_fp8 with your own scratch for bigger tensors.
+ *
+ * First call on a device: the library looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and remembers it.  Make that
+ * first call ahead of any stream capture.
+ *
+ * Sharing: every call on a device uses the same array, which keeps whatever the
+ * previous call left in it.  That is harmless -- each slot a call reads is
+ * written by that call first, nothing has to start at zero -- but two calls
+ * that overlap on the GPU (different streams, no ordering between them) would
+ * overwrite each other's partial maxima: order them, or use the scratch-taking
+ * entry point for concurrent work.
+ */
+#define SM120_QUANTIZE_FP8_STATIC_MAX_ELEMENTS 268435456ll
+cudaError_t sm120_launch_quantize_fp8_static(
+    const void* x, SM120DataType x_dtype, int64_t n,
+    void* q, float* scale_out,
+    cudaStream_t stream);
+
+/*
  * Replaces sm120_is_supported (src/cuda_kernels/sm120_c_interface.h:153, body
  * src/cuda_kernels/sm120_c_interface.cu:285-293, which accepts only compute
  * capability 12.0).  This build accepts compute capability 10.x (B200).
