@@ -39,7 +39,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "cfg2": 110551808,      # profiles/gemm_tcgen05_cfg2_fp16_4096.txt: 89.68 MB read + 20.87 MB written
+    "cfg2bf16": 110551808,  # same kernel, shape and byte counts as cfg2
+    "cfg3": 604509184,      # profiles/gemm_tcgen05_cfg3_bf16_dense_gelu.txt: 441.7 MB read + 162.8 MB written
+    "cfg4": 547042816,      # profiles/gemm_tcgen05_cfg4_bf16_batched.txt: 67.3 MB read + 479.8 MB written
+}
 
 
 def measured_peaks():
@@ -360,7 +365,7 @@ def run_gpu(args, rank, world, local_rank):
         sampler.stop()
     launches = binding.launch_count() - launches0 - args.warmup
     kernel = binding.last_kernel_name()
-    if sampler and len(sampler.samples) < 5:
+    if sampler and len(sampler.samples) < 5 and not args.lean:
         # the timed region was shorter than a few sampling periods: sample the same launches for ~0.3 s more
         sampler.start()
         t_end = time.perf_counter() + 0.3
@@ -415,8 +420,10 @@ def run_gpu(args, rank, world, local_rank):
         roof["launch_us"] = per_launch * 1e6
 
         cpu_tf, cpu_ms, cores, sample = (None, None, os.cpu_count(), "skipped (N > 1)")
-        if world == 1:
+        if world == 1 and not args.lean:
             cpu_tf, cpu_ms, cores, sample = cpu_product(spec, 3, 1)
+        elif args.lean:
+            sample = "skipped (--lean)"
 
         line = {
             "metric": METRIC, "value": world * tf_gpu, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -439,7 +446,7 @@ def run_gpu(args, rank, world, local_rank):
             "clocks": dict(sampler.summary(), sm_mhz_in_kernel=kernel_mhz) if sampler else None,
             "kernel_status": int(status.value),
         }
-        if world == 1 and not args.no_side_table:
+        if world == 1 and not args.no_side_table and not args.lean:
             del sets
             torch.cuda.empty_cache()
             line["all_configs"] = side_table(torch, ops, binding, device, peaks)
@@ -457,6 +464,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg2bf16", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--impl", default="sm120", choices=["sm120", "reference"])
     ap.add_argument("--no-side-table", action="store_true", help="skip the per-configuration table at N=1")
+    ap.add_argument("--lean", action="store_true",
+                    help="for runs under a profiler: also skip the CPU baseline and the extra launches that lengthen a "
+                         "short timed region for clock sampling")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "sm120" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
