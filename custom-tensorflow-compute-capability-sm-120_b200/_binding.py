@@ -53,6 +53,8 @@ class SM120GemmDesc(Structure):
         ("optimization_level", c_int32),
         ("reserved", c_int32),
         ("stream", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_uint64),
     ]
 
 
@@ -62,6 +64,7 @@ EXPORTS = {
     "launch_sm120_matmul": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "sm120_gemm_desc_init": (None, [POINTER(SM120GemmDesc)]),
     "sm120_launch_matmul_ex": (c_int, [POINTER(SM120GemmDesc)]),
+    "sm120_matmul_workspace_bytes": (ctypes.c_size_t, [POINTER(SM120GemmDesc)]),
     "sm120_launch_matmul_grad_a": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "sm120_launch_matmul_grad_b": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "sm120_quantize_fp8_scratch_bytes": (ctypes.c_size_t, [c_int64]),

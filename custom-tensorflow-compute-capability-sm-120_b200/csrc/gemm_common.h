@@ -25,6 +25,7 @@ struct GemmProblem {
     int64_t stride_a, stride_b, stride_c;  // elements
     int transpose_a, transpose_b;
     int in_dtype, out_dtype, bias_dtype;
+    int tf32_operands;               // in_dtype FLOAT32 whose values already fit tf32 (low 13 mantissa bits zero)
     float alpha, beta;
     float inv_scale;                 // 1 / (scale_a * scale_b) from the by-value scales
     const float* scale_a_dev;
@@ -52,6 +53,11 @@ bool tc_supported(const GemmProblem& p, const char** why);
 // Enqueue on p.stream.  Both return the launch status.
 cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char** kernel_name);
 cudaError_t simt_launch(const GemmProblem& p, const char** kernel_name);
+
+// fp32 on tensor cores (3xTF32): bytes of workspace the split operands need, and the launch
+// (split kernels + tcgen05 kind::tf32 GEMM over the three partial products).
+size_t tf32x3_workspace_bytes(const GemmProblem& p);
+cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_limit_ns, const char** kernel_name);
 
 // Per-device status word of the tcgen05 kernel (0 = no wait ran out).
 cudaError_t tc_read_status(unsigned int* status, int clear);

