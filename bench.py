@@ -176,6 +176,12 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def config_dict(args, spec, world, l2_note):
+    """The `config` object, identical for both arms."""
+    return {"workload": args.workload, "gather": getattr(args, "gather", "none"), "M_per_gpu": spec["M"], "M_total": spec["M"] * world, "N": spec["N"],
+            "K": spec["K"], "batch": spec["batch"], "sharding": "M-slabs, B replicated; collective only with --gather", "l2": l2_note}
+
+
 # ---------------------------------------------------------------------------
 # reference arm / CPU baseline: the oracle's fp32 host-BLAS product
 # ---------------------------------------------------------------------------
@@ -223,9 +229,9 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": min(args.warmup, 2), "ms_per_step": ms, "higher_is_better": True, "scaling": spec["scaling"],
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "M": spec["M"], "N": spec["N"], "K": spec["K"], "batch": spec["batch"],
-                   "note": "CPU restatement of the reference's fallback path (tf.linalg.matmul + bias_add + activation); "
-                           "TensorFlow itself cannot be installed here"},
+        "config": config_dict(args, spec, world, "host memory; every step multiplies the same bounded sample"),
+        "note": "CPU restatement (oracle port) of the reference's fallback path tf.linalg.matmul + bias_add + activation, "
+                "fp32 host BLAS on all cores; TensorFlow itself cannot be installed here",
         "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": cores, "kind": "port", "sample": text},
         "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -247,25 +253,25 @@ def nvml_index(torch, dev_index):
         return dev_index
 
 
-def time_device_steps(torch, ops, sets, kw, steps, warmup, barrier):
-    """W warm-up launches, then K launches rotating over the buffer sets, timed
-    with CUDA events on the launch stream.  Returns seconds for the K launches."""
-    outs = []
+def time_device_steps(torch, ops, sets, kw, steps, warmup, barrier, step_fn=None):
+    """W warm-up steps, then K steps rotating over the buffer sets, timed with CUDA
+    events on the launch stream.  A step is one product (step_fn may add the gather
+    of an M-sharded product).  Returns seconds for the K steps."""
+    if step_fn is None:
+        def step_fn(a, b, out):
+            ops.fused_matmul(a, b, out=out, **kw)
     for i in range(warmup):
-        a, b, out = sets[i % len(sets)]
-        ops.fused_matmul(a, b, out=out, **kw)
+        step_fn(*sets[i % len(sets)])
     torch.cuda.synchronize()
     barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
-        a, b, out = sets[i % len(sets)]
-        ops.fused_matmul(a, b, out=out, **kw)
+        step_fn(*sets[i % len(sets)])
     e1.record()
     torch.cuda.synchronize()
     barrier()
-    del outs
     return e0.elapsed_time(e1) * 1e-3
 
 
@@ -355,12 +361,29 @@ def run_gpu(args, rank, world, local_rank):
     spec = workload_spec(args.workload, world)
     peaks, peak_kind = measured_peaks()
     sets, kw = build_sets(torch, spec, device)
+    n_sets = len(sets)
+
+    # optional gather of the M-sharded product (N > 1): NCCL all-gather per row chunk, or fused into the GEMM epilogue
+    step_fn = None
+    if args.gather != "none":
+        if world == 1:
+            raise SystemExit("--gather needs --gpus N > 1")
+        sh = pkg.mshard.MShardedMatmul(spec["M"] * world, spec["N"])
+        out_dt = sets[0][2].dtype
+        if args.gather == "fused":
+            bufs = pkg.mshard.PeerBuffers(sh, out_dt, device)
+
+            def step_fn(a, b, out):
+                sh.gathered_fused(a, b, bufs, **kw)
+        else:
+            def step_fn(a, b, out):
+                sh.gathered(a, b, out_dtype=out_dt, chunks=4, **kw)
 
     sampler = ClockSampler(nvml_index(torch, local_rank)) if rank == 0 else None
     launches0 = binding.launch_count()
     if sampler:
         sampler.start()
-    secs = time_device_steps(torch, ops, sets, kw, args.steps, args.warmup, barrier)
+    secs = time_device_steps(torch, ops, sets, kw, args.steps, args.warmup, barrier, step_fn)
     if sampler:
         sampler.stop()
     launches = binding.launch_count() - launches0 - args.warmup
@@ -429,10 +452,9 @@ def run_gpu(args, rank, world, local_rank):
             "metric": METRIC, "value": world * tf_gpu, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": per_launch * 1e3, "higher_is_better": True,
             "scaling": spec["scaling"], "vs_baseline": None, "dtype": spec["dtype"], "data": "synthetic",
-            "config": {"workload": args.workload, "M_per_gpu": spec["M"], "M_total": spec["M"] * world, "N": spec["N"],
-                       "K": spec["K"], "batch": spec["batch"], "sharding": "M-slabs, B replicated, no collective",
-                       "l2": f"operands rotate over {len(sets)} buffer set(s) of {spec['bytes'] / 1e6:.0f} MB; "
-                             "consecutive steps never reuse a set, total exceeds the 126 MB L2"},
+            "config": config_dict(args, spec, world,
+                                  f"operands rotate over {n_sets} buffer set(s) of {spec['bytes'] / 1e6:.0f} MB; "
+                                  "consecutive steps never reuse a set, total exceeds the 126 MB L2"),
             "tflops_per_gpu": tf_gpu,
             "pct_of_nominal_dense_peak": 100.0 * tf_gpu / NOMINAL_PEAK[spec["dtype"]],
             "pct_of_measured_bf16_peak": 100.0 * tf_gpu / peak,
@@ -463,6 +485,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg2bf16", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--impl", default="sm120", choices=["sm120", "reference"])
+    ap.add_argument("--gather", default="none", choices=["none", "nccl", "fused"],
+                    help="N > 1 only: also produce the whole C on every rank inside the timed step, by an NCCL "
+                         "all-gather (per row chunk, overlapped) or by the GEMM epilogue's own peer stores")
     ap.add_argument("--no-side-table", action="store_true", help="skip the per-configuration table at N=1")
     ap.add_argument("--lean", action="store_true",
                     help="for runs under a profiler: also skip the CPU baseline and the extra launches that lengthen a "

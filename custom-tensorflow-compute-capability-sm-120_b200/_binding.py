@@ -65,6 +65,11 @@ EXPORTS = {
     "sm120_gemm_desc_init": (None, [POINTER(SM120GemmDesc)]),
     "sm120_launch_matmul_ex": (c_int, [POINTER(SM120GemmDesc)]),
     "sm120_matmul_workspace_bytes": (ctypes.c_size_t, [POINTER(SM120GemmDesc)]),
+    "sm120_launch_matmul_gather": (c_int, [POINTER(SM120GemmDesc), POINTER(c_void_p), c_int]),
+    "sm120_enable_peer_access": (c_int, [c_int]),
+    "sm120_ipc_export": (c_int, [c_void_p, c_void_p, POINTER(c_uint64)]),
+    "sm120_ipc_import": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "sm120_ipc_close": (c_int, [c_void_p]),
     "sm120_launch_matmul_grad_a": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "sm120_launch_matmul_grad_b": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "sm120_quantize_fp8_scratch_bytes": (ctypes.c_size_t, [c_int64]),

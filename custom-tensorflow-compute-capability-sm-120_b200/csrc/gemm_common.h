@@ -35,6 +35,10 @@ struct GemmProblem {
     cudaStream_t stream;
     int device;
     int sm_count;
+    // further buffers that receive a copy of the [M, N] result (same pitch, batch stride and dtype as C):
+    // other GPUs' memory when the launch also does the all-gather of an M-sharded product
+    void* extra_dests[7];
+    int num_extra_dests;
 };
 
 __host__ __device__ inline int dtype_size(int dtype) {

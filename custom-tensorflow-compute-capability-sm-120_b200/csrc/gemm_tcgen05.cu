@@ -70,6 +70,12 @@ constexpr int EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t EPI_STAGE_BYTES = 4096;   // per epilogue warp: 32 rows x 128 B (four warps share 128 rows)
 
+constexpr int MAX_DESTS = 8;
+// Tensor maps of the output: entry 0 is the caller's C; entries 1.. are further
+// copies of the same [M, N] block in other buffers (other GPUs' memory when the
+// launch also performs the all-gather of an M-sharded product).
+struct DestMaps { CUtensorMap m[MAX_DESTS]; };
+
 struct TcParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, k_blocks, num_tiles;   // tiles are (CG*128) x BN
@@ -84,6 +90,7 @@ struct TcParams {
     int out_dtype;
     int c_vec_ok;                   // C rows may be written with 16-byte stores
     int use_tma_store;              // epilogue goes through shared memory and TMA (needs beta == 0, aligned C)
+    int num_dests;                  // how many of DestMaps::m every output block is stored to (>= 1)
     int epi_cols;                   // columns per TMA store: 64 or 32 (one staging row of 128 or 64 bytes)
     int epi_row_bytes;              // bytes per staging row: 128 or 64
     const void* bias;
@@ -621,7 +628,7 @@ struct TileCfg {
 };
 
 template <int KIND, int BN, int STAGES, int CG, int ACTC>
-__device__ __forceinline__ void epilogue_role(const TcParams& p, const CUtensorMap* tmap_c, const WaitCtx& wctx,
+__device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps* dests, const WaitCtx& wctx,
                                               uint32_t tmem_base, uint32_t acc_full_bar, uint32_t acc_empty_addr,
                                               uint32_t stage_addr, int warp, int lane, uint32_t cta_rank, int first_tile,
                                               int tile_step) {
@@ -708,7 +715,8 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const CUtensorM
                         fence_proxy_async_smem();
                         half_barrier(1 + half);
                         if (lane_group == 0 && lane == 0 && cta_row0 < p.M) {
-                            tma_store_3d(tmap_c, stage_addr, col0 - sub * 32, cta_row0, bz);
+                            for (int g = 0; g < p.num_dests; ++g)      // own C, then every peer's copy
+                                tma_store_3d(&dests->m[g], stage_addr, col0 - sub * 32, cta_row0, bz);
                             bulk_commit_group();
                         }
                     }
@@ -723,14 +731,21 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const CUtensorM
             if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
         }
     }
-    if (lane_group == 0 && lane == 0) bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
+    if (lane_group == 0 && lane == 0) {
+        bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
+        if (p.num_dests > 1) {
+            // copies that went to other GPUs: wait for the writes themselves and publish them system-wide
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            __threadfence_system();
+        }
+    }
 }
 
 template <int KIND, int BN, int STAGES, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                           const __grid_constant__ CUtensorMap tmap_b,
-                          const __grid_constant__ CUtensorMap tmap_c,
+                          const __grid_constant__ DestMaps dests,
                           const TcParams p) {
     using Cfg = TileCfg<KIND, BN, STAGES, CG>;
     constexpr int EPB = Cfg::EPB, BK = Cfg::BK, UMMA_K = Cfg::UMMA_K, BN_CTA = Cfg::BN_CTA;
@@ -776,7 +791,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fence_proxy_async_smem();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
-        prefetch_tmap(&tmap_c);
+        prefetch_tmap(&dests.m[0]);
     }
     if (warp == 1) {
         tmem_alloc<CG>(smem_u32(tmem_holder), TMEM_COLS);
@@ -932,16 +947,16 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t stage_addr = smem_u32(epi_smem) + ((warp - 2) >> 2) * (4 * EPI_STAGE_BYTES);   // 16 KB per column half
         switch (p.activation) {
             case SM120_ACTIVATION_NONE:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_NONE>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_NONE>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
                 break;
             case SM120_ACTIVATION_RELU:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_RELU>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_RELU>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
                 break;
             case SM120_ACTIVATION_GELU_ERF:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_GELU_ERF>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_GELU_ERF>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
                 break;
             default:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_DYNAMIC>(p, &tmap_c, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
+                epilogue_role<KIND, BN, STAGES, CG, ACTC_DYNAMIC>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
                 break;
         }
     }
@@ -1046,7 +1061,7 @@ static std::atomic<int> g_force_cta_group{0};     // 0 = choose, 1 / 2 = force (
 void tc_set_force_cta_group(int cg) { g_force_cta_group.store(cg); }
 
 template <int KIND, int BN, int STAGES, int CG>
-static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcParams& tp,
+static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DestMaps& tc, const TcParams& tp,
                                   int sm_count, int device, cudaStream_t stream) {
     using Cfg = TileCfg<KIND, BN, STAGES, CG>;
     static std::atomic<uint64_t> attr_done{0};     // one bit per device
@@ -1172,7 +1187,8 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 
     tp.idesc_half = (tp.idesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>((bn / 2) >> 3) << 17);
 
-    CUtensorMap ta, tb, tc;
+    CUtensorMap ta, tb;
+    DestMaps tc;
     const int64_t nb_a = tp.a_batched ? p.batch : 1;
     const int64_t nb_b = tp.b_batched ? p.batch : 1;
     const uint32_t bn_cta = static_cast<uint32_t>(bn / cg);
@@ -1187,13 +1203,24 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     // 128-byte staging row, but not more than one epilogue warp owns (bn / 2).
     tp.epi_cols = (bn / 2 >= 64 && out_es == 2) ? 64 : 32;
     tp.epi_row_bytes = tp.epi_cols * out_es;
+    tp.num_dests = 1;
     if (tp.use_tma_store) {
-        ok = encode_3d(&tc, p.C, p.out_dtype, p.N, p.M, p.batch, p.ldc, p.batch > 1 ? p.stride_c : p.M * p.ldc,
-                       static_cast<uint32_t>(tp.epi_cols), BM,
-                       tp.epi_row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
-        if (!ok) tp.use_tma_store = 0;
+        const CUtensorMapSwizzle sw = tp.epi_row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+        ok = encode_3d(&tc.m[0], p.C, p.out_dtype, p.N, p.M, p.batch, p.ldc, p.batch > 1 ? p.stride_c : p.M * p.ldc,
+                       static_cast<uint32_t>(tp.epi_cols), BM, sw);
+        for (int g = 0; ok && g < p.num_extra_dests; ++g) {
+            ok = aligned16(p.extra_dests[g]) &&
+                 encode_3d(&tc.m[1 + g], p.extra_dests[g], p.out_dtype, p.N, p.M, p.batch, p.ldc,
+                           p.batch > 1 ? p.stride_c : p.M * p.ldc, static_cast<uint32_t>(tp.epi_cols), BM, sw);
+        }
+        if (ok) tp.num_dests = 1 + p.num_extra_dests;
+        else if (p.num_extra_dests > 0) return cudaErrorInvalidValue;
+        else tp.use_tma_store = 0;
+    } else if (p.num_extra_dests > 0) {
+        return cudaErrorInvalidValue;        // extra destinations are written by TMA stores only
     }
-    if (!tp.use_tma_store) tc = ta;      // never dereferenced by the kernel
+    if (!tp.use_tma_store) tc.m[0] = ta;     // never dereferenced by the kernel
+    for (int g = tp.num_dests; g < MAX_DESTS; ++g) tc.m[g] = tc.m[0];
 
 #define SM120_TC_CASE(KIND_, BN_, ST_, CG_, NAME_)                                                       \
     do {                                                                                                 \

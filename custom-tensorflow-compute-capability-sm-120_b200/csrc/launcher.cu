@@ -200,6 +200,72 @@ cudaError_t sm120_launch_matmul_ex(const SM120GemmDesc* desc) {
     return launch_resolved(p, desc->path, desc->workspace, desc->workspace_bytes);
 }
 
+cudaError_t sm120_launch_matmul_gather(const SM120GemmDesc* desc, void* const* peer_c, int num_peers) {
+    GemmProblem p;
+    cudaError_t e = resolve(desc, &p);
+    if (e != cudaSuccess) return e;
+    if (num_peers < 0 || num_peers > 7 || (num_peers > 0 && peer_c == nullptr)) return cudaErrorInvalidValue;
+    if (p.beta != 0.0f || p.in_dtype == SM120_DTYPE_FLOAT32) return cudaErrorInvalidValue;
+    for (int g = 0; g < num_peers; ++g) {
+        if (peer_c[g] == nullptr) return cudaErrorInvalidValue;
+        p.extra_dests[g] = peer_c[g];
+    }
+    p.num_extra_dests = num_peers;
+    return launch_resolved(p, SM120_PATH_TENSOR_CORE);
+}
+
+cudaError_t sm120_enable_peer_access(int peer_device) {
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();       // clear the sticky-less error state
+        return cudaSuccess;
+    }
+    return e;
+}
+
+cudaError_t sm120_ipc_export(const void* ptr, void* handle_out, uint64_t* offset_out) {
+    if (ptr == nullptr || handle_out == nullptr || offset_out == nullptr) return cudaErrorInvalidValue;
+    // base of the allocation that holds ptr (driver call, resolved at run time: no link-time dependency on libcuda)
+    typedef int (*GetRangeFn)(unsigned long long*, size_t*, unsigned long long);
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q);
+    if (e != cudaSuccess) return e;
+    if (q != cudaDriverEntryPointSuccess || sym == nullptr) return cudaErrorNotSupported;
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (reinterpret_cast<GetRangeFn>(sym)(&base, &size, reinterpret_cast<unsigned long long>(ptr)) != 0) return cudaErrorInvalidValue;
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+    if (e != cudaSuccess) return e;
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    memcpy(handle_out, &h, sizeof(h));
+    *offset_out = reinterpret_cast<unsigned long long>(ptr) - base;
+    return cudaSuccess;
+}
+
+cudaError_t sm120_ipc_import(const void* handle, void** base_out) {
+    if (handle == nullptr || base_out == nullptr) return cudaErrorInvalidValue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* base = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return e;
+    cudaPointerAttributes attr;
+    e = cudaPointerGetAttributes(&attr, base);
+    if (e != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+        cudaIpcCloseMemHandle(base);
+        return e != cudaSuccess ? e : cudaErrorInvalidValue;
+    }
+    *base_out = base;
+    return cudaSuccess;
+}
+
+cudaError_t sm120_ipc_close(void* base) {
+    if (base == nullptr) return cudaErrorInvalidValue;
+    return cudaIpcCloseMemHandle(base);
+}
+
 size_t sm120_matmul_workspace_bytes(const SM120GemmDesc* desc) {
     GemmProblem p;
     if (resolve(desc, &p) != cudaSuccess) return 0;

@@ -4,9 +4,15 @@ C = A @ B is split by rows: rank r of G owns the contiguous slab
 A[r*Ms:(r+1)*Ms, :] (Ms = ceil(M / G), rounded up to the 128-row tile) and
 computes the same rows of C with B replicated on every GPU.  The slabs are
 independent, so the product itself needs no communication.  Only when the
-caller asks for the gathered C does a collective run: an all-gather of the
-[Ms, N] slabs over NCCL (NVLink / NVSwitch), issued per row-chunk on a side
-stream so that the all-gather of chunk c overlaps the GEMM of chunk c+1.
+caller asks for the gathered C is anything exchanged, in one of two ways:
+
+* ``gathered``: an all-gather of the [Ms, N] slabs over NCCL (NVLink /
+  NVSwitch), issued per row-chunk on a side stream so that the all-gather of
+  chunk c overlaps the GEMM of chunk c+1;
+* ``gathered_fused``: the GEMM kernel's own epilogue stores every output block
+  into every rank's copy of C (peer memory mapped through CUDA IPC, TMA stores
+  over NVLink), so the all-gather happens while the tiles are computed and the
+  only collective left is a one-element barrier.
 
 The reference has no multi-GPU code (its only trace is
 tf.distribute.MirroredStrategy in docs/api-reference.md:510-511); this module
@@ -138,3 +144,78 @@ class MShardedMatmul:
             dist.all_gather_into_tensor(full, chunk.contiguous() if not chunk.is_contiguous() else chunk, group=self.group)
         else:
             dist.all_gather(views, chunk, group=self.group)
+
+
+class PeerBuffers:
+    """Every rank's gathered-C buffer [G*Ms, N], reachable from this process.
+
+    Each rank allocates its buffer with torch and publishes the CUDA IPC handle of
+    the allocation that holds it (plus the buffer's offset inside it); every other
+    rank opens that handle with ITS OWN device current, which maps the memory for
+    kernels of that device and sets up peer access.  `addr[r]` is then the address
+    of rank r's buffer in this process.  Set up once, outside timed regions; the
+    buffer must stay alive as long as any rank uses it."""
+
+    def __init__(self, sharded: "MShardedMatmul", out_dtype: torch.dtype, device: torch.device):
+        import ctypes
+        from . import _binding
+        G, ms = sharded.world_size, sharded.rows_per_rank
+        self.rank = sharded.rank
+        self.device = device
+        self.full = torch.zeros((G * ms, sharded.N), dtype=out_dtype, device=device)
+        self.row_bytes = sharded.N * self.full.element_size()
+        lib = _binding.load_library()
+        handle = ctypes.create_string_buffer(64)
+        offset = ctypes.c_uint64(0)
+        with torch.cuda.device(device):
+            rc = lib.sm120_ipc_export(self.full.data_ptr(), handle, ctypes.byref(offset))
+        if rc != 0:
+            raise RuntimeError(f"cannot export the C buffer through CUDA IPC: {_binding.error_string(rc)}")
+        published: List[object] = [None] * G
+        dist.all_gather_object(published, (bytes(handle.raw), int(offset.value)), group=sharded.group)
+        self.addr: List[int] = []
+        self._opened: List[int] = []
+        with torch.cuda.device(device):
+            for r in range(G):
+                if r == self.rank:
+                    self.addr.append(self.full.data_ptr())
+                    continue
+                raw, off = published[r]
+                base = ctypes.c_void_p(0)
+                rc = lib.sm120_ipc_import(ctypes.create_string_buffer(raw, 64), ctypes.byref(base))
+                if rc != 0 or not base.value:
+                    raise RuntimeError(f"cannot open rank {r}'s C buffer: {_binding.error_string(rc)}")
+                self._opened.append(base.value)
+                self.addr.append(base.value + off)
+        dist.barrier(group=sharded.group)                             # nobody proceeds before every handle is open
+
+    def close(self) -> None:
+        """Unmap the peers' buffers (collective: every rank calls it, with no kernel in flight)."""
+        from . import _binding
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+        lib = _binding.load_library()
+        with torch.cuda.device(self.device):
+            for base in self._opened:
+                lib.sm120_ipc_close(base)
+        self._opened = []
+        dist.barrier()
+
+
+def _gathered_fused(self, a_slab: torch.Tensor, b: torch.Tensor, buffers: PeerBuffers, **kwargs) -> torch.Tensor:
+    """The whole C [M, N] on every rank from ONE kernel per rank: the epilogue
+    writes this rank's rows into every rank's buffer.  A one-element all-reduce
+    afterwards orders the ranks (it moves no matrix data)."""
+    if a_slab.shape[0] != self.local_rows:
+        raise ValueError(f"rank {self.rank} owns {self.local_rows} rows of A, got {a_slab.shape[0]}")
+    ms = self.rows_per_rank
+    lo, hi = self.rank * ms, self.rank * ms + self.local_rows
+    if self.local_rows > 0:
+        peers = [buffers.addr[r] + lo * buffers.row_bytes for r in range(self.world_size) if r != self.rank]
+        self.matmul_fn(a_slab, b, out=buffers.full[lo:hi], peer_outs=peers, **kwargs)
+    token = torch.zeros(1, device=a_slab.device)
+    dist.all_reduce(token, group=self.group)        # enqueued behind the GEMM: completes when every rank's GEMM has
+    return buffers.full[: self.M]
+
+
+MShardedMatmul.gathered_fused = _gathered_fused

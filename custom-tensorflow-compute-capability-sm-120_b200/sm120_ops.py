@@ -217,6 +217,7 @@ def fused_matmul(
     use_tensor_cores: Optional[bool] = None,
     optimization_level: Optional[int] = None,
     fp32_tensor_cores: bool = False,
+    peer_outs: Optional[Sequence[torch.Tensor]] = None,
 ):
     """out = act(alpha / (scale_a * scale_b) * op(a) @ op(b) + beta * out + bias).
 
@@ -231,6 +232,11 @@ def fused_matmul(
     the 3xTF32 tensor-core path instead: several times faster on large products, but
     the tensor cores' truncating accumulation leaves a relative error of about
     K * 2^-27 (1.2e-5 at K = 1024), outside the op's 1e-5 gate.
+
+    ``peer_outs`` (used by ``mshard``): up to 7 more destinations, tensors or raw device
+    addresses (other GPUs' memory opened through CUDA IPC), that receive the same
+    result as ``out`` from the same launch (``sm120_launch_matmul_gather``); they use
+    ``out``'s shape, dtype and strides.
 
     Inputs on the host (numpy arrays or CPU tensors) are copied to the current
     CUDA device, and the result is copied back and returned in the same form;
@@ -367,8 +373,24 @@ def fused_matmul(
         d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
         d.path = _b.PATH_TENSOR_CORE
 
-    with torch.cuda.device(a.device):
-        rc = _b.load_library().sm120_launch_matmul_ex(ctypes.byref(d))
+    if peer_outs:
+        if host_kind is not None or beta != 0.0:
+            raise ValueError("peer_outs needs device operands and beta == 0")
+        addrs = []
+        for t in peer_outs:
+            if isinstance(t, torch.Tensor):
+                if not (t.is_cuda and tuple(t.shape) == tuple(out.shape) and t.dtype == out.dtype and t.stride() == out.stride()):
+                    raise ValueError("every peer output must match `out` in shape, dtype and strides")
+                keep.append(t)
+                addrs.append(t.data_ptr())
+            else:
+                addrs.append(int(t))           # a raw device address (memory of another process, opened through IPC)
+        ptrs = (ctypes.c_void_p * len(addrs))(*addrs)
+        with torch.cuda.device(a.device):
+            rc = _b.load_library().sm120_launch_matmul_gather(ctypes.byref(d), ptrs, len(addrs))
+    else:
+        with torch.cuda.device(a.device):
+            rc = _b.load_library().sm120_launch_matmul_ex(ctypes.byref(d))
     if rc == _b.CUDA_ERROR_INVALID_VALUE:
         raise InvalidArgumentError("SM120MatMul rejected its arguments (cudaErrorInvalidValue)")
     if rc != _b.CUDA_SUCCESS:

@@ -159,6 +159,43 @@ void sm120_gemm_desc_init(SM120GemmDesc* desc);
 cudaError_t sm120_launch_matmul_ex(const SM120GemmDesc* desc);
 
 /*
+ * The product of sm120_launch_matmul_ex whose result block is ALSO written, by
+ * the same kernel's epilogue, into up to 7 further buffers: peer_c[g] points
+ * (in this process's address space) at the place of this [M, N] block inside
+ * buffer g, which uses the same pitch (ldc), batch stride and dtype as desc->C.
+ * With one process per GPU and the buffers living on the other GPUs of the box
+ * (mapped through CUDA IPC, peer access enabled, see
+ * sm120_enable_peer_access), this is the M-sharded product and its all-gather
+ * in one launch: every rank's rows reach every rank's copy of C over NVLink
+ * while the tiles are being computed, and no collective moves data afterwards.
+ * The caller still has to order the ranks (any barrier) before reading rows
+ * that other ranks wrote.  Requires the tensor-core path with beta == 0 and C,
+ * ldc and every peer_c[g] 16-byte aligned; otherwise cudaErrorInvalidValue.
+ * No counterpart in the reference, which has no multi-GPU code.
+ */
+cudaError_t sm120_launch_matmul_gather(const SM120GemmDesc* desc, void* const* peer_c, int num_peers);
+
+/* Lets kernels launched on the current device write to memory of peer_device
+ * (cudaDeviceEnablePeerAccess; already-enabled is not an error).
+ * No counterpart in the reference. */
+cudaError_t sm120_enable_peer_access(int peer_device);
+
+/*
+ * Sharing one rank's C buffer with the other processes of the box (CUDA IPC),
+ * for sm120_launch_matmul_gather.  No counterpart in the reference.
+ *   export: `ptr` is any device pointer of this process (e.g. inside a framework
+ *     allocator's block); handle_out receives the 64-byte IPC handle of the
+ *     allocation that contains it and *offset_out the byte offset of ptr in it.
+ *   import: call with the device current whose kernels will write the memory;
+ *     *base_out receives the address of the peer's allocation in this process
+ *     (add the exporter's offset).  Peer access is set up by the import.
+ *   close: unmaps an imported allocation.
+ */
+cudaError_t sm120_ipc_export(const void* ptr, void* handle_out, uint64_t* offset_out);
+cudaError_t sm120_ipc_import(const void* handle, void** base_out);
+cudaError_t sm120_ipc_close(void* base);
+
+/*
  * Workspace for the opt-in FP32-on-tensor-cores path (3xTF32: each operand is
  * split into two tf32 pieces and three partial products are accumulated by the
  * tensor cores).  It is used only when desc->path == SM120_PATH_TENSOR_CORE and

@@ -50,7 +50,12 @@ def _worker(rank, world, port, ret):
             slab = a[sh.start:sh.stop]
             local = sh.local(slab, b_local, **kw)
             full = sh.gathered(slab, b_local, out_dtype=torch.bfloat16, chunks=chunks, **kw)
+            bufs = ms.PeerBuffers(sh, torch.bfloat16, torch.device("cuda", rank))
+            fused = sh.gathered_fused(slab, b_local, bufs, **kw).clone()
             torch.cuda.synchronize()
+            results[name + "_fused"] = bool(tuple(fused.shape) == (M, N) and torch.equal(fused, whole))
+            bufs.close()
+            del bufs
             results[name] = bool(torch.equal(b_local, b) and torch.equal(local, whole[sh.start:sh.stop])
                                  and tuple(full.shape) == (M, N) and torch.equal(full, whole))
         ret[rank] = results

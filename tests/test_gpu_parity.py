@@ -472,3 +472,18 @@ def test_fp32_tensor_core_path_is_opt_in(ops, binding):
     d.path = binding.PATH_TENSOR_CORE
     assert lib.sm120_matmul_workspace_bytes(ctypes.byref(d)) == 2 * 256 * 3 * 256 * 4
     assert lib.sm120_launch_matmul_ex(ctypes.byref(d)) == 1
+
+
+def test_empty_and_zero_inner_dimension(ops, binding):
+    # no rows / no columns: nothing is launched, the (empty) result has the right shape
+    for (M, N, K) in ((0, 8, 16), (8, 0, 16), (0, 0, 0)):
+        out = ops.advanced_matmul(torch.zeros(M, K, device="cuda"), torch.zeros(K, N, device="cuda"))
+        assert tuple(out.shape) == (M, N)
+    # K == 0: the product is the zero matrix; the epilogue still applies (bias, activation)
+    bias = torch.arange(7, dtype=torch.float32, device="cuda") - 3
+    out = ops.fused_matmul(torch.zeros(5, 0, device="cuda"), torch.zeros(0, 7, device="cuda"), bias=bias, activation="relu")
+    torch.cuda.synchronize()
+    assert binding.last_kernel_name().startswith("simt_f32")
+    assert torch.equal(out, torch.relu(bias).expand(5, 7))
+    out = ops.advanced_matmul(torch.zeros(5, 0, device="cuda").bfloat16(), torch.zeros(0, 7, device="cuda").bfloat16())
+    assert tuple(out.shape) == (5, 7) and float(out.abs().max()) == 0.0
