@@ -17,15 +17,22 @@ namespace sm120 {
 
 // Status and probe words of the kernel (see gemm_tcgen05_kernel.cuh), one set per device.
 __device__ unsigned int g_sm120_status[4];
+#ifdef SM120_EPI_TRACE
+__device__ unsigned long long g_sm120_probe[2 + 256];
+extern "C" int sm120_debug_read_trace(unsigned long long* out) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_sm120_probe, (2 + 256) * sizeof(unsigned long long)));
+}
+#else
 __device__ unsigned long long g_sm120_probe[2];
+#endif
 
 // the variants are compiled in gemm_tcgen05_inst_*.cu
 #define SM120_TC_EXTERN(KIND_, BN_, ST_, CG_) \
     extern template cudaError_t launch_variant<KIND_, BN_, ST_, CG_>(const CUtensorMap&, const CUtensorMap&, const DestMaps&, \
                                                                      const TcParams&, int, int, cudaStream_t);
-SM120_TC_EXTERN(KIND_F16, 256, 6, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
-SM120_TC_EXTERN(KIND_F8, 256, 6, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
-SM120_TC_EXTERN(KIND_TF32, 256, 6, 2) SM120_TC_EXTERN(KIND_TF32, 256, 4, 1) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
+SM120_TC_EXTERN(KIND_F16, 256, 5, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
+SM120_TC_EXTERN(KIND_F8, 256, 5, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
+SM120_TC_EXTERN(KIND_TF32, 256, 5, 2) SM120_TC_EXTERN(KIND_TF32, 256, 4, 1) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
 #undef SM120_TC_EXTERN
 
 // ---------------------------------------------------------------------------
@@ -155,6 +162,10 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         gm = gm < 4 ? 4 : (gm > 64 ? 64 : gm);
         tp.group_m = static_cast<int>(gm < tp.tiles_m ? gm : tp.tiles_m);
     }
+    tp.div_per_batch = make_fast_div(static_cast<uint32_t>(tp.tiles_m) * static_cast<uint32_t>(tp.tiles_n));
+    tp.div_group_span = make_fast_div(static_cast<uint32_t>(tp.group_m) * static_cast<uint32_t>(tp.tiles_n));
+    tp.div_group_m = make_fast_div(static_cast<uint32_t>(tp.group_m));
+    tp.div_group_last = make_fast_div(static_cast<uint32_t>(tp.tiles_m % tp.group_m == 0 ? tp.group_m : tp.tiles_m % tp.group_m));
     tp.num_work = tp.num_tiles;
     tp.full_work = tp.num_tiles;
     tp.a_mn_major = a_mn ? 1 : 0;
@@ -215,19 +226,19 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     if (!b_mn) ok = encode_3d(&tb, p.B, p.in_dtype, p.K, p.N, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.N * p.ldb, bk, bn_cta, CU_TENSOR_MAP_SWIZZLE_128B);
     else       ok = encode_3d(&tb, p.B, p.in_dtype, p.N, p.K, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.K * p.ldb, epb, bk, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
-    // One TMA store writes 128 rows x epi_cols columns: as many columns as fit a
-    // 128-byte staging row, but not more than one epilogue warp owns (bn / 2).
+    // One TMA store writes the 32 rows of one epilogue warp x epi_cols columns: as many columns
+    // as fit a 128-byte staging row, but not more than one epilogue warp owns (bn / 2).
     tp.epi_cols = (bn / 2 >= 64 && out_es == 2) ? 64 : 32;
     tp.epi_row_bytes = tp.epi_cols * out_es;
     tp.num_dests = 1;
     if (tp.use_tma_store) {
         const CUtensorMapSwizzle sw = tp.epi_row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
         ok = encode_3d(&tc.m[0], p.C, p.out_dtype, p.N, p.M, p.batch, p.ldc, p.batch > 1 ? p.stride_c : p.M * p.ldc,
-                       static_cast<uint32_t>(tp.epi_cols), BM, sw);
+                       static_cast<uint32_t>(tp.epi_cols), 32u, sw);
         for (int g = 0; ok && g < p.num_extra_dests; ++g) {
             ok = aligned16(p.extra_dests[g]) &&
                  encode_3d(&tc.m[1 + g], p.extra_dests[g], p.out_dtype, p.N, p.M, p.batch, p.ldc,
-                           p.batch > 1 ? p.stride_c : p.M * p.ldc, static_cast<uint32_t>(tp.epi_cols), BM, sw);
+                           p.batch > 1 ? p.stride_c : p.M * p.ldc, static_cast<uint32_t>(tp.epi_cols), 32u, sw);
         }
         if (ok) tp.num_dests = 1 + p.num_extra_dests;
         else if (p.num_extra_dests > 0) return cudaErrorInvalidValue;
@@ -236,6 +247,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         return cudaErrorInvalidValue;        // extra destinations are written by TMA stores only
     }
     if (!tp.use_tma_store) tc.m[0] = ta;     // never dereferenced by the kernel
+    tp.fast_epi = (tp.use_tma_store && p.N % 32 == 0 && (p.bias == nullptr || tp.bias_vec_ok)) ? 1 : 0;
     for (int g = tp.num_dests; g < MAX_DESTS; ++g) tc.m[g] = tc.m[0];
 
 #define SM120_TC_CASE(KIND_, BN_, ST_, CG_, NAME_)                                                       \
@@ -246,18 +258,18 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 
     if (p.in_dtype == SM120_DTYPE_FLOAT32) {
         // operands already split into tf32 pieces (see split_tf32.cu)
-        if (cg == 2) SM120_TC_CASE(KIND_TF32, 256, 6, 2, "tc_tf32x3_2cta_256x256x32_s6");
+        if (cg == 2) SM120_TC_CASE(KIND_TF32, 256, 5, 2, "tc_tf32x3_2cta_256x256x32_s5");
         if (bn == 256) SM120_TC_CASE(KIND_TF32, 256, 4, 1, "tc_tf32x3_128x256x32_s4");
         if (bn == 128) SM120_TC_CASE(KIND_TF32, 128, 6, 1, "tc_tf32x3_128x128x32_s6");
         SM120_TC_CASE(KIND_TF32, 64, 8, 1, "tc_tf32x3_128x64x32_s8");
     } else if (!fp8) {
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
-        if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 6, 2, bf ? "tc_bf16_2cta_256x256x64_s6" : "tc_f16_2cta_256x256x64_s6");
+        if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 5, 2, bf ? "tc_bf16_2cta_256x256x64_s5" : "tc_f16_2cta_256x256x64_s5");
         if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
         if (bn == 128) SM120_TC_CASE(KIND_F16, 128, 6, 1, bf ? "tc_bf16_128x128x64_s6" : "tc_f16_128x128x64_s6");
         SM120_TC_CASE(KIND_F16, 64, 8, 1, bf ? "tc_bf16_128x64x64_s8" : "tc_f16_128x64x64_s8");
     } else {
-        if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 6, 2, "tc_e4m3_2cta_256x256x128_s6");
+        if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 5, 2, "tc_e4m3_2cta_256x256x128_s5");
         if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, 1, "tc_e4m3_128x256x128_s4");
         if (bn == 128) SM120_TC_CASE(KIND_F8, 128, 6, 1, "tc_e4m3_128x128x128_s6");
         SM120_TC_CASE(KIND_F8, 64, 8, 1, "tc_e4m3_128x64x128_s8");

@@ -68,18 +68,48 @@ enum : int { ACTC_NONE = 0, ACTC_RELU = 1, ACTC_GELU_ERF = 2, ACTC_DYNAMIC = 3 }
 constexpr int BM = 128;                 // rows per CTA
 constexpr int EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
-constexpr uint32_t EPI_STAGE_BYTES = 4096;   // per epilogue warp: 32 rows x 128 B (four warps share 128 rows)
+constexpr uint32_t EPI_STAGE_BYTES = 4096;   // one staging buffer of an epilogue warp: 32 rows x 128 B
 
+constexpr int EPI_PREFETCH = 2;             // 32-column TMEM loads an epilogue warp keeps in flight
 constexpr int MAX_DESTS = 8;
 // Tensor maps of the output: entry 0 is the caller's C; entries 1.. are further
 // copies of the same [M, N] block in other buffers (other GPUs' memory when the
 // launch also performs the all-gather of an M-sharded product).
 struct DestMaps { CUtensorMap m[MAX_DESTS]; };
 
+// Tuning aid, compiled out unless SM120_EPI_TRACE is defined: CTA 0 records SM clock
+// values of its first 16 tiles (16 slots per tile) after the two probe words.
+#ifdef SM120_EPI_TRACE
+#define SM120_TRACE(cond, local, slot) do { if ((cond) && blockIdx.x == 0 && (local) < 16) p.probe[2 + (local) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define SM120_TRACE(cond, local, slot) do {} while (0)
+#endif
+
+// Division by a value fixed at launch: q = (umulhi(n, mul) + n) >> shift for 0 <= n < 2^31.
+struct FastDiv {
+    uint32_t div, mul, shift;
+};
+inline FastDiv make_fast_div(uint32_t d) {
+    FastDiv f{d, 1u, 0u};
+    if (d <= 1u) { f.div = 1u; return f; }
+    uint32_t s = 0;
+    while ((1ull << s) < d) ++s;
+    f.shift = s;
+    f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << s) - d)) / d + 1ull);
+    return f;
+}
+__device__ __forceinline__ int fast_div(int n, const FastDiv& f) {
+    return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shift);
+}
+
 struct TcParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, k_blocks, num_tiles;   // tiles are (CG*128) x BN
     int group_m;                    // row tiles per raster group (tiles of a group share their B columns in L2)
+    FastDiv div_per_batch;          // tiles_m * tiles_n
+    FastDiv div_group_span;         // group_m * tiles_n
+    FastDiv div_group_m;            // rows of a whole group
+    FastDiv div_group_last;         // rows of the last (possibly shorter) group
     int num_work, full_work;        // work items: [0, full_work) are whole tiles, the rest are half-width tiles (two per tile)
     uint32_t idesc;
     uint32_t idesc_half;            // instruction descriptor of a half-width tile (N = BN / 2)
@@ -90,6 +120,7 @@ struct TcParams {
     int out_dtype;
     int c_vec_ok;                   // C rows may be written with 16-byte stores
     int use_tma_store;              // epilogue goes through shared memory and TMA (needs beta == 0, aligned C)
+    int fast_epi;                   // use_tma_store, N % 32 == 0 and a bias (if any) that 16-byte loads can read: straight-line epilogue
     int num_dests;                  // how many of DestMaps::m every output block is stored to (>= 1)
     int epi_cols;                   // columns per TMA store: 64 or 32 (one staging row of 128 or 64 bytes)
     int epi_row_bytes;              // bytes per staging row: 128 or 64
@@ -158,7 +189,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 // arrive on a barrier given by a shared::cluster address (own or peer CTA)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -166,20 +197,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         "{\n\t"
         ".reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// same with cluster-scope acquire: used where the arrivals come from the peer CTA
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
@@ -350,9 +367,8 @@ __device__ __forceinline__ void raise_abort(const WaitCtx& w, uint32_t code) {
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code, bool watch_abort) {
     const unsigned long long t0 = global_timer_ns();
     uint32_t spins = 0;
-    const bool paired = w.peer_abort_addr != 0u;
     for (;;) {
-        if (paired ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 31u) == 0u) {
             if (watch_abort && *w.abort_flag != 0u) return false;
             if (global_timer_ns() - t0 > w.limit_ns) {
@@ -363,21 +379,20 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code, bool watch_abort = true) {
-    if (w.peer_abort_addr != 0u ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, w, code, watch_abort);
 }
 
 __device__ __forceinline__ void decode_tile(int tile, const TcParams& p, int& bz, int& tm, int& tn) {
-    const int per_batch = p.tiles_m * p.tiles_n;
-    bz = tile / per_batch;
-    const int t = tile - bz * per_batch;
-    const int group_span = p.group_m * p.tiles_n;
-    const int g = t / group_span;
+    bz = fast_div(tile, p.div_per_batch);
+    const int t = tile - bz * static_cast<int>(p.div_per_batch.div);
+    const int g = fast_div(t, p.div_group_span);
     const int first_m = g * p.group_m;
-    const int gm = min(p.tiles_m - first_m, p.group_m);
-    const int r = t - g * group_span;
-    tm = first_m + r % gm;
-    tn = r / gm;
+    const int r = t - g * static_cast<int>(p.div_group_span.div);
+    const bool last = first_m + p.group_m > p.tiles_m;          // the shorter group at the bottom
+    const int gm = last ? static_cast<int>(p.div_group_last.div) : p.group_m;
+    tn = last ? fast_div(r, p.div_group_last) : fast_div(r, p.div_group_m);
+    tm = first_m + (r - tn * gm);
 }
 
 // Work item -> batch entry, row tile, first column and width.  The last
@@ -442,6 +457,8 @@ __device__ __forceinline__ void act_apply32(float (&v)[32], int act) {
         for (int j = 0; j < 32; ++j) v[j] = gelu_erf_fast(v[j]);
     } else {
         switch (act) {
+            case SM120_ACTIVATION_RELU:       act_apply32<ACTC_RELU>(v, act); break;
+            case SM120_ACTIVATION_GELU_ERF:   act_apply32<ACTC_GELU_ERF>(v, act); break;
             case SM120_ACTIVATION_LEAKY_RELU: act_loop<SM120_ACTIVATION_LEAKY_RELU>(v); break;
             case SM120_ACTIVATION_ELU:        act_loop<SM120_ACTIVATION_ELU>(v); break;
             case SM120_ACTIVATION_SELU:       act_loop<SM120_ACTIVATION_SELU>(v); break;
@@ -564,26 +581,6 @@ __device__ __forceinline__ void stage_row32(uint32_t block_addr, int r, int row_
     }
 }
 
-// Named barrier among the 128 threads of one column half of the epilogue.
-__device__ __forceinline__ void half_barrier(int id) {
-    asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
-}
-// The same barrier with an AND vote: true when every participant passed true.
-__device__ __forceinline__ bool half_barrier_all(int id, bool pred) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %2, 0;\n\t"
-        "bar.red.and.pred p, %1, 128, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(r)
-        : "r"(id), "r"(pred ? 1u : 0u)
-        : "memory");
-    return r != 0;
-}
-
 // Direct path: this lane writes its row segment to global memory itself (used
 // when beta != 0 or when C cannot be described to TMA).
 __device__ __forceinline__ void store_row32_direct(const TcParams& p, long long off, int ncols, const float (&v)[32]) {
@@ -621,8 +618,11 @@ struct TileCfg {
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t MN_BOX_BYTES = BK * 128;   // one {128 B of M/N, BK} box
     static constexpr uint32_t TMEM_COLS = 2 * BN;        // 128, 256 or 512: a power of two >= 32
-    static constexpr uint32_t EPI_BYTES = EPI_WARPS * EPI_STAGE_BYTES;
     static constexpr uint32_t BAR_BYTES = 256;
+    // two staging buffers per epilogue warp where the pipeline stages leave room, else one
+    static constexpr int EPI_BUFS =
+        (size_t(STAGES) * STAGE_BYTES + 2 * EPI_WARPS * EPI_STAGE_BYTES + BAR_BYTES + 1024 <= 232448) ? 2 : 1;
+    static constexpr uint32_t EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_STAGE_BYTES;
     static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024 /* alignment slack */;
     static_assert(BN_CTA % 64 == 0 && BN % 64 == 0, "tile width");
     static_assert((2 * STAGES + 5) * 8 + 8 <= BAR_BYTES, "barrier block");
@@ -635,6 +635,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
                                               uint32_t tmem_base, uint32_t acc_full_bar, uint32_t acc_empty_addr,
                                               uint32_t stage_addr, int warp, int lane, uint32_t cta_rank, int first_tile,
                                               int tile_step) {
+    constexpr int EPI_BUFS = TileCfg<KIND, BN, STAGES, CG>::EPI_BUFS;
     const int lane_group = warp & 3;          // TMEM lanes [32*lane_group, +32) belong to this warp
     const int half = (warp - 2) >> 2;         // which half of the tile's columns
     constexpr int CHUNKS = BN / 64;           // 32-column chunks per warp in a whole tile
@@ -642,6 +643,9 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
     if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
     if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
     const bool has_bias = p.bias != nullptr;
+    const int spg = p.epi_cols >> 5;                    // 32-column chunks per TMA store: 1 or 2
+    const int chunk16_per_sub = (p.out_dtype == SM120_DTYPE_FLOAT32) ? 8 : 4;
+    uint32_t stores = 0;                                // TMA stores committed by this warp: picks the staging buffer
     int local = 0;
     for (int tile = first_tile; tile < p.num_work; tile += tile_step, ++local) {
         int bz, tm, n0, width;
@@ -660,36 +664,47 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
 
         bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
         ok = __all_sync(0xFFFFFFFFu, ok);
-        // the four warps of a column half share staging memory and named barriers: they go on, or leave, together
-        ok = half_barrier_all(1 + half, ok);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * cols_per_warp;
-        const int cta_row0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
-        const int spg = p.epi_cols >> 5;                    // 32-column chunks per TMA store: 1 or 2
-        const int chunk16_per_sub = (p.out_dtype == SM120_DTYPE_FLOAT32) ? 8 : 4;
 
-        uint32_t acc[2][32];
+        // Drain: up to PRE loads of 32 columns are in flight at once, so the TMEM latency is
+        // paid about once per tile, and the buffer goes back to the MMA role as soon as the
+        // last load has landed (before the values are processed).
+        constexpr int PRE = CHUNKS < EPI_PREFETCH ? CHUNKS : EPI_PREFETCH;
+        uint32_t acc[PRE][32];
         __syncwarp();
-        if (nvalid > 0) tmem_ld_32x32(t_row, acc[0]);
+#pragma unroll
+        for (int c = 0; c < PRE; ++c)
+            if (c < nvalid) tmem_ld_32x32(t_row + c * 32, acc[c]);
+        if (nvalid == 0) {
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+        }
+
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
-            if (c < nvalid) {                               // warp-uniform, and the same in the four warps of a half
+            if (c < nvalid) {                               // warp-uniform
                 const int col0 = colbase + c * 32;
                 const int ncols = min(32, p.N - col0);
-                tmem_ld_wait_regs(acc[c & 1]);
-                if (c + 1 < nvalid) {
-                    __syncwarp();
-                    tmem_ld_32x32(t_row + (c + 1) * 32, acc[(c + 1) & 1]);   // in flight while this chunk is processed
-                } else {
-                    // every column of this warp is in registers: hand the TMEM buffer back
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+                // loads were issued before step 0 and at every step s with s + PRE < nvalid
+                if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
+#pragma unroll
+                    for (int q = 0; q < PRE; ++q) tmem_ld_wait_regs(acc[q]);
+                    if (c + PRE >= nvalid) {                // nothing more to load: hand the TMEM buffer back
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+                    }
                 }
                 float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[c & 1][j]);
+                for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[c % PRE][j]);
+                if (c + PRE < CHUNKS && c + PRE < nvalid) {
+                    __syncwarp();
+                    tmem_ld_32x32(t_row + (c + PRE) * 32, acc[c % PRE]);    // in flight while this chunk is processed
+                }
                 const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
                 if (p.beta != 0.0f && row < p.M) {
 #pragma unroll
@@ -705,36 +720,179 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
                 act_apply32<ACTC>(v, p.activation);
 
                 if (p.use_tma_store) {
+                    // Each warp stages and stores its own 32 rows: no barrier with the other warps.
                     const int sub = (spg == 2) ? (c & 1) : 0;           // position of this chunk in its store
                     const bool first_of_store = sub == 0;
                     const bool last_of_store = (sub == spg - 1) || (c == nvalid - 1);
+                    const uint32_t sbuf = stage_addr + (EPI_BUFS == 2 ? (stores & 1u) * EPI_STAGE_BYTES : 0u);
                     if (first_of_store) {
-                        // the staging block is about to be overwritten: its previous TMA store must have read it
-                        if (lane_group == 0 && lane == 0) bulk_wait_group_read<0>();
-                        half_barrier(1 + half);
+                        // the staging buffer is about to be overwritten: the TMA store that last used it must have read it
+                        if (lane == 0) bulk_wait_group_read<EPI_BUFS - 1>();
+                        __syncwarp();
                     }
-                    stage_row32(stage_addr, lane_group * 32 + lane, p.epi_row_bytes, sub * chunk16_per_sub, v, p.out_dtype);
+                    stage_row32(sbuf, lane, p.epi_row_bytes, sub * chunk16_per_sub, v, p.out_dtype);
                     if (last_of_store) {
                         fence_proxy_async_smem();
-                        half_barrier(1 + half);
-                        if (lane_group == 0 && lane == 0 && cta_row0 < p.M) {
-                            for (int g = 0; g < p.num_dests; ++g)      // own C, then every peer's copy
-                                tma_store_3d(&dests->m[g], stage_addr, col0 - sub * 32, cta_row0, bz);
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (row0 < p.M) {
+                                for (int g = 0; g < p.num_dests; ++g)      // own C, then every peer's copy
+                                    tma_store_3d(&dests->m[g], sbuf, col0 - sub * 32, row0, bz);
+                            }
                             bulk_commit_group();
                         }
+                        ++stores;
                     }
                 } else if (row < p.M) {
                     store_row32_direct(p, off, ncols, v);
                 }
             }
         }
+    }
+    if (lane == 0) {
+        bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
+        if (p.num_dests > 1) {
+            // copies that went to other GPUs: wait for the writes themselves and publish them system-wide
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            __threadfence_system();
+        }
+    }
+}
+
+// The common case, as straight-line code: the result goes out through TMA stores
+// (beta == 0, C aligned), N is a multiple of 32 (a 32-column chunk is inside the
+// matrix or outside it, never across its edge) and the bias, if any, can be read
+// with 16-byte loads.  The output width class is a template parameter so that the
+// staging layout is a compile-time constant.
+constexpr int OUT32 = 0, OUT16 = 1;
+
+template <int KIND, int BN, int STAGES, int CG, int ACTC, int OUTK>
+__device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps* dests, const WaitCtx& wctx,
+                                              uint32_t tmem_base, uint32_t acc_full_bar, uint32_t acc_empty_addr,
+                                              uint32_t stage_addr, int warp, int lane, uint32_t cta_rank, int first_tile,
+                                              int tile_step) {
+    constexpr int EPI_BUFS = TileCfg<KIND, BN, STAGES, CG>::EPI_BUFS;
+    constexpr int CHUNKS = BN / 64;                                    // 32-column chunks per warp in a whole tile
+    constexpr int PRE = CHUNKS < EPI_PREFETCH ? CHUNKS : EPI_PREFETCH;
+    constexpr int EPI_COLS = (OUTK == OUT16 && BN / 2 >= 64) ? 64 : 32; // columns per TMA store (host: TcParams::epi_cols)
+    constexpr int SPG = EPI_COLS / 32;                                  // chunks per TMA store
+    constexpr int ROWB = EPI_COLS * (OUTK == OUT16 ? 2 : 4);            // bytes per staging row: 128 or 64
+    constexpr int C16 = (OUTK == OUT16) ? 4 : 8;                        // 16-byte pieces per 32 values
+    const int lane_group = warp & 3;
+    const int half = (warp - 2) >> 2;
+    float alpha = p.alpha;
+    if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
+    if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
+    const bool scaled = alpha != 1.0f;
+    const bool has_bias = p.bias != nullptr;
+    const bool bf16 = p.out_dtype == SM120_DTYPE_BFLOAT16;
+    // this lane's staging row, and its swizzle term: 16-byte piece k of row r sits at piece k ^ (r & 7)
+    // under the 128-byte swizzle and at k ^ ((r >> 1) & 3) under the 64-byte swizzle
+    const uint32_t srow = stage_addr + static_cast<uint32_t>(lane) * ROWB;
+    const uint32_t swz = static_cast<uint32_t>(ROWB == 128 ? (lane & 7) : ((lane >> 1) & 3)) << 4;
+    uint32_t stores = 0;                                // TMA stores committed by this warp: picks the staging buffer
+    int local = 0;
+    for (int tile = first_tile; tile < p.num_work; tile += tile_step, ++local) {
+        int bz, tm, n0, width;
+        decode_work(tile, p, BN, bz, tm, n0, width);
+        const uint32_t buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
+        const int cols_per_warp = width >> 1;
+        const int colbase = n0 + half * cols_per_warp;
+        const int nvalid = max(0, min(cols_per_warp >> 5, (p.N - colbase) >> 5));          // chunks inside the matrix
+        BiasRaw braw;
+        if (has_bias && nvalid > 0) bias_prefetch32(p, colbase, braw);
+
+        SM120_TRACE(warp == 2 && lane == 0, local, 0);
+        bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        SM120_TRACE(warp == 2 && lane == 0, local, 1);
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * cols_per_warp;
+
+        uint32_t acc[PRE][32];
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < PRE; ++c)
+            if (c < nvalid) tmem_ld_32x32(t_row + c * 32, acc[c]);
         if (nvalid == 0) {
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
         }
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            if (c < nvalid) {                               // warp-uniform
+                const int col0 = colbase + c * 32;
+                // loads were issued before step 0 and at every step s with s + PRE < nvalid
+                if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
+#pragma unroll
+                    for (int q = 0; q < PRE; ++q) tmem_ld_wait_regs(acc[q]);
+                    SM120_TRACE(warp == 2 && lane == 0 && c == 0, local, 2);
+                    if (c + PRE >= nvalid) {                // nothing more to load: hand the TMEM buffer back
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+                    }
+                }
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[c % PRE][j]);
+                if (c + PRE < CHUNKS && c + PRE < nvalid) {
+                    __syncwarp();
+                    tmem_ld_32x32(t_row + (c + PRE) * 32, acc[c % PRE]);    // in flight while this chunk is processed
+                }
+                if (scaled) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] *= alpha;
+                }
+                if (has_bias) {
+                    bias_add_raw32(p, col0, braw, v);
+                    if (c + 1 < nvalid) bias_prefetch32(p, col0 + 32, braw);   // consumed one chunk later
+                }
+                act_apply32<ACTC>(v, p.activation);
+
+                // Each warp stages and stores its own 32 rows: no barrier with the other warps.
+                const int sub = (SPG == 2) ? (c & 1) : 0;              // position of this chunk in its store
+                const bool last_of_store = (sub == SPG - 1) || (c == nvalid - 1);
+                const uint32_t sbuf = (EPI_BUFS == 2) ? (stores & 1u) * EPI_STAGE_BYTES : 0u;
+                if (sub == 0) {
+                    // the staging buffer is about to be overwritten: the TMA store that last used it must have read it
+                    if (lane == 0) bulk_wait_group_read<EPI_BUFS - 1>();
+                    __syncwarp();
+                }
+                if constexpr (OUTK == OUT16) {
+                    uint32_t packed[16];
+                    pack16(v, bf16, packed);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        st_shared_v4(srow + sbuf + ((static_cast<uint32_t>(sub * C16 + k) << 4) ^ swz), packed[4 * k],
+                                     packed[4 * k + 1], packed[4 * k + 2], packed[4 * k + 3]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        st_shared_v4(srow + sbuf + ((static_cast<uint32_t>(sub * C16 + k) << 4) ^ swz), __float_as_uint(v[4 * k]),
+                                     __float_as_uint(v[4 * k + 1]), __float_as_uint(v[4 * k + 2]), __float_as_uint(v[4 * k + 3]));
+                }
+                if (last_of_store) {
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (row0 < p.M) {
+                            for (int g = 0; g < p.num_dests; ++g)      // own C, then every peer's copy
+                                tma_store_3d(&dests->m[g], stage_addr + sbuf, col0 - sub * 32, row0, bz);
+                        }
+                        bulk_commit_group();
+                    }
+                    ++stores;
+                }
+            }
+        }
+        SM120_TRACE(warp == 2 && lane == 0, local, 3);
     }
-    if (lane_group == 0 && lane == 0) {
+    if (lane == 0) {
         bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
         if (p.num_dests > 1) {
             // copies that went to other GPUs: wait for the writes themselves and publish them system-wide
@@ -895,16 +1053,19 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const uint32_t idesc = tile < p.full_work ? p.idesc : p.idesc_half;
                 const uint32_t buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
+                SM120_TRACE(lane == 0, local, 8);
                 bool w = mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u);
                 w = __all_sync(0xFFFFFFFFu, w);
                 if (!w) { ok = false; break; }
                 tcgen05_fence_after();
+                SM120_TRACE(lane == 0, local, 9);
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     w = mbar_wait(full_bar + 8 * stage, phase, wctx, 0x22000000u);
                     w = __all_sync(0xFFFFFFFFu, w);
                     if (!w) { ok = false; break; }
                     tcgen05_fence_after();
+                    SM120_TRACE(lane == 0 && kb == 0, local, 10);
                     const uint32_t soff = stage * (STAGE_BYTES >> 4);
                     if (elect_one_sync()) {
                         if (p.debug_mode == 1) {
@@ -936,6 +1097,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 }
                 __syncwarp();
+                SM120_TRACE(lane == 0, local, 11);
             }
             if (*abort_flag != 0u && issued_any && p.debug_mode != 1) {
                 if (elect_one_sync()) umma_commit<CG>(drain_bar);
@@ -947,21 +1109,22 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // ------------------------------ epilogue ------------------------------
         uint32_t acc_empty_addr = acc_empty_bar;                       // the leader's barrier collects every arrival
         if constexpr (CG == 2) acc_empty_addr = map_to_cta(acc_empty_bar, 0u);
-        const uint32_t stage_addr = smem_u32(epi_smem) + ((warp - 2) >> 2) * (4 * EPI_STAGE_BYTES);   // 16 KB per column half
-        switch (p.activation) {
-            case SM120_ACTIVATION_NONE:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_NONE>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
-                break;
-            case SM120_ACTIVATION_RELU:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_RELU>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
-                break;
-            case SM120_ACTIVATION_GELU_ERF:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_GELU_ERF>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
-                break;
-            default:
-                epilogue_role<KIND, BN, STAGES, CG, ACTC_DYNAMIC>(p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step);
-                break;
+        const uint32_t stage_addr = smem_u32(epi_smem) + (warp - 2) * (Cfg::EPI_BUFS * EPI_STAGE_BYTES);   // this warp's staging buffers
+#define SM120_EPI_ARGS p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step
+#define SM120_EPI_FAST(OUTK)                                                                                        \
+    switch (p.activation) {                                                                                         \
+        case SM120_ACTIVATION_NONE:     epilogue_fast<KIND, BN, STAGES, CG, ACTC_NONE, OUTK>(SM120_EPI_ARGS); break;     \
+        case SM120_ACTIVATION_RELU:     epilogue_fast<KIND, BN, STAGES, CG, ACTC_RELU, OUTK>(SM120_EPI_ARGS); break;     \
+        case SM120_ACTIVATION_GELU_ERF: epilogue_fast<KIND, BN, STAGES, CG, ACTC_GELU_ERF, OUTK>(SM120_EPI_ARGS); break; \
+        default:                        epilogue_fast<KIND, BN, STAGES, CG, ACTC_DYNAMIC, OUTK>(SM120_EPI_ARGS); break;  \
+    }
+        if (p.fast_epi) {
+            if (p.out_dtype == SM120_DTYPE_FLOAT32) { SM120_EPI_FAST(OUT32) } else { SM120_EPI_FAST(OUT16) }
+        } else {
+            epilogue_role<KIND, BN, STAGES, CG, ACTC_DYNAMIC>(SM120_EPI_ARGS);
         }
+#undef SM120_EPI_FAST
+#undef SM120_EPI_ARGS
     }
 
     // ------------------------------ teardown ------------------------------
