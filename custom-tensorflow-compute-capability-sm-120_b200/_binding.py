@@ -109,6 +109,8 @@ def load_library() -> ctypes.CDLL:
         lib.sm120_debug_skip_kblock.argtypes = [c_int]
         lib.sm120_debug_force_cta_group.restype = None
         lib.sm120_debug_force_cta_group.argtypes = [c_int]
+        lib.sm120_debug_force_epi_warps.restype = None
+        lib.sm120_debug_force_epi_warps.argtypes = [c_int]
     except Exception as e:  # remember and re-raise on every later call
         _load_error = e
         raise

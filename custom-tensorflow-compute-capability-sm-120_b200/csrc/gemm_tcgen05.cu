@@ -34,6 +34,11 @@ SM120_TC_EXTERN(KIND_F16, 256, 5, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_
 SM120_TC_EXTERN(KIND_F8, 256, 5, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
 SM120_TC_EXTERN(KIND_TF32, 256, 5, 2) SM120_TC_EXTERN(KIND_TF32, 256, 4, 1) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
 #undef SM120_TC_EXTERN
+// the pair tile with 16 epilogue warps, for short-K (store-bound) problems
+extern template cudaError_t launch_variant<KIND_F16, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+                                                                    const TcParams&, int, int, cudaStream_t);
+extern template cudaError_t launch_variant<KIND_F8, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+                                                                   const TcParams&, int, int, cudaStream_t);
 
 // ---------------------------------------------------------------------------
 // Host side
@@ -116,6 +121,8 @@ void tc_set_split_tail(int on) { g_split_tail.store(on); }
 bool tc_split_tail_enabled() { return g_split_tail.load() != 0; }
 static std::atomic<int> g_force_cta_group{0};     // 0 = choose, 1 / 2 = force (tests and tuning)
 void tc_set_force_cta_group(int cg) { g_force_cta_group.store(cg); }
+static std::atomic<int> g_force_epi_warps{0};     // 0 = choose, 8 / 16 = force where the variant exists (tests and tuning)
+void tc_set_force_epi_warps(int ew) { g_force_epi_warps.store(ew); }
 
 cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char** kernel_name) {
     const int es = dtype_size(p.in_dtype);
@@ -152,6 +159,13 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.tiles_m = static_cast<int>((p.M + BM * cg - 1) / (BM * cg));
     tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
     tp.k_blocks = static_cast<int>((p.K + bk - 1) / bk);
+    // Epilogue warps: with at most 8 k-blocks per tile the MMAs of a tile take less time than
+    // its epilogue, and 16 epilogue warps (pair tiles only) hide the epilogue's latencies.
+    int ew = (cg == 2 && p.in_dtype != SM120_DTYPE_FLOAT32 && tp.k_blocks <= 8) ? 16 : 8;
+    {
+        const int fe = g_force_epi_warps.load();
+        if (fe == 8 || (fe == 16 && cg == 2 && p.in_dtype != SM120_DTYPE_FLOAT32)) ew = fe;
+    }
     tp.num_tiles = static_cast<int>(tiles_for(BM * cg, bn));
     // Raster: tiles are visited in groups of group_m row tiles, column by column, so a
     // group's slice of A (group_m x tile rows x K) stays in L2 while B streams past it once
@@ -227,8 +241,8 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     else       ok = encode_3d(&tb, p.B, p.in_dtype, p.N, p.K, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.K * p.ldb, epb, bk, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
     // One TMA store writes the 32 rows of one epilogue warp x epi_cols columns: as many columns
-    // as fit a 128-byte staging row, but not more than one epilogue warp owns (bn / 2).
-    tp.epi_cols = (bn / 2 >= 64 && out_es == 2) ? 64 : 32;
+    // as fit a 128-byte staging row, but not more than one epilogue warp owns (bn / 2, or bn / 4 with 16 warps).
+    tp.epi_cols = (bn / (ew / 4) >= 64 && out_es == 2) ? 64 : 32;
     tp.epi_row_bytes = tp.epi_cols * out_es;
     tp.num_dests = 1;
     if (tp.use_tma_store) {
@@ -264,11 +278,19 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         SM120_TC_CASE(KIND_TF32, 64, 8, 1, "tc_tf32x3_128x64x32_s8");
     } else if (!fp8) {
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
+        if (cg == 2 && ew == 16) {
+            if (kernel_name) *kernel_name = bf ? "tc_bf16_2cta_256x256x64_s5_e16" : "tc_f16_2cta_256x256x64_s5_e16";
+            return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);
+        }
         if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 5, 2, bf ? "tc_bf16_2cta_256x256x64_s5" : "tc_f16_2cta_256x256x64_s5");
         if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
         if (bn == 128) SM120_TC_CASE(KIND_F16, 128, 6, 1, bf ? "tc_bf16_128x128x64_s6" : "tc_f16_128x128x64_s6");
         SM120_TC_CASE(KIND_F16, 64, 8, 1, bf ? "tc_bf16_128x64x64_s8" : "tc_f16_128x64x64_s8");
     } else {
+        if (cg == 2 && ew == 16) {
+            if (kernel_name) *kernel_name = "tc_e4m3_2cta_256x256x128_s5_e16";
+            return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);
+        }
         if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 5, 2, "tc_e4m3_2cta_256x256x128_s5");
         if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, 1, "tc_e4m3_128x256x128_s4");
         if (bn == 128) SM120_TC_CASE(KIND_F8, 128, 6, 1, "tc_e4m3_128x128x128_s6");

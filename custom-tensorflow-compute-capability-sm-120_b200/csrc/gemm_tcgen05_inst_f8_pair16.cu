@@ -1,0 +1,8 @@
+// Instantiates tensor-core GEMM variants (see gemm_tcgen05_kernel.cuh); one of several files so that
+// the variants compile in parallel.
+#include "gemm_tcgen05_kernel.cuh"
+
+namespace sm120 {
+template cudaError_t launch_variant<KIND_F8, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+                                                            const TcParams&, int, int, cudaStream_t);
+}  // namespace sm120

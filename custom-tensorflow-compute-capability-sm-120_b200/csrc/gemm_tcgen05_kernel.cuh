@@ -66,8 +66,8 @@ enum : int { KIND_F16 = 0, KIND_F8 = 1, KIND_TF32 = 2 };
 enum : int { ACTC_NONE = 0, ACTC_RELU = 1, ACTC_GELU_ERF = 2, ACTC_DYNAMIC = 3 };
 
 constexpr int BM = 128;                 // rows per CTA
-constexpr int EPI_WARPS = 8;
-constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
+// Epilogue warps per CTA (template parameter EW): 8 split a tile's columns in two halves, 16 in four
+// quarters (twice the warps to hide the latencies of a store-bound, short-K problem; 96 registers each).
 constexpr uint32_t EPI_STAGE_BYTES = 4096;   // one staging buffer of an epilogue warp: 32 rows x 128 B
 
 constexpr int EPI_PREFETCH = 2;             // 32-column TMEM loads an epilogue warp keeps in flight
@@ -319,6 +319,23 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
         "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+// The same load and the wait for it in one statement: the registers are valid when it returns.
+// (With the split form the compiler may copy or spill the destination registers between the load
+// and the wait, while the hardware has not written them yet; that is only safe where register
+// pressure is low.)
+__device__ __forceinline__ void tmem_ld_32x32_sync(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
@@ -606,8 +623,10 @@ __device__ __forceinline__ void store_row32_direct(const TcParams& p, long long 
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int KIND, int BN, int STAGES, int CG>
+template <int KIND, int BN, int STAGES, int CG, int EW = 8>
 struct TileCfg {
+    static constexpr int THREADS = 64 + 32 * EW;
+    static constexpr int NSPLIT = EW / 4;           // column parts of a tile, one per group of four epilogue warps
     static constexpr int ES = (KIND == KIND_F16) ? 2 : (KIND == KIND_F8 ? 1 : 4);
     static constexpr int EPB = 128 / ES;            // elements per 128 bytes
     static constexpr int BK = EPB;                  // K elements per stage
@@ -621,8 +640,10 @@ struct TileCfg {
     static constexpr uint32_t BAR_BYTES = 256;
     // two staging buffers per epilogue warp where the pipeline stages leave room, else one
     static constexpr int EPI_BUFS =
-        (size_t(STAGES) * STAGE_BYTES + 2 * EPI_WARPS * EPI_STAGE_BYTES + BAR_BYTES + 1024 <= 232448) ? 2 : 1;
-    static constexpr uint32_t EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_STAGE_BYTES;
+        (size_t(STAGES) * STAGE_BYTES + 2 * EW * EPI_STAGE_BYTES + BAR_BYTES + 1024 <= 232448) ? 2 : 1;
+    static constexpr uint32_t EPI_BYTES = EW * EPI_BUFS * EPI_STAGE_BYTES;
+    static_assert(EW == 8 || EW == 16, "epilogue warps");
+    static_assert(BN >= 32 * NSPLIT, "every epilogue warp needs at least 32 columns");
     static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024 /* alignment slack */;
     static_assert(BN_CTA % 64 == 0 && BN % 64 == 0, "tile width");
     static_assert((2 * STAGES + 5) * 8 + 8 <= BAR_BYTES, "barrier block");
@@ -630,15 +651,16 @@ struct TileCfg {
     static_assert(SMEM > 116224, "one CTA per SM is assumed: shared memory must exceed half of an SM's");
 };
 
-template <int KIND, int BN, int STAGES, int CG, int ACTC>
+template <int KIND, int BN, int STAGES, int CG, int EW, int ACTC>
 __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps* dests, const WaitCtx& wctx,
                                               uint32_t tmem_base, uint32_t acc_full_bar, uint32_t acc_empty_addr,
                                               uint32_t stage_addr, int warp, int lane, uint32_t cta_rank, int first_tile,
                                               int tile_step) {
-    constexpr int EPI_BUFS = TileCfg<KIND, BN, STAGES, CG>::EPI_BUFS;
+    constexpr int EPI_BUFS = TileCfg<KIND, BN, STAGES, CG, EW>::EPI_BUFS;
+    constexpr int NSPLIT = EW / 4;
     const int lane_group = warp & 3;          // TMEM lanes [32*lane_group, +32) belong to this warp
-    const int half = (warp - 2) >> 2;         // which half of the tile's columns
-    constexpr int CHUNKS = BN / 64;           // 32-column chunks per warp in a whole tile
+    const int half = (warp - 2) >> 2;         // which part (half or quarter) of the tile's columns
+    constexpr int CHUNKS = BN / (32 * NSPLIT); // 32-column chunks per warp in a whole tile
     float alpha = p.alpha;
     if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
     if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
@@ -654,7 +676,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
         const uint32_t acc_phase = (local >> 1) & 1;
         const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
         const int row = row0 + lane;
-        const int cols_per_warp = width >> 1;
+        const int cols_per_warp = width / NSPLIT;
         const int colbase = n0 + half * cols_per_warp;
         // chunks of 32 columns this warp owns that start inside the matrix (warp-uniform)
         const int nvalid = max(0, min(cols_per_warp >> 5, (p.N - colbase + 31) / 32));
@@ -671,8 +693,9 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
         // Drain: up to PRE loads of 32 columns are in flight at once, so the TMEM latency is
         // paid about once per tile, and the buffer goes back to the MMA role as soon as the
         // last load has landed (before the values are processed).
-        constexpr int PRE = CHUNKS < EPI_PREFETCH ? CHUNKS : EPI_PREFETCH;
-        uint32_t acc[PRE][32];
+        constexpr int PRE = 0;                  // this path is register-heavy: load and wait in one step
+        constexpr int MODP = PRE > 0 ? PRE : 1;
+        uint32_t acc[MODP][32];
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < PRE; ++c)
@@ -689,7 +712,15 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
                 const int col0 = colbase + c * 32;
                 const int ncols = min(32, p.N - col0);
                 // loads were issued before step 0 and at every step s with s + PRE < nvalid
-                if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
+                if constexpr (PRE == 0) {
+                    __syncwarp();
+                    tmem_ld_32x32_sync(t_row + c * 32, acc[0]);
+                    if (c == nvalid - 1) {                  // nothing more to load: hand the TMEM buffer back
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+                    }
+                } else if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
 #pragma unroll
                     for (int q = 0; q < PRE; ++q) tmem_ld_wait_regs(acc[q]);
                     if (c + PRE >= nvalid) {                // nothing more to load: hand the TMEM buffer back
@@ -700,10 +731,10 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
                 }
                 float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[c % PRE][j]);
-                if (c + PRE < CHUNKS && c + PRE < nvalid) {
+                for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[c % MODP][j]);
+                if (PRE > 0 && c + PRE < CHUNKS && c + PRE < nvalid) {
                     __syncwarp();
-                    tmem_ld_32x32(t_row + (c + PRE) * 32, acc[c % PRE]);    // in flight while this chunk is processed
+                    tmem_ld_32x32(t_row + (c + PRE) * 32, acc[c % MODP]);    // in flight while this chunk is processed
                 }
                 const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
                 if (p.beta != 0.0f && row < p.M) {
@@ -766,15 +797,20 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
 // staging layout is a compile-time constant.
 constexpr int OUT32 = 0, OUT16 = 1;
 
-template <int KIND, int BN, int STAGES, int CG, int ACTC, int OUTK>
+template <int KIND, int BN, int STAGES, int CG, int EW, int ACTC, int OUTK>
 __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps* dests, const WaitCtx& wctx,
                                               uint32_t tmem_base, uint32_t acc_full_bar, uint32_t acc_empty_addr,
                                               uint32_t stage_addr, int warp, int lane, uint32_t cta_rank, int first_tile,
                                               int tile_step) {
-    constexpr int EPI_BUFS = TileCfg<KIND, BN, STAGES, CG>::EPI_BUFS;
-    constexpr int CHUNKS = BN / 64;                                    // 32-column chunks per warp in a whole tile
-    constexpr int PRE = CHUNKS < EPI_PREFETCH ? CHUNKS : EPI_PREFETCH;
-    constexpr int EPI_COLS = (OUTK == OUT16 && BN / 2 >= 64) ? 64 : 32; // columns per TMA store (host: TcParams::epi_cols)
+    constexpr int EPI_BUFS = TileCfg<KIND, BN, STAGES, CG, EW>::EPI_BUFS;
+    constexpr int NSPLIT = EW / 4;
+    constexpr int CHUNKS = BN / (32 * NSPLIT);                         // 32-column chunks per warp in a whole tile
+    // TMEM loads kept in flight while a chunk is processed: only where registers are plentiful (8 warps,
+    // cheap activation); elsewhere the load and its wait are one step (PRE == 0)
+    constexpr bool ASYNC_LD = (EW == 8) && (ACTC == ACTC_NONE || ACTC == ACTC_RELU);
+    constexpr int PRE = ASYNC_LD ? (CHUNKS < EPI_PREFETCH ? CHUNKS : EPI_PREFETCH) : 0;
+    constexpr int MODP = PRE > 0 ? PRE : 1;
+    constexpr int EPI_COLS = (OUTK == OUT16 && BN / NSPLIT >= 64) ? 64 : 32; // columns per TMA store (host: TcParams::epi_cols)
     constexpr int SPG = EPI_COLS / 32;                                  // chunks per TMA store
     constexpr int ROWB = EPI_COLS * (OUTK == OUT16 ? 2 : 4);            // bytes per staging row: 128 or 64
     constexpr int C16 = (OUTK == OUT16) ? 4 : 8;                        // 16-byte pieces per 32 values
@@ -798,7 +834,7 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
         const uint32_t buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
-        const int cols_per_warp = width >> 1;
+        const int cols_per_warp = width / NSPLIT;
         const int colbase = n0 + half * cols_per_warp;
         const int nvalid = max(0, min(cols_per_warp >> 5, (p.N - colbase) >> 5));          // chunks inside the matrix
         BiasRaw braw;
@@ -812,7 +848,7 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
         SM120_TRACE(warp == 2 && lane == 0, local, 1);
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * cols_per_warp;
 
-        uint32_t acc[PRE][32];
+        uint32_t acc[MODP][32];
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < PRE; ++c)
@@ -827,7 +863,15 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
             if (c < nvalid) {                               // warp-uniform
                 const int col0 = colbase + c * 32;
                 // loads were issued before step 0 and at every step s with s + PRE < nvalid
-                if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
+                if constexpr (PRE == 0) {
+                    __syncwarp();
+                    tmem_ld_32x32_sync(t_row + c * 32, acc[0]);
+                    if (c == nvalid - 1) {                  // nothing more to load: hand the TMEM buffer back
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+                    }
+                } else if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
 #pragma unroll
                     for (int q = 0; q < PRE; ++q) tmem_ld_wait_regs(acc[q]);
                     SM120_TRACE(warp == 2 && lane == 0 && c == 0, local, 2);
@@ -839,10 +883,10 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
                 }
                 float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[c % PRE][j]);
-                if (c + PRE < CHUNKS && c + PRE < nvalid) {
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[c % MODP][j]);
+                if (PRE > 0 && c + PRE < CHUNKS && c + PRE < nvalid) {
                     __syncwarp();
-                    tmem_ld_32x32(t_row + (c + PRE) * 32, acc[c % PRE]);    // in flight while this chunk is processed
+                    tmem_ld_32x32(t_row + (c + PRE) * 32, acc[c % MODP]);    // in flight while this chunk is processed
                 }
                 if (scaled) {
 #pragma unroll
@@ -902,13 +946,13 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
     }
 }
 
-template <int KIND, int BN, int STAGES, int CG>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int KIND, int BN, int STAGES, int CG, int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
 sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                           const __grid_constant__ CUtensorMap tmap_b,
                           const __grid_constant__ DestMaps dests,
                           const TcParams p) {
-    using Cfg = TileCfg<KIND, BN, STAGES, CG>;
+    using Cfg = TileCfg<KIND, BN, STAGES, CG, EW>;
     constexpr int EPB = Cfg::EPB, BK = Cfg::BK, UMMA_K = Cfg::UMMA_K, BN_CTA = Cfg::BN_CTA;
     constexpr uint32_t A_BYTES = Cfg::A_BYTES, STAGE_BYTES = Cfg::STAGE_BYTES, MN_BOX_BYTES = Cfg::MN_BOX_BYTES;
     constexpr uint32_t TMEM_COLS = Cfg::TMEM_COLS;
@@ -944,7 +988,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar + 8 * b, 1);
-            mbar_init(acc_empty_bar + 8 * b, EPI_WARPS * CG);   // one arrival per epilogue warp of every CTA of the pair
+            mbar_init(acc_empty_bar + 8 * b, EW * CG);   // one arrival per epilogue warp of every CTA of the pair
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0u;
@@ -1113,15 +1157,15 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #define SM120_EPI_ARGS p, &dests, wctx, tmem_base, acc_full_bar, acc_empty_addr, stage_addr, warp, lane, cta_rank, first_tile, tile_step
 #define SM120_EPI_FAST(OUTK)                                                                                        \
     switch (p.activation) {                                                                                         \
-        case SM120_ACTIVATION_NONE:     epilogue_fast<KIND, BN, STAGES, CG, ACTC_NONE, OUTK>(SM120_EPI_ARGS); break;     \
-        case SM120_ACTIVATION_RELU:     epilogue_fast<KIND, BN, STAGES, CG, ACTC_RELU, OUTK>(SM120_EPI_ARGS); break;     \
-        case SM120_ACTIVATION_GELU_ERF: epilogue_fast<KIND, BN, STAGES, CG, ACTC_GELU_ERF, OUTK>(SM120_EPI_ARGS); break; \
-        default:                        epilogue_fast<KIND, BN, STAGES, CG, ACTC_DYNAMIC, OUTK>(SM120_EPI_ARGS); break;  \
+        case SM120_ACTIVATION_NONE:     epilogue_fast<KIND, BN, STAGES, CG, EW, ACTC_NONE, OUTK>(SM120_EPI_ARGS); break;     \
+        case SM120_ACTIVATION_RELU:     epilogue_fast<KIND, BN, STAGES, CG, EW, ACTC_RELU, OUTK>(SM120_EPI_ARGS); break;     \
+        case SM120_ACTIVATION_GELU_ERF: epilogue_fast<KIND, BN, STAGES, CG, EW, ACTC_GELU_ERF, OUTK>(SM120_EPI_ARGS); break; \
+        default:                        epilogue_fast<KIND, BN, STAGES, CG, EW, ACTC_DYNAMIC, OUTK>(SM120_EPI_ARGS); break;  \
     }
         if (p.fast_epi) {
             if (p.out_dtype == SM120_DTYPE_FLOAT32) { SM120_EPI_FAST(OUT32) } else { SM120_EPI_FAST(OUT16) }
         } else {
-            epilogue_role<KIND, BN, STAGES, CG, ACTC_DYNAMIC>(SM120_EPI_ARGS);
+            epilogue_role<KIND, BN, STAGES, CG, EW, ACTC_DYNAMIC>(SM120_EPI_ARGS);
         }
 #undef SM120_EPI_FAST
 #undef SM120_EPI_ARGS
@@ -1153,13 +1197,13 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // ---------------------------------------------------------------------------
 bool tc_split_tail_enabled();
 
-template <int KIND, int BN, int STAGES, int CG>
+template <int KIND, int BN, int STAGES, int CG, int EW = 8>
 cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DestMaps& tc, const TcParams& tp,
                                   int sm_count, int device, cudaStream_t stream) {
-    using Cfg = TileCfg<KIND, BN, STAGES, CG>;
+    using Cfg = TileCfg<KIND, BN, STAGES, CG, EW>;
     static std::atomic<uint64_t> attr_done{0};     // one bit per device
     static std::atomic<int> max_clusters[64];      // CG == 2: co-resident clusters per device (0 = not asked yet)
-    auto kern = sm120_gemm_tcgen05_kernel<KIND, BN, STAGES, CG>;
+    auto kern = sm120_gemm_tcgen05_kernel<KIND, BN, STAGES, CG, EW>;
     const uint64_t bit = 1ull << (device & 63);
     if ((attr_done.load(std::memory_order_acquire) & bit) == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::SMEM));
@@ -1167,7 +1211,7 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const D
         attr_done.fetch_or(bit, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg{};
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -1193,7 +1237,8 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const D
         // A final wave that is less than half full is run as half-width tiles.
         TcParams t = tp;
         const int rest = tp.num_tiles % clusters;
-        if (tp.num_tiles > clusters && rest > 0 && 2 * rest <= clusters && tc_split_tail_enabled() != 0) {
+        // (not with 16 epilogue warps: a warp's quarter of a half-width tile is narrower than its 64-column store)
+        if (EW == 8 && tp.num_tiles > clusters && rest > 0 && 2 * rest <= clusters && tc_split_tail_enabled() != 0) {
             t.full_work = tp.num_tiles - rest;
             t.num_work = t.full_work + 2 * rest;
         }

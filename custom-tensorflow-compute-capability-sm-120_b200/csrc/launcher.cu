@@ -22,6 +22,8 @@ cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, 
 cudaError_t quant_launch_static(const void* x, int x_dtype, void* q, float* scale_out, long long n, int device, cudaStream_t stream);
 void tc_set_debug_skip_kblock(int kb);
 void tc_set_force_cta_group(int cg);
+void tc_set_force_epi_warps(int ew);
+void tc_set_force_epi_warps(int ew);
 void tc_set_debug_mode(int m);
 void tc_set_split_tail(int on);
 cudaError_t tc_read_probe(unsigned long long* cycles_ns);
@@ -416,6 +418,7 @@ void sm120_debug_skip_kblock(int kb) { tc_set_debug_skip_kblock(kb); }
 // single-CTA or the CTA-pair flavour of the tensor-core kernel, 0 restores the
 // launcher's own choice.
 void sm120_debug_force_cta_group(int cg) { tc_set_force_cta_group(cg); }
+void sm120_debug_force_epi_warps(int ew) { tc_set_force_epi_warps(ew); }
 
 // Timing-experiment hook, not declared in the public header: 1 = the MMA role
 // issues no tcgen05.mma, 2 = the producer issues no TMA loads (results are

@@ -487,3 +487,49 @@ def test_empty_and_zero_inner_dimension(ops, binding):
     assert torch.equal(out, torch.relu(bias).expand(5, 7))
     out = ops.advanced_matmul(torch.zeros(5, 0, device="cuda").bfloat16(), torch.zeros(0, 7, device="cuda").bfloat16())
     assert tuple(out.shape) == (5, 7) and float(out.abs().max()) == 0.0
+
+
+# ----- short-K problems: the 16-warp epilogue of the pair tile against the 8-warp one and the oracle -----
+@pytest.mark.parametrize("case", ["bf16", "bf16_bias_gelu_f32out", "fp8", "f16_relu_batched_ragged_tail"])
+def test_short_k_epilogue_variants_agree(ops, binding, case):
+    lib = binding.load_library()
+    torch.manual_seed(21)
+    kw = {}
+    if case == "bf16":
+        a = torch.randn(2560, 192, device="cuda").bfloat16(); b = torch.randn(192, 2304, device="cuda").bfloat16()
+    elif case == "bf16_bias_gelu_f32out":
+        a = torch.randn(2048, 256, device="cuda").bfloat16(); b = torch.randn(256, 3072, device="cuda").bfloat16()
+        kw = dict(bias=torch.randn(3072, device="cuda").bfloat16(), activation="gelu", out_dtype=torch.float32)
+    elif case == "fp8":
+        a, sa = ops.quantize_fp8(torch.randn(2048, 512, device="cuda")); b, sb = ops.quantize_fp8(torch.randn(2560, 512, device="cuda"))
+        kw = dict(transpose_b=True, scale_a=sa, scale_b=sb)
+    else:   # 5 x 20 x 8 = 800 pair tiles: the last wave is short; M is not a multiple of the tile
+        a = torch.randn(5, 2500, 128, device="cuda").half(); b = torch.randn(5, 128, 2048, device="cuda").half()
+        kw = dict(activation="relu")
+    outs, names = [], []
+    try:
+        for ew in (8, 16):
+            lib.sm120_debug_force_epi_warps(ew)
+            outs.append(ops.fused_matmul(a, b, **kw))
+            torch.cuda.synchronize()
+            names.append(binding.last_kernel_name())
+    finally:
+        lib.sm120_debug_force_epi_warps(0)
+    assert "2cta" in names[0] and not names[0].endswith("_e16") and names[1].endswith("_e16"), names
+    assert torch.equal(outs[0], outs[1]), case
+    assert torch.equal(ops.fused_matmul(a, b, **kw), outs[1])     # the launcher's own choice for short K
+    assert binding.last_kernel_name().endswith("_e16")
+    # and against the float64 oracle on sampled rows (operands as stored; fp8 through its scales)
+    rows = torch.randint(0, a.shape[-2], (24,), device="cuda")
+    a2, b2 = (a[0], b[0]) if a.dim() == 3 else (a, b)
+    o2 = outs[1][0] if a.dim() == 3 else outs[1]
+    A = a2[rows].float().double().cpu().numpy()
+    B = b2.float().double().cpu().numpy()
+    want = A @ (B.T if kw.get("transpose_b") else B)
+    if case == "fp8":
+        want = want / (float(kw["scale_a"]) * float(kw["scale_b"]))
+    if "bias" in kw:
+        want = ref.activation(want + kw["bias"].float().double().cpu().numpy(), ref.ACT_CODES["gelu"])
+    if kw.get("activation") == "relu":
+        want = np.maximum(want, 0.0)
+    assert ref.rel_frobenius(o2[rows].float().cpu().numpy(), want) <= TOL["bfloat16"]
