@@ -132,8 +132,11 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     const bool a_mn = p.transpose_a != 0;       // stored [K,M]: M contiguous
     const bool b_mn = p.transpose_b == 0;       // stored [K,N]: N contiguous
 
-    // Tile choice.  A pair of CTAs on a 256 x 256 tile when that still gives every
-    // SM work; otherwise the widest single-CTA tile that does; level 0 keeps
+    // Tile choice.  A pair of CTAs on a 256 x 256 tile from about 25 such tiles up: the pair
+    // needs half the operand bytes per MMA cycle of a 128 x 128 tile, and measured faster than
+    // narrower tiles on every SM down to that size (1536^3: 36 pair tiles, 12.4 us against
+    // 15.2 us; 1024^3: 16 pair tiles, 9.5 us against 6.0 us).  Otherwise the widest single-CTA
+    // tile that gives every SM work; level 0 keeps
     // 128 x 128.  An MN-major operand is loaded in boxes of 128 bytes of M/N, so a
     // CTA's share of the B tile cannot be narrower than one box (128 fp8 elements).
     const int min_bn = (b_mn && es == 1) ? 128 : 64;
@@ -143,7 +146,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     if (p.optimization_level == 0) {
         bn = p.N > 64 ? 128 : min_bn;
     } else {
-        if (force != 1 && p.M > 128 && p.N > 128 && (force == 2 || tiles_for(256, 256) * 2 >= p.sm_count)) {
+        if (force != 1 && p.M > 128 && p.N > 128 && (force == 2 || tiles_for(256, 256) * 6 >= p.sm_count)) {
             cg = 2; bn = 256;
         } else {
             const int wide[2] = {256, 128};

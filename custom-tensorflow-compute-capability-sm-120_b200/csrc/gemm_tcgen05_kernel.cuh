@@ -1010,6 +1010,11 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // Programmatic dependent launch: everything above touched only this CTA's shared memory and TMEM, so
+    // it may run while the previous kernel of the stream drains; global memory is first touched after
+    // the wait.  The next kernel of the stream may start its own set-up as soon as SMs free up.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -1214,14 +1219,17 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const D
     cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see griddepcontrol in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (CG == 2) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
         int clusters = max_clusters[device & 63].load(std::memory_order_acquire);
         if (clusters == 0) {
             cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1), 1, 1);
