@@ -11,14 +11,15 @@
 // form of src/cuda_kernels/sm120_dynamic_shapes.cu:107-183 and the fused
 // bias + activation + cast epilogue.
 //
-// One CTA = 10 warps:
+// One CTA = 2 + EW warps (EW = 8, or 16 for short-K problems):
 //   warp 0      TMA producer (one elected lane issues): fills the shared-memory ring
 //   warp 1      TMEM allocator; one elected lane issues tcgen05.mma and the commits
-//   warps 2..9  epilogue.  Warp w reads TMEM lanes [32*(w%4), +32) (the hardware
-//               ties a warp to that quarter) and the column half (w-2)/4 of the
-//               tile, 32 columns at a time: tcgen05.ld, alpha/scale, bias,
-//               activation, cast, swizzled st.shared; the four warps of a column half
-//               share a 128-row staging block and one TMA store per 128 x 64 (or 32) block.
+//   warps 2..   epilogue.  Warp w reads TMEM lanes [32*(w%4), +32) (the hardware
+//               ties a warp to that quarter) and the column part (w-2)/4 of the
+//               tile (a half with 8 warps, a quarter with 16), 32 columns at a time:
+//               tcgen05.ld, alpha/scale, bias, activation, cast, swizzled st.shared
+//               into the warp's own staging buffer, and one TMA store per
+//               32 rows x 64 (or 32) columns.  Epilogue warps never wait for one another.
 //
 // Two flavours, chosen by the template parameter CG:
 //   CG = 1  one CTA per tile of 128 x BN (BN = 64, 128, 256).
