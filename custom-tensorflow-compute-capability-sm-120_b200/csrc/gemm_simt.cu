@@ -131,13 +131,11 @@ struct TileLoader {
 };
 
 template <typename T, int BMT, int BNT>
-__global__ void __launch_bounds__(SIMT_THREADS, 2)      // two CTAs per SM: one CTA's barrier waits hide behind the other's FMAs
+__global__ void __launch_bounds__(SIMT_THREADS)
 sm120_gemm_simt_kernel(const SimtParams p) {
     constexpr int TM = BMT / 16, TN = BNT / 16;      // outputs per thread: 8 or 4 in each direction
-    // two shared-memory buffers per operand: the next K step is stored while the current one is read,
-    // so one barrier per step is enough
-    __shared__ __align__(16) float As[2][SIMT_BK][BMT + 4];
-    __shared__ __align__(16) float Bs[2][SIMT_BK][BNT + 4];
+    __shared__ __align__(16) float As[SIMT_BK][BMT + 4];
+    __shared__ __align__(16) float Bs[SIMT_BK][BNT + 4];
 
     const int tid = threadIdx.x;
     const int tx = tid & 15;
@@ -163,14 +161,12 @@ sm120_gemm_simt_kernel(const SimtParams p) {
     if (p.K > 0) {
         la.load(A, p.lda, m0, 0, p.M, p.K, a_kc, a_vec, tid);
         lb.load(B, p.ldb, n0, 0, p.N, p.K, b_kc, b_vec, tid);
-        la.template store<BMT + 4>(As[0], a_kc, a_vec, tid);
-        lb.template store<BNT + 4>(Bs[0], b_kc, b_vec, tid);
     }
-    __syncthreads();
-    int cur = 0;
-    for (long long k0 = 0; k0 < p.K; k0 += SIMT_BK, cur ^= 1) {
-        const bool more = k0 + SIMT_BK < p.K;
-        if (more) {                        // next K step's operands travel while this step is multiplied
+    for (long long k0 = 0; k0 < p.K; k0 += SIMT_BK) {
+        la.template store<BMT + 4>(As, a_kc, a_vec, tid);
+        lb.template store<BNT + 4>(Bs, b_kc, b_vec, tid);
+        __syncthreads();
+        if (k0 + SIMT_BK < p.K) {          // next K step's operands travel while this step is multiplied
             la.load(A, p.lda, m0, k0 + SIMT_BK, p.M, p.K, a_kc, a_vec, tid);
             lb.load(B, p.ldb, n0, k0 + SIMT_BK, p.N, p.K, b_kc, b_vec, tid);
         }
@@ -179,22 +175,18 @@ sm120_gemm_simt_kernel(const SimtParams p) {
             float a[TM], b[TN];
 #pragma unroll
             for (int i = 0; i < TM; i += 4) {
-                const float4 av = *reinterpret_cast<const float4*>(&As[cur][k][ty * 4 + i * 16]);
+                const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4 + i * 16]);
                 a[i] = av.x; a[i + 1] = av.y; a[i + 2] = av.z; a[i + 3] = av.w;
             }
 #pragma unroll
             for (int j = 0; j < TN; j += 4) {
-                const float4 bv = *reinterpret_cast<const float4*>(&Bs[cur][k][tx * 4 + j * 16]);
+                const float4 bv = *reinterpret_cast<const float4*>(&Bs[k][tx * 4 + j * 16]);
                 b[j] = bv.x; b[j + 1] = bv.y; b[j + 2] = bv.z; b[j + 3] = bv.w;
             }
 #pragma unroll
             for (int i = 0; i < TM; ++i)
 #pragma unroll
                 for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-        }
-        if (more) {                        // the other buffer was last read before the previous barrier
-            la.template store<BMT + 4>(As[cur ^ 1], a_kc, a_vec, tid);
-            lb.template store<BNT + 4>(Bs[cur ^ 1], b_kc, b_vec, tid);
         }
         __syncthreads();
     }
