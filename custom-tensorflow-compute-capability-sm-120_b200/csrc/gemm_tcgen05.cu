@@ -30,9 +30,9 @@ __device__ unsigned long long g_sm120_probe[2];
 #define SM120_TC_EXTERN(KIND_, BN_, ST_, CG_) \
     extern template cudaError_t launch_variant<KIND_, BN_, ST_, CG_>(const CUtensorMap&, const CUtensorMap&, const DestMaps&, \
                                                                      const TcParams&, int, int, cudaStream_t);
-SM120_TC_EXTERN(KIND_F16, 256, 5, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
-SM120_TC_EXTERN(KIND_F8, 256, 5, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
-SM120_TC_EXTERN(KIND_TF32, 256, 5, 2) SM120_TC_EXTERN(KIND_TF32, 256, 4, 1) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
+SM120_TC_EXTERN(KIND_F16, 256, 6, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
+SM120_TC_EXTERN(KIND_F8, 256, 6, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
+SM120_TC_EXTERN(KIND_TF32, 256, 6, 2) SM120_TC_EXTERN(KIND_TF32, 256, 4, 1) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
 #undef SM120_TC_EXTERN
 // the pair tile with 16 epilogue warps, for short-K (store-bound) problems
 extern template cudaError_t launch_variant<KIND_F16, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
@@ -275,7 +275,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 
     if (p.in_dtype == SM120_DTYPE_FLOAT32) {
         // operands already split into tf32 pieces (see split_tf32.cu)
-        if (cg == 2) SM120_TC_CASE(KIND_TF32, 256, 5, 2, "tc_tf32x3_2cta_256x256x32_s5");
+        if (cg == 2) SM120_TC_CASE(KIND_TF32, 256, 6, 2, "tc_tf32x3_2cta_256x256x32_s6");
         if (bn == 256) SM120_TC_CASE(KIND_TF32, 256, 4, 1, "tc_tf32x3_128x256x32_s4");
         if (bn == 128) SM120_TC_CASE(KIND_TF32, 128, 6, 1, "tc_tf32x3_128x128x32_s6");
         SM120_TC_CASE(KIND_TF32, 64, 8, 1, "tc_tf32x3_128x64x32_s8");
@@ -285,7 +285,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
             if (kernel_name) *kernel_name = bf ? "tc_bf16_2cta_256x256x64_s5_e16" : "tc_f16_2cta_256x256x64_s5_e16";
             return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);
         }
-        if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 5, 2, bf ? "tc_bf16_2cta_256x256x64_s5" : "tc_f16_2cta_256x256x64_s5");
+        if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 6, 2, bf ? "tc_bf16_2cta_256x256x64_s6" : "tc_f16_2cta_256x256x64_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
         if (bn == 128) SM120_TC_CASE(KIND_F16, 128, 6, 1, bf ? "tc_bf16_128x128x64_s6" : "tc_f16_128x128x64_s6");
         SM120_TC_CASE(KIND_F16, 64, 8, 1, bf ? "tc_bf16_128x64x64_s8" : "tc_f16_128x64x64_s8");
@@ -294,7 +294,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
             if (kernel_name) *kernel_name = "tc_e4m3_2cta_256x256x128_s5_e16";
             return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);
         }
-        if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 5, 2, "tc_e4m3_2cta_256x256x128_s5");
+        if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 6, 2, "tc_e4m3_2cta_256x256x128_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, 1, "tc_e4m3_128x256x128_s4");
         if (bn == 128) SM120_TC_CASE(KIND_F8, 128, 6, 1, "tc_e4m3_128x128x128_s6");
         SM120_TC_CASE(KIND_F8, 64, 8, 1, "tc_e4m3_128x64x128_s8");
