@@ -40,10 +40,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised under profiles/ (None until captured).
 NCU_TRAFFIC_BYTES = {
-    "cfg2": 91042816,       # profiles/gemm_tcgen05_cfg2_fp16_4096.txt: 74.15 MB read + 16.89 MB written
-    "cfg2bf16": 91042816,   # same kernel, shape and byte counts as cfg2
-    "cfg3": 530652928,      # profiles/gemm_tcgen05_cfg3_bf16_dense_gelu.txt: 367.5 MB read + 163.1 MB written
-    "cfg4": 547926528,      # profiles/gemm_tcgen05_cfg4_bf16_batched.txt: 67.3 MB read + 480.7 MB written
+    "cfg2": 93319680,       # profiles/gemm_tcgen05_cfg2_fp16_4096.txt: 74.60 MB read + 18.72 MB written
+    "cfg2bf16": 93319680,   # same kernel, shape and byte counts as cfg2
+    "cfg3": 529810176,      # profiles/gemm_tcgen05_cfg3_bf16_dense_gelu.txt: 366.6 MB read + 163.2 MB written
+    "cfg4": 546989312,      # profiles/gemm_tcgen05_cfg4_bf16_batched.txt: 67.2 MB read + 479.8 MB written
 }
 
 
