@@ -27,6 +27,20 @@ CUDA_SUCCESS = 0
 CUDA_ERROR_INVALID_VALUE = 1
 QUANTIZE_FP8_STATIC_MAX_ELEMENTS = 268435456      # SM120_QUANTIZE_FP8_STATIC_MAX_ELEMENTS
 
+# SM120_TUNE_* bits of SM120GemmDesc.tuning (per-call overrides for tests and tuning runs)
+TUNE_CTA_GROUP_1, TUNE_CTA_GROUP_2, TUNE_EPI_WARPS_8, TUNE_EPI_WARPS_16 = 0x1, 0x2, 0x4, 0x8
+TUNE_NO_SPLIT_TAIL, TUNE_TRACE = 0x10, 0x20
+TRACE_WORDS_PER_CTA, TRACE_MAX_CTAS = 40, 160
+TRACE_BYTES = TRACE_MAX_CTAS * TRACE_WORDS_PER_CTA * 8
+
+
+def tune_group_m(g: int) -> int:
+    return (int(g) & 0xFF) << 8
+
+
+def tune_stall_kblock(kb: int) -> int:
+    return ((int(kb) + 1) & 0xFF) << 16
+
 
 class SM120GemmDesc(Structure):
     """Field-for-field image of ``struct SM120GemmDesc``."""
@@ -51,7 +65,7 @@ class SM120GemmDesc(Structure):
         ("activation", c_int32),
         ("path", c_int32),
         ("optimization_level", c_int32),
-        ("reserved", c_int32),
+        ("tuning", c_int32),
         ("stream", c_void_p),
         ("workspace", c_void_p),
         ("workspace_bytes", c_uint64),
@@ -78,6 +92,8 @@ EXPORTS = {
     "sm120_is_supported": (c_bool, [c_int]),
     "sm120_get_error_string": (c_char_p, [c_int]),
     "sm120_get_kernel_status": (c_int, [c_int, POINTER(c_uint), c_int]),
+    "sm120_get_kernel_clock": (c_int, [c_int, POINTER(ctypes.c_ulonglong), POINTER(ctypes.c_ulonglong)]),
+    "sm120_get_tensor_map_stats": (None, [POINTER(c_uint64), POINTER(c_uint64)]),
     "sm120_set_wait_limit_ms": (None, [c_uint]),
     "sm120_get_launch_count": (c_uint64, []),
     "sm120_get_last_kernel_name": (c_char_p, []),
@@ -104,13 +120,6 @@ def load_library() -> ctypes.CDLL:
             fn = getattr(lib, name)   # AttributeError if the symbol is not exported
             fn.restype = restype
             fn.argtypes = argtypes
-        # test hook, not part of the public header
-        lib.sm120_debug_skip_kblock.restype = None
-        lib.sm120_debug_skip_kblock.argtypes = [c_int]
-        lib.sm120_debug_force_cta_group.restype = None
-        lib.sm120_debug_force_cta_group.argtypes = [c_int]
-        lib.sm120_debug_force_epi_warps.restype = None
-        lib.sm120_debug_force_epi_warps.argtypes = [c_int]
     except Exception as e:  # remember and re-raise on every later call
         _load_error = e
         raise
@@ -144,3 +153,19 @@ def last_kernel_name() -> str:
 
 def launch_count() -> int:
     return int(load_library().sm120_get_launch_count())
+
+
+def kernel_clock_mhz(device_index: int):
+    """SM clock (MHz) seen from inside the last tensor-core launch on the device, or None."""
+    cyc, ns = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+    rc = load_library().sm120_get_kernel_clock(int(device_index), ctypes.byref(cyc), ctypes.byref(ns))
+    if rc != CUDA_SUCCESS or ns.value == 0:
+        return None
+    return 1e3 * cyc.value / ns.value
+
+
+def tensor_map_stats():
+    """(maps encoded through the driver, launches' maps taken from a thread's cache) since load."""
+    enc, hit = c_uint64(0), c_uint64(0)
+    load_library().sm120_get_tensor_map_stats(ctypes.byref(enc), ctypes.byref(hit))
+    return int(enc.value), int(hit.value)

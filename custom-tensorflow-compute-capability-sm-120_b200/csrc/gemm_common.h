@@ -39,6 +39,8 @@ struct GemmProblem {
     // other GPUs' memory when the launch also does the all-gather of an M-sharded product
     void* extra_dests[7];
     int num_extra_dests;
+    int tuning;                      // SM120GemmDesc::tuning (SM120_TUNE_* bits)
+    void* trace;                     // null, or the caller's buffer for SM120_TUNE_TRACE
 };
 
 __host__ __device__ inline int dtype_size(int dtype) {
@@ -65,6 +67,10 @@ cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_l
 
 // Per-device status word of the tcgen05 kernel (0 = no wait ran out).
 cudaError_t tc_read_status(unsigned int* status, int clear);
+// SM cycles and nanoseconds that CTA 0 of the last tcgen05 launch on the current device was alive.
+cudaError_t tc_read_probe(unsigned long long* cycles_ns);
+// How many tensor maps this process has encoded / taken from a thread's cache so far.
+void tc_map_cache_stats(uint64_t* encodes, uint64_t* hits);
 
 // ---------------------------------------------------------------------------
 // Epilogue math, shared by both kernel families.  Formulas and constants follow

@@ -9,6 +9,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 #include <atomic>
 
 #include "gemm_tcgen05_kernel.cuh"
@@ -17,28 +18,21 @@ namespace sm120 {
 
 // Status and probe words of the kernel (see gemm_tcgen05_kernel.cuh), one set per device.
 __device__ unsigned int g_sm120_status[4];
-#ifdef SM120_EPI_TRACE
-__device__ unsigned long long g_sm120_probe[2 + 256];
-extern "C" int sm120_debug_read_trace(unsigned long long* out) {
-    return static_cast<int>(cudaMemcpyFromSymbol(out, g_sm120_probe, (2 + 256) * sizeof(unsigned long long)));
-}
-#else
 __device__ unsigned long long g_sm120_probe[2];
-#endif
 
 // the variants are compiled in gemm_tcgen05_inst_*.cu
 #define SM120_TC_EXTERN(KIND_, BN_, ST_, CG_) \
     extern template cudaError_t launch_variant<KIND_, BN_, ST_, CG_>(const CUtensorMap&, const CUtensorMap&, const DestMaps&, \
-                                                                     const TcParams&, int, int, cudaStream_t);
+                                                                     const TcParams&, int, int, cudaStream_t, bool);
 SM120_TC_EXTERN(KIND_F16, 256, 6, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
 SM120_TC_EXTERN(KIND_F8, 256, 6, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
 SM120_TC_EXTERN(KIND_TF32, 256, 6, 2) SM120_TC_EXTERN(KIND_TF32, 256, 4, 1) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
 #undef SM120_TC_EXTERN
 // the pair tile with 16 epilogue warps, for short-K (store-bound) problems
 extern template cudaError_t launch_variant<KIND_F16, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                                    const TcParams&, int, int, cudaStream_t);
+                                                                    const TcParams&, int, int, cudaStream_t, bool);
 extern template cudaError_t launch_variant<KIND_F8, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                                   const TcParams&, int, int, cudaStream_t);
+                                                                   const TcParams&, int, int, cudaStream_t, bool);
 
 // ---------------------------------------------------------------------------
 // Host side
@@ -71,21 +65,73 @@ static CUtensorMapDataType tmap_dtype(int dtype) {
     }
 }
 
+// Tensor maps are pure functions of (address, type, extents, pitches, box, swizzle), and a
+// framework calls the op again and again on the same buffers and shapes, so each host thread
+// keeps the maps it encoded: a direct-mapped table, thread-local and therefore free of locks
+// and safe under any number of concurrent callers.  A hit costs one hash and one 64-byte
+// compare instead of a driver call.
+struct MapKey {
+    uint64_t ptr, inner, outer, nbatch, pitch_bytes, bstride_bytes;
+    uint32_t box_inner, box_outer, dtype, swizzle;
+};
+static_assert(sizeof(MapKey) == 64, "MapKey must have no padding: it is compared with memcmp");
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int MAP_CACHE_SLOTS = 256;
+static thread_local MapSlot t_map_cache[MAP_CACHE_SLOTS];
+static std::atomic<uint64_t> g_map_encodes{0}, g_map_hits{0};
+
+void tc_map_cache_stats(uint64_t* encodes, uint64_t* hits) {
+    *encodes = g_map_encodes.load(std::memory_order_relaxed);
+    *hits = g_map_hits.load(std::memory_order_relaxed);
+}
+
+static uint32_t map_key_hash(const MapKey& k) {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    for (int i = 0; i < 8; ++i) {
+        h ^= w[i];
+        h *= 0xFF51AFD7ED558CCDull;
+        h ^= h >> 29;
+    }
+    return static_cast<uint32_t>(h);
+}
+
 // 3-D map over a stored matrix: `inner` contiguous elements per row, `outer`
 // rows `pitch` elements apart, `nbatch` matrices `bstride` elements apart.
 static bool encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch,
                       int64_t pitch, int64_t bstride, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+    const uint64_t es = static_cast<uint64_t>(dtype_size(dtype));
+    MapKey key{};
+    key.ptr = reinterpret_cast<uint64_t>(ptr);
+    key.inner = static_cast<uint64_t>(inner); key.outer = static_cast<uint64_t>(outer); key.nbatch = static_cast<uint64_t>(nbatch);
+    key.pitch_bytes = static_cast<uint64_t>(pitch) * es; key.bstride_bytes = static_cast<uint64_t>(bstride) * es;
+    key.box_inner = box_inner; key.box_outer = box_outer;
+    key.dtype = static_cast<uint32_t>(dtype); key.swizzle = static_cast<uint32_t>(swizzle);
+    MapSlot& slot = t_map_cache[map_key_hash(key) & (MAP_CACHE_SLOTS - 1)];
+    if (slot.used && memcmp(&slot.key, &key, sizeof(key)) == 0) {
+        *map = slot.map;
+        g_map_hits.fetch_add(1, std::memory_order_relaxed);
+        return true;
+    }
     EncodeTiledFn fn = get_encode_fn();
     if (fn == nullptr) return false;
-    const uint64_t es = static_cast<uint64_t>(dtype_size(dtype));
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), static_cast<cuuint64_t>(nbatch)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch) * es, static_cast<cuuint64_t>(bstride) * es};
+    cuuint64_t dims[3] = {key.inner, key.outer, key.nbatch};
+    cuuint64_t strides[2] = {key.pitch_bytes, key.bstride_bytes};
     cuuint32_t box[3] = {box_inner, box_outer, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, tmap_dtype(dtype), 3, const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    if (r != CUDA_SUCCESS) return false;
+    g_map_encodes.fetch_add(1, std::memory_order_relaxed);
+    slot.key = key;
+    slot.map = *map;
+    slot.used = true;
+    return true;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -112,18 +158,6 @@ bool tc_supported(const GemmProblem& p, const char** why) {
     return true;
 }
 
-static std::atomic<int> g_debug_skip_kblock{-1};
-void tc_set_debug_skip_kblock(int kb) { g_debug_skip_kblock.store(kb); }
-static std::atomic<int> g_debug_mode{0};
-void tc_set_debug_mode(int m) { g_debug_mode.store(m); }
-static std::atomic<int> g_split_tail{1};           // 0 switches the half-width tail tiles off (tuning)
-void tc_set_split_tail(int on) { g_split_tail.store(on); }
-bool tc_split_tail_enabled() { return g_split_tail.load() != 0; }
-static std::atomic<int> g_force_cta_group{0};     // 0 = choose, 1 / 2 = force (tests and tuning)
-void tc_set_force_cta_group(int cg) { g_force_cta_group.store(cg); }
-static std::atomic<int> g_force_epi_warps{0};     // 0 = choose, 8 / 16 = force where the variant exists (tests and tuning)
-void tc_set_force_epi_warps(int ew) { g_force_epi_warps.store(ew); }
-
 cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char** kernel_name) {
     const int es = dtype_size(p.in_dtype);
     const int epb = 128 / es;
@@ -142,7 +176,8 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     const int min_bn = (b_mn && es == 1) ? 128 : 64;
     auto tiles_for = [&](int bm, int bn) { return ((p.M + bm - 1) / bm) * ((p.N + bn - 1) / bn) * p.batch; };
     int cg = 1, bn = min_bn;
-    const int force = g_force_cta_group.load();
+    // per-call overrides (SM120GemmDesc::tuning): 0 = choose, 1 / 2 = force
+    const int force = (p.tuning & SM120_TUNE_CTA_GROUP_2) ? 2 : ((p.tuning & SM120_TUNE_CTA_GROUP_1) ? 1 : 0);
     if (p.optimization_level == 0) {
         bn = p.N > 64 ? 128 : min_bn;
     } else {
@@ -171,7 +206,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
                            p.activation != SM120_ACTIVATION_LEAKY_RELU;
     int ew = (cg == 2 && p.in_dtype != SM120_DTYPE_FLOAT32 && (tp.k_blocks <= 8 || heavy_act)) ? 16 : 8;
     {
-        const int fe = g_force_epi_warps.load();
+        const int fe = (p.tuning & SM120_TUNE_EPI_WARPS_16) ? 16 : ((p.tuning & SM120_TUNE_EPI_WARPS_8) ? 8 : 0);
         if (fe == 8 || (fe == 16 && cg == 2 && p.in_dtype != SM120_DTYPE_FLOAT32)) ew = fe;
     }
     tp.num_tiles = static_cast<int>(tiles_for(BM * cg, bn));
@@ -182,6 +217,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         const long long slice = static_cast<long long>(BM * cg) * p.K * es;
         long long gm = (40ll << 20) / (slice > 0 ? slice : 1);
         gm = gm < 4 ? 4 : (gm > 64 ? 64 : gm);
+        if (((p.tuning >> 8) & 0xFF) != 0) gm = (p.tuning >> 8) & 0xFF;
         tp.group_m = static_cast<int>(gm < tp.tiles_m ? gm : tp.tiles_m);
     }
     tp.div_per_batch = make_fast_div(static_cast<uint32_t>(tp.tiles_m) * static_cast<uint32_t>(tp.tiles_n));
@@ -203,9 +239,10 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.alpha = p.alpha * p.inv_scale; tp.beta = p.beta;
     tp.scale_a_dev = p.scale_a_dev; tp.scale_b_dev = p.scale_b_dev;
     tp.activation = p.activation;
-    tp.debug_skip_kblock = g_debug_skip_kblock.load();
-    tp.debug_mode = g_debug_mode.load();
+    tp.stall_kblock = ((p.tuning >> 16) & 0xFF) - 1;
+    tp.trace = static_cast<unsigned long long*>(p.trace);
     tp.wait_limit_ns = wait_limit_ns;
+    const bool split_tail = (p.tuning & SM120_TUNE_NO_SPLIT_TAIL) == 0;
     {
         // device addresses of this device's status / probe words (looked up once per device)
         static std::atomic<unsigned int*> status_addr[64];
@@ -275,7 +312,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 #define SM120_TC_CASE(KIND_, BN_, ST_, CG_, NAME_)                                                       \
     do {                                                                                                 \
         if (kernel_name) *kernel_name = NAME_;                                                           \
-        return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);       \
+        return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tc, tp, p.sm_count, p.device, p.stream, split_tail);       \
     } while (0)
 
     if (p.in_dtype == SM120_DTYPE_FLOAT32) {
@@ -288,7 +325,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
         if (cg == 2 && ew == 16) {
             if (kernel_name) *kernel_name = bf ? "tc_bf16_2cta_256x256x64_s5_e16" : "tc_f16_2cta_256x256x64_s5_e16";
-            return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);
+            return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream, split_tail);
         }
         if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 6, 2, bf ? "tc_bf16_2cta_256x256x64_s6" : "tc_f16_2cta_256x256x64_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
@@ -297,7 +334,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     } else {
         if (cg == 2 && ew == 16) {
             if (kernel_name) *kernel_name = "tc_e4m3_2cta_256x256x128_s5_e16";
-            return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream);
+            return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream, split_tail);
         }
         if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 6, 2, "tc_e4m3_2cta_256x256x128_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, 1, "tc_e4m3_128x256x128_s4");

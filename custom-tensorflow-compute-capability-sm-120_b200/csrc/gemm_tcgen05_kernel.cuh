@@ -78,13 +78,11 @@ constexpr int MAX_DESTS = 8;
 // launch also performs the all-gather of an M-sharded product).
 struct DestMaps { CUtensorMap m[MAX_DESTS]; };
 
-// Tuning aid, compiled out unless SM120_EPI_TRACE is defined: CTA 0 records SM clock
-// values of its first 16 tiles (16 slots per tile) after the two probe words.
-#ifdef SM120_EPI_TRACE
-#define SM120_TRACE(cond, local, slot) do { if ((cond) && blockIdx.x == 0 && (local) < 16) p.probe[2 + (local) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define SM120_TRACE(cond, local, slot) do {} while (0)
-#endif
+// Optional timeline of a launch (TcParams::trace, null in normal launches): every CTA owns
+// TRACE_WORDS 64-bit words of a caller-provided buffer; the layout is documented with
+// SM120_TUNE_TRACE in the public header.
+constexpr int TRACE_WORDS = SM120_TRACE_WORDS_PER_CTA;
+constexpr int TRACE_TILES = 8;
 
 // Division by a value fixed at launch: q = (umulhi(n, mul) + n) >> shift for 0 <= n < 2^31.
 struct FastDiv {
@@ -132,11 +130,11 @@ struct TcParams {
     const float* scale_a_dev;
     const float* scale_b_dev;
     int activation;
-    int debug_skip_kblock;          // >= 0: the producer never fills this k-block of its first tile (wait-limit test)
-    int debug_mode;                 // timing experiments only (results are garbage): 1 = no MMA issue, 2 = no TMA loads
+    int stall_kblock;               // >= 0: the producer never fills this k-block of its first tile (self-test of the bounded waits)
     unsigned long long wait_limit_ns;
     unsigned int* status;           // device array of 4 words, see above
     unsigned long long* probe;      // device array of 2 words, see above
+    unsigned long long* trace;      // null, or the caller's timeline buffer (see TRACE_WORDS)
 };
 
 // ---------------------------------------------------------------------------
@@ -841,12 +839,12 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
         BiasRaw braw;
         if (has_bias && nvalid > 0) bias_prefetch32(p, colbase, braw);
 
-        SM120_TRACE(warp == 2 && lane == 0, local, 0);
         bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
         tcgen05_fence_after();
-        SM120_TRACE(warp == 2 && lane == 0, local, 1);
+        if (p.trace != nullptr && warp == 2 && lane == 0 && local < TRACE_TILES)
+            p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 2] = clock64();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * cols_per_warp;
 
         uint32_t acc[MODP][32];
@@ -875,7 +873,6 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
                 } else if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
 #pragma unroll
                     for (int q = 0; q < PRE; ++q) tmem_ld_wait_regs(acc[q]);
-                    SM120_TRACE(warp == 2 && lane == 0 && c == 0, local, 2);
                     if (c + PRE >= nvalid) {                // nothing more to load: hand the TMEM buffer back
                         tcgen05_fence_before();
                         __syncwarp();
@@ -935,7 +932,8 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
                 }
             }
         }
-        SM120_TRACE(warp == 2 && lane == 0, local, 3);
+        if (p.trace != nullptr && warp == 2 && lane == 0 && local < TRACE_TILES)
+            p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 3] = clock64();
     }
     if (lane == 0) {
         bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
@@ -1016,6 +1014,14 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // the wait.  The next kernel of the stream may start its own set-up as soon as SMs free up.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (p.trace != nullptr && threadIdx.x == 0) {
+        unsigned long long* t = p.trace + static_cast<size_t>(blockIdx.x) * TRACE_WORDS;
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        t[0] = probe_t0; t[1] = static_cast<unsigned long long>(probe_c0);
+        t[2] = global_timer_ns(); t[3] = static_cast<unsigned long long>(clock64());
+        t[7] = smid;
+    }
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -1036,34 +1042,30 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // box of BN_CTA rows of B; the MMA reads only the first width / CG of them)
             const int n0 = nt + static_cast<int>(cta_rank) * (width / CG);
             for (int kb = 0; kb < p.k_blocks; ++kb) {
-                if (first && kb == p.debug_skip_kblock) { ok = false; break; }
+                if (first && kb == p.stall_kblock) { ok = false; break; }
                 bool w = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u);
                 w = __all_sync(0xFFFFFFFFu, w);
                 if (!w) { ok = false; break; }
                 if (elect_one_sync()) {
-                    if (p.debug_mode == 2) {
-                        if (leader) mbar_arrive(full_bar + 8 * stage);
+                    // transaction bytes of the whole pair are expected on the leader's barrier
+                    if (leader) mbar_expect_tx(full_bar + 8 * stage, STAGE_BYTES * CG);
+                    const uint32_t fb = full_for_tma + 8 * stage;
+                    const uint32_t a_dst = smem_u32(smem) + stage * STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_BYTES;
+                    const int k0 = kb * BK;
+                    if (!p.a_mn_major) {
+                        tma_load_3d<CG>(a_dst, &tmap_a, fb, k0, m0, za);
                     } else {
-                        // transaction bytes of the whole pair are expected on the leader's barrier
-                        if (leader) mbar_expect_tx(full_bar + 8 * stage, STAGE_BYTES * CG);
-                        const uint32_t fb = full_for_tma + 8 * stage;
-                        const uint32_t a_dst = smem_u32(smem) + stage * STAGE_BYTES;
-                        const uint32_t b_dst = a_dst + A_BYTES;
-                        const int k0 = kb * BK;
-                        if (!p.a_mn_major) {
-                            tma_load_3d<CG>(a_dst, &tmap_a, fb, k0, m0, za);
-                        } else {
 #pragma unroll
-                            for (int j = 0; j < BM / EPB; ++j)
-                                tma_load_3d<CG>(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, m0 + j * EPB, k0, za);
-                        }
-                        if (!p.b_mn_major) {
-                            tma_load_3d<CG>(b_dst, &tmap_b, fb, k0, n0, zb);
-                        } else {
+                        for (int j = 0; j < BM / EPB; ++j)
+                            tma_load_3d<CG>(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, m0 + j * EPB, k0, za);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_3d<CG>(b_dst, &tmap_b, fb, k0, n0, zb);
+                    } else {
 #pragma unroll
-                            for (int j = 0; j < BN_CTA / EPB; ++j)
-                                tma_load_3d<CG>(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, n0 + j * EPB, k0, zb);
-                        }
+                        for (int j = 0; j < BN_CTA / EPB; ++j)
+                            tma_load_3d<CG>(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, n0 + j * EPB, k0, zb);
                     }
                 }
                 __syncwarp();
@@ -1103,53 +1105,43 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const uint32_t idesc = tile < p.full_work ? p.idesc : p.idesc_half;
                 const uint32_t buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
-                SM120_TRACE(lane == 0, local, 8);
                 bool w = mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u);
                 w = __all_sync(0xFFFFFFFFu, w);
                 if (!w) { ok = false; break; }
                 tcgen05_fence_after();
-                SM120_TRACE(lane == 0, local, 9);
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     w = mbar_wait(full_bar + 8 * stage, phase, wctx, 0x22000000u);
                     w = __all_sync(0xFFFFFFFFu, w);
                     if (!w) { ok = false; break; }
                     tcgen05_fence_after();
-                    SM120_TRACE(lane == 0 && kb == 0, local, 10);
+                    if (p.trace != nullptr && kb == 0 && lane == 0 && local < TRACE_TILES)
+                        p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local] = clock64();
                     const uint32_t soff = stage * (STAGE_BYTES >> 4);
                     if (elect_one_sync()) {
-                        if (p.debug_mode == 1) {
-                            mbar_arrive(empty_bar + 8 * stage);
-                            if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(empty_bar + 8 * stage, 1u));
-                        } else {
 #pragma unroll
-                            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                                const uint64_t a_desc = desc_hi | (a_lo0 + soff + kk * a_kstep);
-                                const uint64_t b_desc = desc_hi | (b_lo0 + soff + kk * b_kstep);
-                                umma_ss<KIND, CG>(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
-                            }
-                            // free the stage, in both CTAs of a pair, when these MMAs retire
-                            umma_commit<CG>(empty_bar + 8 * stage);
-                            if constexpr (CG == 2) umma_commit<CG>(map_to_cta(empty_bar + 8 * stage, 1u));
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            const uint64_t a_desc = desc_hi | (a_lo0 + soff + kk * a_kstep);
+                            const uint64_t b_desc = desc_hi | (b_lo0 + soff + kk * b_kstep);
+                            umma_ss<KIND, CG>(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
                         }
+                        // free the stage, in both CTAs of a pair, when these MMAs retire
+                        umma_commit<CG>(empty_bar + 8 * stage);
+                        if constexpr (CG == 2) umma_commit<CG>(map_to_cta(empty_bar + 8 * stage, 1u));
                     }
                     __syncwarp();
                     issued_any = true;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok && elect_one_sync()) {
-                    if (p.debug_mode == 1) {
-                        mbar_arrive(acc_full_bar + 8 * buf);
-                        if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(acc_full_bar + 8 * buf, 1u));
-                    } else {                                // accumulator complete, in both CTAs of a pair
-                        umma_commit<CG>(acc_full_bar + 8 * buf);
-                        if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
-                    }
+                if (ok && elect_one_sync()) {               // accumulator complete, in both CTAs of a pair
+                    umma_commit<CG>(acc_full_bar + 8 * buf);
+                    if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
                 }
                 __syncwarp();
-                SM120_TRACE(lane == 0, local, 11);
+                if (p.trace != nullptr && lane == 0 && local < TRACE_TILES)
+                    p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 1] = clock64();
             }
-            if (*abort_flag != 0u && issued_any && p.debug_mode != 1) {
+            if (*abort_flag != 0u && issued_any) {
                 if (elect_one_sync()) umma_commit<CG>(drain_bar);
                 __syncwarp();
                 mbar_wait(drain_bar, 0u, wctx, 0x23000000u, false);
@@ -1193,6 +1185,13 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         p.probe[0] = static_cast<unsigned long long>(clock64() - probe_c0);
         p.probe[1] = global_timer_ns() - probe_t0;
     }
+    if (p.trace != nullptr && threadIdx.x == 0) {
+        unsigned long long* t = p.trace + static_cast<size_t>(blockIdx.x) * TRACE_WORDS;
+        int mine = 0;
+        for (int tile = first_tile; tile < p.num_work; tile += tile_step) ++mine;
+        t[4] = global_timer_ns(); t[5] = static_cast<unsigned long long>(clock64());
+        t[6] = static_cast<unsigned long long>(mine);
+    }
 }
 
 
@@ -1201,11 +1200,9 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // own translation unit (gemm_tcgen05_inst_*.cu) so that the variants compile in
 // parallel; gemm_tcgen05.cu only declares them.
 // ---------------------------------------------------------------------------
-bool tc_split_tail_enabled();
-
 template <int KIND, int BN, int STAGES, int CG, int EW = 8>
 cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DestMaps& tc, const TcParams& tp,
-                                  int sm_count, int device, cudaStream_t stream) {
+                                  int sm_count, int device, cudaStream_t stream, bool split_tail) {
     using Cfg = TileCfg<KIND, BN, STAGES, CG, EW>;
     static std::atomic<uint64_t> attr_done{0};     // one bit per device
     static std::atomic<int> max_clusters[64];      // CG == 2: co-resident clusters per device (0 = not asked yet)
@@ -1247,7 +1244,7 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const D
         TcParams t = tp;
         const int rest = tp.num_tiles % clusters;
         // (not with 16 epilogue warps: a warp's quarter of a half-width tile is narrower than its 64-column store)
-        if (EW == 8 && tp.num_tiles > clusters && rest > 0 && 2 * rest <= clusters && tc_split_tail_enabled() != 0) {
+        if (EW == 8 && tp.num_tiles > clusters && rest > 0 && 2 * rest <= clusters && split_tail) {
             t.full_work = tp.num_tiles - rest;
             t.num_work = t.full_work + 2 * rest;
         }

@@ -3,9 +3,10 @@
 // Mirrors the role of src/cuda_kernels/sm120_c_interface.cu:32-60 in the
 // reference (grid choice + dtype dispatch + cudaGetLastError()).
 //
-// The launchers hold no mutable global state except monotonic counters and
-// per-device caches of immutable device attributes, so they may be called
-// concurrently from any number of host threads.
+// The launchers hold no mutable global state except monotonic counters,
+// per-device caches of immutable device attributes and each thread's own cache
+// of tensor maps, so they may be called concurrently from any number of host
+// threads; everything that varies per call travels in the descriptor.
 
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -20,13 +21,6 @@ namespace sm120 {
 long long quant_spans(long long n);
 cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, long long n, float* partial, cudaStream_t stream);
 cudaError_t quant_launch_static(const void* x, int x_dtype, void* q, float* scale_out, long long n, int device, cudaStream_t stream);
-void tc_set_debug_skip_kblock(int kb);
-void tc_set_force_cta_group(int cg);
-void tc_set_force_epi_warps(int ew);
-void tc_set_force_epi_warps(int ew);
-void tc_set_debug_mode(int m);
-void tc_set_split_tail(int on);
-cudaError_t tc_read_probe(unsigned long long* cycles_ns);
 
 namespace {
 
@@ -94,6 +88,14 @@ cudaError_t resolve(const SM120GemmDesc* d, GemmProblem* out) {
             return cudaErrorInvalidValue;
     }
     if (d->scale_a < 0.0f || d->scale_b < 0.0f) return cudaErrorInvalidValue;
+    if ((d->tuning & ~0x00FFFF3F) != 0) return cudaErrorInvalidValue;
+    if ((d->tuning & SM120_TUNE_CTA_GROUP_1) && (d->tuning & SM120_TUNE_CTA_GROUP_2)) return cudaErrorInvalidValue;
+    if ((d->tuning & SM120_TUNE_EPI_WARPS_8) && (d->tuning & SM120_TUNE_EPI_WARPS_16)) return cudaErrorInvalidValue;
+    if (d->tuning & SM120_TUNE_TRACE) {
+        if (d->workspace == nullptr || (reinterpret_cast<uintptr_t>(d->workspace) & 7u) != 0 || d->workspace_bytes < SM120_TRACE_BYTES)
+            return cudaErrorInvalidValue;
+        if (d->in_dtype == SM120_DTYPE_FLOAT32 && d->path == SM120_PATH_TENSOR_CORE) return cudaErrorInvalidValue;
+    }
 
     GemmProblem p{};
     p.M = d->M; p.N = d->N; p.K = d->K; p.batch = d->batch;
@@ -128,6 +130,8 @@ cudaError_t resolve(const SM120GemmDesc* d, GemmProblem* out) {
     p.scale_a_dev = d->scale_a_dev; p.scale_b_dev = d->scale_b_dev;
     p.activation = d->activation;
     p.optimization_level = d->optimization_level;
+    p.tuning = d->tuning;
+    p.trace = (d->tuning & SM120_TUNE_TRACE) ? d->workspace : nullptr;
     p.stream = d->stream;
     *out = p;
     return cudaSuccess;
@@ -409,28 +413,28 @@ uint64_t sm120_get_launch_count(void) { return g_launch_count.load(std::memory_o
 
 const char* sm120_get_last_kernel_name(void) { return t_last_kernel; }
 
-// Test hook, not declared in the public header: the TMA producer of every CTA
-// stops before filling k-block `kb` of its first tile, so the consumer's bounded
-// wait runs out and the status word is set.  kb < 0 switches the hook off.
-void sm120_debug_skip_kblock(int kb) { tc_set_debug_skip_kblock(kb); }
+cudaError_t sm120_get_kernel_clock(int device_id, unsigned long long* cycles, unsigned long long* ns) {
+    if (cycles == nullptr || ns == nullptr) return cudaErrorInvalidValue;
+    int prev = 0;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev != device_id) {
+        e = cudaSetDevice(device_id);
+        if (e != cudaSuccess) return e;
+    }
+    unsigned long long both[2] = {0, 0};
+    e = tc_read_probe(both);
+    if (prev != device_id) cudaSetDevice(prev);
+    *cycles = both[0];
+    *ns = both[1];
+    return e;
+}
 
-// Tuning/test hook, not declared in the public header: 1 or 2 forces the
-// single-CTA or the CTA-pair flavour of the tensor-core kernel, 0 restores the
-// launcher's own choice.
-void sm120_debug_force_cta_group(int cg) { tc_set_force_cta_group(cg); }
-void sm120_debug_force_epi_warps(int ew) { tc_set_force_epi_warps(ew); }
-
-// Timing-experiment hook, not declared in the public header: 1 = the MMA role
-// issues no tcgen05.mma, 2 = the producer issues no TMA loads (results are
-// garbage in both), 0 = normal.
-void sm120_debug_mode(int m) { tc_set_debug_mode(m); }
-
-// Tuning hook, not declared in the public header: 0 switches off the half-width
-// tiles that the CTA-pair kernel uses for a short final wave, 1 (default) on.
-void sm120_debug_split_tail(int on) { tc_set_split_tail(on); }
-
-// Tuning hook, not declared in the public header: SM cycles and nanoseconds that
-// CTA 0 of the last tensor-core launch on the current device was alive.
-int sm120_debug_read_probe(unsigned long long* cycles_ns) { return static_cast<int>(tc_read_probe(cycles_ns)); }
+void sm120_get_tensor_map_stats(uint64_t* encoded, uint64_t* reused) {
+    uint64_t e = 0, h = 0;
+    tc_map_cache_stats(&e, &h);
+    if (encoded != nullptr) *encoded = e;
+    if (reused != nullptr) *reused = h;
+}
 
 }  // extern "C"

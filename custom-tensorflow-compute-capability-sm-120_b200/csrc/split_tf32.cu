@@ -11,8 +11,10 @@
 // with Kp = K rounded up to 32 and zero padding, accumulated in fp32 in TMEM by
 // the same kernel as the 16-bit types.  The split kernels below write A3 and B3
 // into caller-provided workspace, handling the caller's transposes and pitches,
-// so the GEMM always sees two K-major operands.  Measured relative Frobenius
-// error against float64 stays near 3e-7 (gate: 1e-5).
+// so the GEMM always sees two K-major operands.  The tensor cores truncate when
+// they add into the fp32 accumulator, so the relative Frobenius error against
+// float64 grows with K, about K * 2^-27: 1.16e-5 measured at K = 1024, outside
+// the op's 1e-5 gate, which is why this path is opt-in.
 //
 // This is the tensor-core answer to the reference's fp32 kernels
 // (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:46-101,
@@ -87,6 +89,17 @@ cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_l
     if (nb_a > 65535 || nb_b > 65535 || (p.M + 31) / 32 > 65535 || (p.N + 31) / 32 > 65535) return cudaErrorInvalidValue;
     float* a3 = static_cast<float*>(workspace);
     float* b3 = a3 + p.M * nb_a * 3 * kp;
+    // the GEMM over the split operands; checked before anything is enqueued, so a rejected call launches nothing
+    GemmProblem g = p;
+    g.A = a3; g.B = b3;
+    g.K = 3 * kp;
+    g.lda = 3 * kp; g.ldb = 3 * kp;
+    g.transpose_a = 0; g.transpose_b = 1;
+    g.stride_a = (nb_a > 1) ? p.M * 3 * kp : 0;
+    g.stride_b = (nb_b > 1) ? p.N * 3 * kp : 0;
+    g.tf32_operands = 1;
+    const char* why = nullptr;
+    if (!tc_supported(g, &why)) return cudaErrorInvalidValue;
     const dim3 block(256);
     const dim3 grid_a(static_cast<unsigned>(kp / 32), static_cast<unsigned>((p.M + 31) / 32), static_cast<unsigned>(nb_a));
     const dim3 grid_b(static_cast<unsigned>(kp / 32), static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(nb_b));
@@ -98,16 +111,6 @@ cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_l
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
 
-    GemmProblem g = p;
-    g.A = a3; g.B = b3;
-    g.K = 3 * kp;
-    g.lda = 3 * kp; g.ldb = 3 * kp;
-    g.transpose_a = 0; g.transpose_b = 1;
-    g.stride_a = (nb_a > 1) ? p.M * 3 * kp : 0;
-    g.stride_b = (nb_b > 1) ? p.N * 3 * kp : 0;
-    g.tf32_operands = 1;
-    const char* why = nullptr;
-    if (!tc_supported(g, &why)) return cudaErrorInvalidValue;
     return tc_launch(g, wait_limit_ns, kernel_name);
 }
 

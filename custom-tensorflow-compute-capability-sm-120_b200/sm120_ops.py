@@ -218,6 +218,8 @@ def fused_matmul(
     optimization_level: Optional[int] = None,
     fp32_tensor_cores: bool = False,
     peer_outs: Optional[Sequence[torch.Tensor]] = None,
+    tuning: int = 0,
+    trace: Optional[torch.Tensor] = None,
 ):
     """out = act(alpha / (scale_a * scale_b) * op(a) @ op(b) + beta * out + bias).
 
@@ -237,6 +239,11 @@ def fused_matmul(
     addresses (other GPUs' memory opened through CUDA IPC), that receive the same
     result as ``out`` from the same launch (``sm120_launch_matmul_gather``); they use
     ``out``'s shape, dtype and strides.
+
+    ``tuning`` passes ``SM120_TUNE_*`` bits (``_binding.TUNE_*``) to this one launch;
+    ``trace`` is a CUDA int64 tensor of at least ``_binding.TRACE_BYTES // 8`` words
+    that receives the launch's timeline (``SM120_TUNE_TRACE``).  Both are for tests
+    and tuning runs.
 
     Inputs on the host (numpy arrays or CPU tensors) are copied to the current
     CUDA device, and the result is copied back and returned in the same form;
@@ -363,6 +370,13 @@ def fused_matmul(
         raise ValueError("Optimization level must be 0, 1, or 2")
     d.optimization_level = int(optimization_level)
     d.path = _b.PATH_AUTO if use_tensor_cores else _b.PATH_SIMT
+    d.tuning = int(tuning)
+    if trace is not None:
+        if not (trace.is_cuda and trace.dtype == torch.int64 and trace.is_contiguous() and trace.numel() * 8 >= _b.TRACE_BYTES):
+            raise ValueError(f"trace must be a contiguous CUDA int64 tensor of at least {_b.TRACE_BYTES // 8} words")
+        keep.append(trace)
+        d.tuning |= _b.TUNE_TRACE
+        d.workspace, d.workspace_bytes = trace.data_ptr(), trace.numel() * 8
     d.stream = torch.cuda.current_stream(a.device).cuda_stream
     if fp32_tensor_cores and a.dtype == torch.float32 and K >= 1:
         # opt-in 3xTF32: scratch for the split operands comes from the caller's allocator (torch),

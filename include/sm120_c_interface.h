@@ -144,11 +144,49 @@ typedef struct SM120GemmDesc {
     int32_t activation;        /* SM120ActivationType */
     int32_t path;              /* SM120KernelPath */
     int32_t optimization_level;/* 0..2 as SM120Config.optimization_level (python/sm120_ops.py:108-122); 0 = conservative tile, 1/2 = tuned */
-    int32_t reserved;
+    int32_t tuning;            /* SM120_TUNE_* bits, 0 = every choice is the launcher's (see below) */
     cudaStream_t stream;
     void*    workspace;        /* optional device scratch owned by the caller (16-byte aligned), or null */
-    uint64_t workspace_bytes;  /* its size; see sm120_matmul_workspace_bytes */
+    uint64_t workspace_bytes;  /* its size; see sm120_matmul_workspace_bytes and SM120_TUNE_TRACE */
 } SM120GemmDesc;
+
+/*
+ * Per-call overrides of the tensor-core launcher's own choices, for tests and
+ * tuning runs.  They live in the descriptor, not in the library, so one thread's
+ * experiment never changes another thread's launch.  0 asks for nothing.  An
+ * override that the chosen kernel has no variant for is ignored.
+ *   CTA_GROUP_1 / _2     single-CTA tiles (128 x BN) / CTA-pair tiles (256 x 256)
+ *   EPI_WARPS_8 / _16    epilogue warps per CTA (16 exists for pair tiles only)
+ *   NO_SPLIT_TAIL        a short last wave is not cut into half-width tiles
+ *   GROUP_M(g)           raster group of g row tiles, 1 <= g <= 255 (0 = heuristic)
+ *   STALL_KBLOCK(kb)     self-test of the bounded waits: every TMA producer stops
+ *                        before k-block kb (0 <= kb <= 254) of its first tile, so a
+ *                        consumer's wait runs out, the kernel records a status code
+ *                        (sm120_get_kernel_status) and returns; C is garbage
+ *   TRACE                desc->workspace (>= SM120_TRACE_BYTES, 8-byte aligned)
+ *                        receives a timeline of the launch, SM120_TRACE_WORDS_PER_CTA
+ *                        64-bit words per CTA, CTA b at word b * WORDS_PER_CTA:
+ *                          0 %globaltimer (ns) at kernel entry     1 %clock64 at entry
+ *                          2 %globaltimer after set-up and the wait for the previous kernel    3 %clock64 then
+ *                          4 %globaltimer at exit                  5 %clock64 at exit
+ *                          6 tiles this CTA worked on              7 SM id
+ *                          8 + 4 i + {0,1,2,3}, tile i < 8: %clock64 when the tile's first k-block had
+ *                            landed / when its last MMA was issued (both: MMA warp, pair leader only) /
+ *                            when its accumulator became readable / when its last store was committed
+ *                            (both: first epilogue warp)
+ *                        Not together with the FP32 tensor-core path, which needs the workspace itself.
+ */
+#define SM120_TUNE_CTA_GROUP_1     0x1
+#define SM120_TUNE_CTA_GROUP_2     0x2
+#define SM120_TUNE_EPI_WARPS_8     0x4
+#define SM120_TUNE_EPI_WARPS_16    0x8
+#define SM120_TUNE_NO_SPLIT_TAIL   0x10
+#define SM120_TUNE_TRACE           0x20
+#define SM120_TUNE_GROUP_M(g)      (((g) & 0xFF) << 8)
+#define SM120_TUNE_STALL_KBLOCK(kb) ((((kb) + 1) & 0xFF) << 16)
+#define SM120_TRACE_WORDS_PER_CTA  40
+#define SM120_TRACE_MAX_CTAS       160
+#define SM120_TRACE_BYTES          (SM120_TRACE_MAX_CTAS * SM120_TRACE_WORDS_PER_CTA * 8)
 
 /* Fills *desc with defaults: struct_size, batch = 1, alpha = 1, beta = 0,
  * scales = 1, activation NONE, path AUTO, optimization_level = 1, all else 0. */
@@ -306,6 +344,24 @@ const char* sm120_get_error_string(cudaError_t error);
  * (src/cuda_kernels/sm120_error_handling.cu:48-94), which only logs.
  */
 cudaError_t sm120_get_kernel_status(int device_id, unsigned int* status, int clear);
+
+/*
+ * Clock seen from inside the most recent tensor-core launch on `device_id`:
+ * *cycles = SM cycles (%clock64) and *ns = nanoseconds (%globaltimer) that CTA 0
+ * of that launch was alive; cycles / ns is the SM clock in GHz under the load the
+ * kernel itself produced (a power-capped part runs well below its maximum).  It
+ * synchronises the device.  Two launches in flight at once overwrite each
+ * other's two words; nothing else depends on them.  No counterpart in the reference.
+ */
+cudaError_t sm120_get_kernel_clock(int device_id, unsigned long long* cycles, unsigned long long* ns);
+
+/*
+ * TMA tensor maps (three per tensor-core launch) are cached per host thread,
+ * keyed by address, type, extents, pitches and box; this reports how many the
+ * process has encoded through the driver and how many launches reused a cached
+ * one.  Either pointer may be null.  No counterpart in the reference.
+ */
+void sm120_get_tensor_map_stats(uint64_t* encoded, uint64_t* reused);
 
 /* Wait limit, in milliseconds, used by launches made after the call
  * (default 2000; also read once from the environment variable

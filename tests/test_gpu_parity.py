@@ -3,9 +3,13 @@ package's host code), against the CPU oracle on identical seeded inputs.
 
 Shapes, dtypes and tolerances of the first groups restate the reference's own
 tests (tests/test_sm120_operations.py:47-214,
-tests/integration/test_comprehensive_validation.py:145-193); the BASELINE groups
-use the five configurations of BASELINE.json with its relative-Frobenius gates
-(1e-5 fp32, 1e-2 fp16/bf16, 5e-2 fp8)."""
+tests/integration/test_comprehensive_validation.py:145-193); the "workload" groups
+use the op's five benchmark workloads (fp32 1024^3; fp16 4096^3 with B stored
+[N,K]; the bf16 Dense 8192x4096 . 4096x11008 + bias + GELU; the bf16 batch of 64
+attention-score products 2048x128 . 128x2048; the FP8 65536x8192x8192 product)
+with relative-Frobenius gates of 1e-5 fp32, 1e-2 fp16/bf16 and 5e-2 fp8."""
+import threading
+
 import ctypes
 
 import numpy as np
@@ -260,7 +264,49 @@ def test_fp8_scaled(ops, binding):
     assert ref.rel_frobenius(got_simt, want_deq) <= 1e-2
 
 
-# ----- BASELINE configurations at oracle-friendly size -----
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_fp8_all_operand_layouts(ops, binding, ta, tb):
+    # an FP8 operand whose M or N is contiguous (A stored [K,M], B stored [K,N]) is loaded in 128-byte
+    # boxes of M/N and multiplied through the MN-major descriptor mode: every pairing against float64
+    rng = np.random.default_rng(300 + 2 * ta + tb)
+    for (M, N, K) in ((256, 384, 512), (144, 272, 400)):          # on the tile grid, and ragged in M, N and K
+        a, b, sa, sb = U.random_operands(rng, M, N, K, 1, ta, tb, "fp8_e4m3")
+        want = ref.matmul_oracle(a, b, transpose_a=ta, transpose_b=tb, scale_a=sa, scale_b=sb, out_dtype="bfloat16")
+        got = run(ops, a, b, ta=ta, tb=tb, sa=sa, sb=sb)
+        assert binding.last_kernel_name().startswith("tc_e4m3"), binding.last_kernel_name()
+        assert ref.rel_frobenius(got, want) <= 1e-2, (M, N, K, ta, tb)
+        simt = run(ops, a, b, ta=ta, tb=tb, sa=sa, sb=sb, use_tensor_cores=False)
+        assert ref.rel_frobenius(simt, want) <= 1e-2
+        assert ref.rel_frobenius(got, simt) <= 1e-2
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (True, True)])
+def test_fp8_mn_major_on_pair_tiles_with_split_tail(ops, binding, ta, tb):
+    # the CTA-pair kernel on FP8 operands stored with M / N contiguous: K > 1024 keeps the 8-warp variant, whose
+    # short last wave is cut into half-width tiles (each CTA then multiplies 64 of the 128 N-bytes of a swizzle atom)
+    torch.manual_seed(31)
+    M, N, K = 2304, 2560 + 128, 1152                  # 9 x 11 = 99 pair tiles on 74 clusters: 25 tiles in the last wave
+    a32 = torch.randn((K, M) if ta else (M, K), device="cuda")
+    b32 = torch.randn((N, K) if tb else (K, N), device="cuda")
+    qa, sa = ops.quantize_fp8(a32)
+    qb, sb = ops.quantize_fp8(b32)
+    kw = dict(transpose_a=ta, transpose_b=tb, scale_a=sa, scale_b=sb)
+    got = ops.fused_matmul(qa, qb, tuning=binding.TUNE_CTA_GROUP_2 | binding.TUNE_EPI_WARPS_8, **kw)
+    assert binding.last_kernel_name() == "tc_e4m3_2cta_256x256x128_s6"
+    whole = ops.fused_matmul(qa, qb, tuning=binding.TUNE_CTA_GROUP_2 | binding.TUNE_EPI_WARPS_8 | binding.TUNE_NO_SPLIT_TAIL, **kw)
+    assert torch.equal(got, whole)                    # half-width tiles change the schedule, not the sums
+    simt = ops.fused_matmul(qa, qb, use_tensor_cores=False, **kw)
+    assert binding.last_kernel_name().startswith("simt_e4m3")
+    diff = (got.float() - simt.float()).abs().max().item()
+    assert diff <= 2.0 ** -6 * simt.float().abs().max().item(), diff       # whole matrix: at most a couple of bf16 ulps
+    rows = torch.randint(0, M, (24,), device="cuda")
+    A = (qa.float().double().T if ta else qa.float().double())[rows].cpu().numpy()
+    B = qb.float().double().cpu().numpy()
+    want = (A @ (B.T if tb else B)) / (float(sa) * float(sb))
+    assert ref.rel_frobenius(got[rows].float().cpu().numpy(), want) <= 1e-2
+
+
+# ----- the benchmark workloads at oracle-friendly size -----
 @pytest.mark.parametrize("idx,shrink", [(1, 1), (2, 4), (3, 8), (4, 4), (5, 16)])
 def test_baseline_configs_reduced(ops, idx, shrink):
     cfg = ref.make_config(idx, shrink)
@@ -288,6 +334,17 @@ def _sampled_rows_check(ops, a_t, b_t, got_t, rows, *, tb, bias_t=None, act=-1, 
     return ref.rel_frobenius(U.to_numpy(got_t[rows]), v) <= tol
 
 
+def _whole_matrix_vs_simt(ops, binding, a, b, got, **kw):
+    """Every element of a tensor-core result against the SIMT kernel's (itself oracle-tested): a wrong tile
+    anywhere would show as a large difference, which row samples and run-to-run equality cannot see."""
+    simt = ops.fused_matmul(a, b, use_tensor_cores=False, **kw)
+    assert binding.last_kernel_name().startswith("simt_")
+    scale = simt.float().abs().max().item()
+    diff = (got.float() - simt.float()).abs().max().item()
+    assert diff <= 2.0 ** -6 * scale, (diff, scale)           # 16-bit outputs: a couple of ulps of the largest value
+    return diff
+
+
 def test_baseline_config2_full_size(ops, binding):
     torch.manual_seed(1)
     n = 4096
@@ -304,7 +361,8 @@ def test_baseline_config2_full_size(ops, binding):
     assert torch.equal(c32.half(), c)
     # run-to-run determinism (DEPLOYMENT_GUIDE.md:498-519)
     assert torch.equal(ops.advanced_matmul(a, b, transpose_b=True), c)
-    # same shape in bf16 (the north-star headline size)
+    _whole_matrix_vs_simt(ops, binding, a, b, c, transpose_b=True)
+    # same shape in bf16 (the headline size)
     cb = ops.advanced_matmul(a.bfloat16(), b.bfloat16(), transpose_b=True)
     assert _sampled_rows_check(ops, a.bfloat16(), b.bfloat16(), cb, rows, tb=True)
 
@@ -319,9 +377,10 @@ def test_baseline_config3_full_size(ops, binding):
     rows = torch.randint(0, 8192, (32,), device="cuda")
     assert _sampled_rows_check(ops, x, w, y, rows, tb=False, bias_t=bias, act=9)
     assert torch.equal(ops.fused_matmul(x, w, bias=bias, activation="gelu"), y)
+    _whole_matrix_vs_simt(ops, binding, x, w, y, bias=bias, activation="gelu")
 
 
-def test_baseline_config4_full_size(ops):
+def test_baseline_config4_full_size(ops, binding):
     torch.manual_seed(3)
     q = torch.randn(64, 2048, 128, device="cuda").bfloat16()
     k = torch.randn(64, 128, 2048, device="cuda").bfloat16()
@@ -331,6 +390,7 @@ def test_baseline_config4_full_size(ops):
         rows = torch.randint(0, 2048, (16,), device="cuda")
         assert _sampled_rows_check(ops, q[bz], k[bz], s[bz], rows, tb=False)
     assert torch.equal(ops.batched_matmul(q, k), s)
+    _whole_matrix_vs_simt(ops, binding, q, k, s)
 
 
 def test_baseline_config5_slab(ops, binding):
@@ -348,6 +408,47 @@ def test_baseline_config5_slab(ops, binding):
     # BASELINE gate against the unquantised product on the sampled rows
     exact = a32[rows].double() @ b32.double().T
     assert ref.rel_frobenius(U.to_numpy(c[rows]), exact.cpu().numpy()) <= TOL["fp8_e4m3"]
+
+
+def test_baseline_config5_full_size_one_gpu(ops, binding):
+    # the whole FP8 workload, M = 65536, N = K = 8192, on one GPU (1.7 GB): 256 x 32 pair tiles, more row tiles
+    # and raster groups than any slab has
+    torch.manual_seed(4)
+    M, N, K, G = 65536, 8192, 8192, 8
+    b32 = torch.randn(N, K, device="cuda")
+    qb, sb = ops.quantize_fp8(b32)
+    qa = torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda")
+    # one scale for the whole A, from its global amax, as every rank of the sharded run would use
+    amax = torch.zeros((), device="cuda")
+    slabs = []
+    gen = torch.Generator(device="cuda")
+    for r in range(G):
+        gen.manual_seed(1000 + r)
+        a32 = torch.randn(M // G, K, device="cuda", generator=gen)
+        amax = torch.maximum(amax, a32.abs().max())
+    sa = (448.0 / amax).reshape(1).float()
+    for r in range(G):
+        gen.manual_seed(1000 + r)
+        a32 = torch.randn(M // G, K, device="cuda", generator=gen)
+        qa[r * (M // G):(r + 1) * (M // G)] = (a32 * sa).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        if r in (0, G - 1):
+            slabs.append((r, a32))
+    c = ops.fused_matmul(qa, qb, transpose_b=True, scale_a=sa, scale_b=sb)
+    assert binding.last_kernel_name().startswith("tc_e4m3_2cta") and tuple(c.shape) == (M, N) and c.dtype == torch.bfloat16
+    # float64 oracle on one row of every 128-row tile
+    rows = torch.arange(0, M, 128, device="cuda") + torch.randint(0, 128, (M // 128,), device="cuda")
+    inv = 1.0 / (float(sa) * float(sb))
+    assert _sampled_rows_check(ops, qa, qb, c, rows, tb=True, inv_scale=inv, tol=1e-2)
+    # the gate against the unquantised product, on the rows of the first and the last slab
+    for r, a32 in slabs:
+        rr = torch.randint(0, M // G, (16,), device="cuda")
+        exact = a32[rr].double() @ b32.double().T
+        assert ref.rel_frobenius(U.to_numpy(c[r * (M // G) + rr]), exact.cpu().numpy()) <= TOL["fp8_e4m3"]
+    # the eight slab launches of the M-sharded run produce the same bits
+    for r in range(G):
+        lo, hi = r * (M // G), (r + 1) * (M // G)
+        assert torch.equal(ops.fused_matmul(qa[lo:hi], qb, transpose_b=True, scale_a=sa, scale_b=sb), c[lo:hi]), r
+    assert torch.equal(ops.fused_matmul(qa, qb, transpose_b=True, scale_a=sa, scale_b=sb), c)
 
 
 def test_determinism_small_and_ragged(ops):
@@ -507,14 +608,10 @@ def test_short_k_epilogue_variants_agree(ops, binding, case):
         a = torch.randn(5, 2500, 128, device="cuda").half(); b = torch.randn(5, 128, 2048, device="cuda").half()
         kw = dict(activation="relu")
     outs, names = [], []
-    try:
-        for ew in (8, 16):
-            lib.sm120_debug_force_epi_warps(ew)
-            outs.append(ops.fused_matmul(a, b, **kw))
-            torch.cuda.synchronize()
-            names.append(binding.last_kernel_name())
-    finally:
-        lib.sm120_debug_force_epi_warps(0)
+    for bit in (binding.TUNE_EPI_WARPS_8, binding.TUNE_EPI_WARPS_16):
+        outs.append(ops.fused_matmul(a, b, tuning=bit, **kw))
+        torch.cuda.synchronize()
+        names.append(binding.last_kernel_name())
     assert "2cta" in names[0] and not names[0].endswith("_e16") and names[1].endswith("_e16"), names
     assert torch.equal(outs[0], outs[1]), case
     assert torch.equal(ops.fused_matmul(a, b, **kw), outs[1])     # the launcher's own choice for short K
@@ -533,3 +630,84 @@ def test_short_k_epilogue_variants_agree(ops, binding, case):
     if kw.get("activation") == "relu":
         want = np.maximum(want, 0.0)
     assert ref.rel_frobenius(o2[rows].float().cpu().numpy(), want) <= TOL["bfloat16"]
+
+
+# ----- re-entrancy: the launchers carry no per-call state outside the descriptor -----
+def test_concurrent_host_threads(ops, binding):
+    """Four host threads, each with its own stream, shape, dtype and tuning bits, launch at the same
+    time; every result must match the oracle."""
+    rng = np.random.default_rng(404)
+    jobs = [
+        dict(M=520, N=264, K=136, dtype="bfloat16", tb=False, tuning=binding.TUNE_CTA_GROUP_1, act=0),
+        dict(M=1024, N=768, K=512, dtype="float16", tb=True, tuning=binding.TUNE_CTA_GROUP_2, act=-1),
+        dict(M=300, N=200, K=100, dtype="float32", tb=False, tuning=0, act=9),
+        dict(M=384, N=640, K=256, dtype="fp8_e4m3", tb=True, tuning=binding.TUNE_CTA_GROUP_2 | binding.TUNE_EPI_WARPS_8, act=-1),
+    ]
+    for j in jobs:
+        j["a"], j["b"], j["sa"], j["sb"] = U.random_operands(rng, j["M"], j["N"], j["K"], 1, False, j["tb"], j["dtype"], scale=0.5)
+        fp8 = j["dtype"] == "fp8_e4m3"
+        j["want"] = ref.matmul_oracle(j["a"], j["b"], transpose_b=j["tb"], act=j["act"],
+                                      scale_a=j["sa"] if fp8 else 1.0, scale_b=j["sb"] if fp8 else 1.0,
+                                      out_dtype="bfloat16" if fp8 else j["dtype"])
+        j["ta_"], j["tb_"] = U.to_cuda(j["a"]), U.to_cuda(j["b"])
+    torch.cuda.synchronize()
+    start = threading.Barrier(len(jobs))
+    errors = []
+
+    def work(j):
+        try:
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            fp8 = j["dtype"] == "fp8_e4m3"
+            start.wait()
+            with torch.cuda.stream(stream):
+                outs = [ops.fused_matmul(j["ta_"], j["tb_"], transpose_b=j["tb"], activation=j["act"], tuning=j["tuning"],
+                                         scale_a=j["sa"] if fp8 else None, scale_b=j["sb"] if fp8 else None)
+                        for _ in range(25)]
+            stream.synchronize()
+            j["got"] = [U.to_numpy(o) for o in (outs[0], outs[-1])]
+        except Exception as e:      # surfaced by the main thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(j,)) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for j in jobs:
+        tol = "bfloat16" if j["dtype"] == "fp8_e4m3" else j["dtype"]
+        for got in j["got"]:
+            check(got, j["want"], tol, f"thread {j['dtype']}")
+        assert np.array_equal(j["got"][0].view(np.uint8), j["got"][1].view(np.uint8))
+
+
+def test_tensor_map_cache_is_reused(ops, binding):
+    a = torch.randn(512, 256, device="cuda").bfloat16()
+    b = torch.randn(256, 384, device="cuda").bfloat16()
+    out = torch.empty(512, 384, device="cuda", dtype=torch.bfloat16)
+    ops.fused_matmul(a, b, out=out)
+    enc0, hit0 = binding.tensor_map_stats()
+    for _ in range(10):
+        ops.fused_matmul(a, b, out=out)
+    enc1, hit1 = binding.tensor_map_stats()
+    assert enc1 == enc0 and hit1 - hit0 == 30          # three maps per launch, all from the cache
+    torch.cuda.synchronize()
+
+
+def test_launch_trace(ops, binding):
+    """The optional timeline (SM120_TUNE_TRACE) of a CTA-pair launch: every CTA reports its tiles in order."""
+    torch.manual_seed(9)
+    a = torch.randn(2048, 1024, device="cuda").bfloat16()
+    b = torch.randn(2048, 1024, device="cuda").bfloat16()
+    trace = torch.zeros(binding.TRACE_BYTES // 8, dtype=torch.int64, device="cuda")
+    c = ops.fused_matmul(a, b, transpose_b=True, tuning=binding.TUNE_CTA_GROUP_2, trace=trace)
+    assert torch.equal(c, ops.fused_matmul(a, b, transpose_b=True, tuning=binding.TUNE_CTA_GROUP_2))
+    t = trace.cpu().numpy().reshape(binding.TRACE_MAX_CTAS, binding.TRACE_WORDS_PER_CTA)
+    ctas = 2 * 64                                       # 8 x 8 pair tiles, one per cluster
+    assert (t[:ctas, 6] == 1).all() and (t[ctas:, :] == 0).all()
+    assert (t[:ctas, 0] <= t[:ctas, 2]).all() and (t[:ctas, 2] < t[:ctas, 4]).all()       # entry <= set-up done < exit (ns)
+    lead = t[0:ctas:2]
+    assert (lead[:, 8] > lead[:, 3]).all() and (lead[:, 9] > lead[:, 8]).all()            # first k-block, last MMA issued
+    assert (t[:ctas, 10] > t[:ctas, 3]).all() and (t[:ctas, 11] > t[:ctas, 10]).all()     # accumulator ready, last store
+    assert (t[:ctas, 5] >= t[:ctas, 11]).all()

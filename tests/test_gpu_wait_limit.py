@@ -1,7 +1,8 @@
 """GPU test of the bounded waits inside the tensor-core kernel.
 
 Every wait on an mbarrier in the kernel has a wall-clock limit.  Here the limit
-is made short (100 ms) and the library's test hook makes every TMA producer stop
+is made short (100 ms) and the launch descriptor's self-test bit
+(SM120_TUNE_STALL_KBLOCK) makes every TMA producer stop
 before one k-block of its first tile, so the MMA role's wait for that k-block
 runs out.  The kernel must then return normally (no trap, no fault, no hang),
 report a non-zero status word, and leave the device usable: the next, ordinary
@@ -34,16 +35,15 @@ def test_wait_limit_reports_status_and_device_survives(ops, binding, cta_group):
     ta, tb = U.to_cuda(a), U.to_cuda(b)
     want = ref.matmul_oracle(a, b, transpose_b=True, out_dtype="bfloat16")
     assert _status(lib, clear=True) == 0
+    flavour = binding.TUNE_CTA_GROUP_2 if cta_group == 2 else binding.TUNE_CTA_GROUP_1
     try:
-        lib.sm120_debug_force_cta_group(cta_group)
         lib.sm120_set_wait_limit_ms(100)
-        lib.sm120_debug_skip_kblock(1)            # k-block 1 of every CTA's first tile never arrives
         t0 = time.perf_counter()
-        ops.fused_matmul(ta, tb, transpose_b=True)          # result is meaningless; it must only return
+        # k-block 1 of every CTA's first tile never arrives; the result is meaningless, the call must only return
+        ops.fused_matmul(ta, tb, transpose_b=True, tuning=flavour | binding.tune_stall_kblock(1))
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - t0
     finally:
-        lib.sm120_debug_skip_kblock(-1)
         lib.sm120_set_wait_limit_ms(2000)
     assert binding.last_kernel_name().startswith("tc_bf16_2cta" if cta_group == 2 else "tc_bf16_128")
     assert 0.05 < elapsed < 5.0, elapsed          # gave up after the limit, not instantly and not never
@@ -51,10 +51,7 @@ def test_wait_limit_reports_status_and_device_survives(ops, binding, cta_group):
     assert status != 0
     assert (status >> 28) in (1, 2, 3)            # role that gave up first: producer, MMA or epilogue
     assert _status(lib, clear=False) == 0         # the read above cleared it
-    try:
-        got = ops.fused_matmul(ta, tb, transpose_b=True)   # same flavour, hook off: a normal launch
-        torch.cuda.synchronize()
-    finally:
-        lib.sm120_debug_force_cta_group(0)
+    got = ops.fused_matmul(ta, tb, transpose_b=True, tuning=flavour)   # same flavour, no stall: a normal launch
+    torch.cuda.synchronize()
     assert ref.rel_frobenius(U.to_numpy(got), want) <= ref.TOLERANCE["bfloat16"]
     assert _status(lib, clear=False) == 0
