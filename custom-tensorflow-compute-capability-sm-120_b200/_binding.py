@@ -89,6 +89,10 @@ EXPORTS = {
     "sm120_quantize_fp8_scratch_bytes": (ctypes.c_size_t, [c_int64]),
     "sm120_launch_quantize_fp8": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
     "sm120_launch_quantize_fp8_static": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "sm120_launch_cast_fp8": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "sm120_launch_activation": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "sm120_launch_bias_activation": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "sm120_launch_bias_grad": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "sm120_is_supported": (c_bool, [c_int]),
     "sm120_get_error_string": (c_char_p, [c_int]),
     "sm120_get_kernel_status": (c_int, [c_int, POINTER(c_uint), c_int]),

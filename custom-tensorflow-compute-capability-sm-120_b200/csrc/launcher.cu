@@ -21,6 +21,11 @@ namespace sm120 {
 long long quant_spans(long long n);
 cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, long long n, float* partial, cudaStream_t stream);
 cudaError_t quant_launch_static(const void* x, int x_dtype, void* q, float* scale_out, long long n, int device, cudaStream_t stream);
+cudaError_t quant_cast_launch(const void* x, int x_dtype, void* q, const float* scale, long long n, cudaStream_t stream);
+cudaError_t activation_launch(const void* in, void* out, long long n, const void* bias, int bias_dtype, long long cols,
+                              int act, int dtype, int sm_count, cudaStream_t stream);
+cudaError_t bias_grad_launch(const void* g, int dtype, long long M, long long N, long long ld, void* out, int out_dtype,
+                             cudaStream_t stream);
 
 namespace {
 
@@ -379,6 +384,90 @@ cudaError_t sm120_launch_quantize_fp8_static(const void* x, SM120DataType x_dtyp
     if (e == cudaSuccess) {
         g_launch_count.fetch_add(3, std::memory_order_relaxed);
         t_last_kernel = "quant_e4m3_amax_scale_cast_static";
+    }
+    return e;
+}
+
+cudaError_t sm120_launch_cast_fp8(const void* x, SM120DataType x_dtype, int64_t n, const float* scale, void* q,
+                                  cudaStream_t stream) {
+    if (n < 0 || scale == nullptr) return cudaErrorInvalidValue;
+    if (x_dtype != SM120_DTYPE_FLOAT32 && x_dtype != SM120_DTYPE_FLOAT16 && x_dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (n > 0 && (x == nullptr || q == nullptr)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(scale) & 3u) != 0) return cudaErrorInvalidValue;
+    if (n == 0) return cudaSuccess;
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    e = quant_cast_launch(x, x_dtype, q, scale, n, stream);
+    if (e == cudaSuccess) {
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+        t_last_kernel = "quant_e4m3_scale_cast";
+    }
+    return e;
+}
+
+namespace {
+cudaError_t activation_common(const void* input, const void* bias, int bias_dtype, void* output, int64_t rows, int64_t cols,
+                              int activation_type, int dtype, cudaStream_t stream, const char* name) {
+    if (rows < 0 || cols < 0) return cudaErrorInvalidValue;
+    if (dtype != SM120_DTYPE_FLOAT32 && dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (bias != nullptr && bias_dtype != SM120_DTYPE_FLOAT32 && bias_dtype != SM120_DTYPE_FLOAT16 && bias_dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (cols != 0 && rows > INT64_MAX / cols) return cudaErrorInvalidValue;
+    const int64_t n = rows * cols;
+    if (n > 0 && (input == nullptr || output == nullptr)) return cudaErrorInvalidValue;
+    if (n == 0) return cudaSuccess;
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    e = activation_launch(input, output, n, bias, bias_dtype, cols, activation_type, dtype, sms, stream);
+    if (e == cudaSuccess) {
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+        t_last_kernel = name;
+    }
+    return e;
+}
+}  // namespace
+
+cudaError_t sm120_launch_activation(const void* input, void* output, int size, SM120ActivationType activation_type,
+                                    SM120DataType dtype, cudaStream_t stream) {
+    return activation_common(input, nullptr, 0, output, 1, size, static_cast<int>(activation_type), static_cast<int>(dtype),
+                             stream, "activation_vec16");
+}
+
+cudaError_t sm120_launch_bias_activation(const void* input, const void* bias, SM120DataType bias_dtype, void* output,
+                                         int64_t rows, int64_t cols, SM120ActivationType activation_type, SM120DataType dtype,
+                                         cudaStream_t stream) {
+    return activation_common(input, bias, static_cast<int>(bias_dtype), output, rows, cols, static_cast<int>(activation_type),
+                             static_cast<int>(dtype), stream, bias != nullptr ? "bias_activation_vec16" : "activation_vec16");
+}
+
+cudaError_t sm120_launch_bias_grad(const void* grad_c, void* grad_bias, int64_t M, int64_t N, int64_t ld, SM120DataType dtype,
+                                   SM120DataType out_dtype, cudaStream_t stream) {
+    if (M < 0 || N < 0) return cudaErrorInvalidValue;
+    if (dtype != SM120_DTYPE_FLOAT32 && dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (out_dtype != SM120_DTYPE_FLOAT32 && out_dtype != dtype) return cudaErrorInvalidValue;
+    if (ld == 0) ld = N;
+    if (ld < N) return cudaErrorInvalidValue;
+    if (N > 0 && grad_bias == nullptr) return cudaErrorInvalidValue;
+    if (N > 0 && M > 0 && grad_c == nullptr) return cudaErrorInvalidValue;
+    if (N == 0) return cudaSuccess;
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    e = bias_grad_launch(grad_c, dtype, M, N, ld, grad_bias, out_dtype, stream);     // M == 0 writes zeros
+    if (e == cudaSuccess) {
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+        t_last_kernel = "bias_grad_colsum";
     }
     return e;
 }

@@ -1,6 +1,10 @@
 // Per-tensor FP8 (e4m3) quantisation for the FP8 matmul path:
 //     scale = 448 / max|x|          (1 when the tensor is all zeros)
 //     q[i]  = saturate_e4m3(x[i] * scale)       round-to-nearest-even, finite
+// Non-finite input: an infinity counts as the largest finite float when the
+// maximum is taken (the scale stays positive and finite; the infinity itself
+// saturates to +-448, everything finite becomes 0); a NaN does not take part in
+// the maximum and is written as the e4m3 NaN.
 // The reference declares the type and the conversion
 // (src/cuda_kernels/sm120_datatype_support.h:71-82,168-171;
 // python/sm120_datatype_manager.py:88-98) but has no kernel that produces FP8
@@ -82,7 +86,7 @@ sm120_quant_amax_final_kernel(const float* __restrict__ partial, int nparts, flo
     float m = 0.0f;
     for (int i = threadIdx.x; i < nparts; i += blockDim.x) m = fmaxf(m, partial[i]);
     m = block_max(m, red);
-    if (threadIdx.x == 0) *scale_out = m > 0.0f ? 448.0f / m : 1.0f;
+    if (threadIdx.x == 0) *scale_out = m > 0.0f ? 448.0f / fminf(m, 3.402823466e38f) : 1.0f;
 }
 
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
@@ -137,6 +141,28 @@ cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, 
         case SM120_DTYPE_BFLOAT16: return quant_typed<__nv_bfloat16>(x, n, static_cast<uint8_t*>(q), scale_out, partial, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+// Only the third kernel, with a scale the caller already has (e.g. from the amax of a
+// tensor that is sharded over several GPUs).
+cudaError_t quant_cast_launch(const void* x, int x_dtype, void* q, const float* scale, long long n, cudaStream_t stream) {
+    const long long spans = quant_spans(n);
+    if (spans > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+    uint8_t* qq = static_cast<uint8_t*>(q);
+    const unsigned grid = static_cast<unsigned>(spans);
+    switch (x_dtype) {
+        case SM120_DTYPE_FLOAT32:
+            sm120_quant_scale_cast_kernel<float><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float*>(x), n, scale, qq);
+            break;
+        case SM120_DTYPE_FLOAT16:
+            sm120_quant_scale_cast_kernel<__half><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __half*>(x), n, scale, qq);
+            break;
+        case SM120_DTYPE_BFLOAT16:
+            sm120_quant_scale_cast_kernel<__nv_bfloat16><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), n, scale, qq);
+            break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------

@@ -14,18 +14,35 @@ caller asks for the gathered C is anything exchanged, in one of two ways:
   over NVLink), so the all-gather happens while the tiles are computed and the
   only collective left is a one-element barrier.
 
+Failure handling is host-side only.  A rank that stops taking part announces it
+in the process group's store (``leave``); the others look there before they
+launch anything that waits for it (``departed``) and raise ``PeerLeft``.  With a
+deadline (``deadline_s``) every collective of ``gathered`` / ``gathered_fused`` is
+waited for on the host with that limit; when it runs out the process group is
+aborted (NCCL) and ``CollectiveTimeout`` is raised, so a rank that silently
+stopped costs its peers one deadline instead of a hang.
+
 The reference has no multi-GPU code (its only trace is
 tf.distribute.MirroredStrategy in docs/api-reference.md:510-511); this module
-is the part of the B200 build that BASELINE config 5 (FP8, M = 65536) runs on.
+is what the M-sharded FP8 workload (M = 65536, N = K = 8192) runs on.
 """
 from __future__ import annotations
 
+import datetime
 from typing import Callable, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
 TILE_M = 128
+
+
+class PeerLeft(RuntimeError):
+    """Another rank announced that it has stopped taking part; nothing was launched."""
+
+
+class CollectiveTimeout(RuntimeError):
+    """A collective did not finish within the deadline; the process group was aborted."""
 
 
 def slab_rows(M: int, world_size: int, align: int = TILE_M) -> int:
@@ -72,10 +89,11 @@ class MShardedMatmul:
     """
 
     def __init__(self, M: int, N: int, group: Optional[dist.ProcessGroup] = None,
-                 matmul_fn: Optional[Callable] = None, align: int = TILE_M):
+                 matmul_fn: Optional[Callable] = None, align: int = TILE_M, deadline_s: Optional[float] = None):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.group = group
+        self.deadline_s = deadline_s
         self.world_size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.M, self.N = int(M), int(N)
@@ -91,6 +109,52 @@ class MShardedMatmul:
     @property
     def local_rows(self) -> int:
         return self.stop - self.start
+
+    # -- failure handling (host side) -------------------------------------------
+    _LEFT_KEY = "sm120_mshard/left/{}"
+
+    @staticmethod
+    def _store():
+        return dist.distributed_c10d._get_default_store()
+
+    def leave(self) -> None:
+        """Announce that this rank stops taking part.  Call it between two steps, with none
+        of this rank's kernels or collectives in flight; the rank may then exit."""
+        self._store().set(self._LEFT_KEY.format(self.rank), "1")
+
+    def departed(self) -> List[int]:
+        """Ranks that have announced their departure (a non-blocking look into the store)."""
+        store = self._store()
+        return [r for r in range(self.world_size) if r != self.rank and store.check([self._LEFT_KEY.format(r)])]
+
+    def _require_peers(self) -> None:
+        gone = self.departed()
+        if gone:
+            raise PeerLeft(f"rank(s) {gone} left the M-sharded product; rank {self.rank} launched nothing")
+
+    def _await(self, work, what: str) -> None:
+        """Wait for an asynchronous collective: stream-ordered without a deadline, on the host with one."""
+        if work is None:
+            return
+        if self.deadline_s is None:
+            work.wait()
+            return
+        try:
+            done = work.wait(datetime.timedelta(seconds=self.deadline_s))
+        except Exception as e:                      # both backends raise when the time is up
+            self._abort()
+            raise CollectiveTimeout(f"{what} did not finish within {self.deadline_s} s on rank {self.rank}: {e}") from e
+        if done is False:
+            self._abort()
+            raise CollectiveTimeout(f"{what} did not finish within {self.deadline_s} s on rank {self.rank}")
+
+    def _abort(self) -> None:
+        """Tear the communicator down without waiting for the peers (NCCL); a no-op where the backend has no abort."""
+        try:
+            if dist.get_backend(self.group) == "nccl" and hasattr(dist.distributed_c10d, "_abort_process_group"):
+                dist.distributed_c10d._abort_process_group(self.group)
+        except Exception:
+            pass
 
     def replicate_b(self, b: torch.Tensor, src: int = 0) -> torch.Tensor:
         """Broadcast B (and anything else every rank needs, e.g. scales) from
@@ -110,6 +174,7 @@ class MShardedMatmul:
         all-gathered while chunk c+1 is being multiplied."""
         if a_slab.shape[0] != self.local_rows:
             raise ValueError(f"rank {self.rank} owns {self.local_rows} rows of A, got {a_slab.shape[0]}")
+        self._require_peers()
         G, ms = self.world_size, self.rows_per_rank
         dev = a_slab.device
         # padded result: slab r at rows [r*ms, (r+1)*ms); trimmed to M at the end
@@ -141,20 +206,29 @@ class MShardedMatmul:
     def _all_gather(self, views, chunk, single: bool, full: torch.Tensor) -> None:
         if single:
             # slabs are contiguous in rank order: one all-gather straight into place
-            dist.all_gather_into_tensor(full, chunk.contiguous() if not chunk.is_contiguous() else chunk, group=self.group)
+            work = dist.all_gather_into_tensor(full, chunk.contiguous() if not chunk.is_contiguous() else chunk,
+                                               group=self.group, async_op=True)
         else:
-            dist.all_gather(views, chunk, group=self.group)
+            work = dist.all_gather(views, chunk, group=self.group, async_op=True)
+        self._await(work, "all-gather of the C slabs")
 
 
 class PeerBuffers:
-    """Every rank's gathered-C buffer [G*Ms, N], reachable from this process.
+    """Every rank's gathered-C buffers [G*Ms, N], reachable from this process.
 
-    Each rank allocates its buffer with torch and publishes the CUDA IPC handle of
-    the allocation that holds it (plus the buffer's offset inside it); every other
-    rank opens that handle with ITS OWN device current, which maps the memory for
-    kernels of that device and sets up peer access.  `addr[r]` is then the address
-    of rank r's buffer in this process.  Set up once, outside timed regions; the
-    buffer must stay alive as long as any rank uses it."""
+    Each rank allocates TWO buffers with torch and publishes the CUDA IPC handle of
+    the allocation that holds each (plus the buffer's offset inside it); every other
+    rank opens the handles with ITS OWN device current, which maps the memory for
+    kernels of that device and sets up peer access.  `addr[k][r]` is then the address
+    of rank r's buffer k in this process.  Set up once, outside timed regions; the
+    buffers must stay alive as long as any rank uses them.
+
+    Why two: call i of ``gathered_fused`` writes buffer i % 2.  A rank's call i + 1 may
+    start while a peer is still reading the result of call i (the ranks are ordered
+    only AFTER each product), so it must not write the same memory; buffer i % 2 is
+    written again by call i + 2, which no rank starts before every rank has passed
+    the closing all-reduce of call i + 1 in stream order.  The view that call i returns
+    is therefore valid for work that this rank enqueues before its call i + 1."""
 
     def __init__(self, sharded: "MShardedMatmul", out_dtype: torch.dtype, device: torch.device):
         import ctypes
@@ -162,60 +236,96 @@ class PeerBuffers:
         G, ms = sharded.world_size, sharded.rows_per_rank
         self.rank = sharded.rank
         self.device = device
-        self.full = torch.zeros((G * ms, sharded.N), dtype=out_dtype, device=device)
-        self.row_bytes = sharded.N * self.full.element_size()
+        self.group = sharded.group
+        self.fulls = [torch.zeros((G * ms, sharded.N), dtype=out_dtype, device=device) for _ in range(2)]
+        self.row_bytes = sharded.N * self.fulls[0].element_size()
+        self.calls = 0
         lib = _binding.load_library()
-        handle = ctypes.create_string_buffer(64)
-        offset = ctypes.c_uint64(0)
-        with torch.cuda.device(device):
-            rc = lib.sm120_ipc_export(self.full.data_ptr(), handle, ctypes.byref(offset))
-        if rc != 0:
-            raise RuntimeError(f"cannot export the C buffer through CUDA IPC: {_binding.error_string(rc)}")
+        mine = []
+        for full in self.fulls:
+            handle = ctypes.create_string_buffer(64)
+            offset = ctypes.c_uint64(0)
+            with torch.cuda.device(device):
+                rc = lib.sm120_ipc_export(full.data_ptr(), handle, ctypes.byref(offset))
+            if rc != 0:
+                raise RuntimeError(f"cannot export the C buffer through CUDA IPC: {_binding.error_string(rc)}")
+            mine.append((bytes(handle.raw), int(offset.value)))
         published: List[object] = [None] * G
-        dist.all_gather_object(published, (bytes(handle.raw), int(offset.value)), group=sharded.group)
-        self.addr: List[int] = []
+        dist.all_gather_object(published, mine, group=sharded.group)
+        self.addr: List[List[int]] = [[], []]
         self._opened: List[int] = []
+        opened_by_handle = {}
         with torch.cuda.device(device):
             for r in range(G):
-                if r == self.rank:
-                    self.addr.append(self.full.data_ptr())
-                    continue
-                raw, off = published[r]
-                base = ctypes.c_void_p(0)
-                rc = lib.sm120_ipc_import(ctypes.create_string_buffer(raw, 64), ctypes.byref(base))
-                if rc != 0 or not base.value:
-                    raise RuntimeError(f"cannot open rank {r}'s C buffer: {_binding.error_string(rc)}")
-                self._opened.append(base.value)
-                self.addr.append(base.value + off)
+                for k in range(2):
+                    if r == self.rank:
+                        self.addr[k].append(self.fulls[k].data_ptr())
+                        continue
+                    raw, off = published[r][k]
+                    base = opened_by_handle.get((r, raw))           # both buffers may sit in one allocation
+                    if base is None:
+                        ptr = ctypes.c_void_p(0)
+                        rc = lib.sm120_ipc_import(ctypes.create_string_buffer(raw, 64), ctypes.byref(ptr))
+                        if rc != 0 or not ptr.value:
+                            raise RuntimeError(f"cannot open rank {r}'s C buffer: {_binding.error_string(rc)}")
+                        base = ptr.value
+                        opened_by_handle[(r, raw)] = base
+                        self._opened.append(base)
+                    self.addr[k].append(base + off)
         dist.barrier(group=sharded.group)                             # nobody proceeds before every handle is open
 
-    def close(self) -> None:
-        """Unmap the peers' buffers (collective: every rank calls it, with no kernel in flight)."""
+    @property
+    def full(self) -> torch.Tensor:
+        """The buffer that the most recent call wrote (the first one before any call)."""
+        return self.fulls[(self.calls - 1) % 2 if self.calls else 0]
+
+    def close(self, collective: bool = True) -> None:
+        """Unmap the peers' buffers.  Normally collective: every rank calls it with no kernel in
+        flight, and the barriers keep any rank from freeing memory a peer may still write.  On an
+        error path (a peer left or timed out) pass collective=False: only this rank's device is
+        synchronised, so its own kernels no longer touch the peers' memory, and nothing waits for
+        a rank that may be gone; keep this object (and its buffers) alive until the process ends."""
         from . import _binding
         torch.cuda.synchronize(self.device)
-        dist.barrier()
+        if collective:
+            dist.barrier(group=self.group)
         lib = _binding.load_library()
         with torch.cuda.device(self.device):
             for base in self._opened:
                 lib.sm120_ipc_close(base)
         self._opened = []
-        dist.barrier()
+        if collective:
+            dist.barrier(group=self.group)
+
+    def __enter__(self) -> "PeerBuffers":
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        self.close(collective=exc_type is None)
 
 
 def _gathered_fused(self, a_slab: torch.Tensor, b: torch.Tensor, buffers: PeerBuffers, **kwargs) -> torch.Tensor:
     """The whole C [M, N] on every rank from ONE kernel per rank: the epilogue
     writes this rank's rows into every rank's buffer.  A one-element all-reduce
-    afterwards orders the ranks (it moves no matrix data)."""
+    afterwards orders the ranks (it moves no matrix data).  The result is a view of
+    one of the two peer buffers: use it (enqueue the work that reads it) before this
+    rank's next call, see PeerBuffers."""
     if a_slab.shape[0] != self.local_rows:
         raise ValueError(f"rank {self.rank} owns {self.local_rows} rows of A, got {a_slab.shape[0]}")
+    self._require_peers()
     ms = self.rows_per_rank
     lo, hi = self.rank * ms, self.rank * ms + self.local_rows
+    k = buffers.calls % 2
+    buffers.calls += 1
+    full = buffers.fulls[k]
     if self.local_rows > 0:
-        peers = [buffers.addr[r] + lo * buffers.row_bytes for r in range(self.world_size) if r != self.rank]
-        self.matmul_fn(a_slab, b, out=buffers.full[lo:hi], peer_outs=peers, **kwargs)
+        peers = [buffers.addr[k][r] + lo * buffers.row_bytes for r in range(self.world_size) if r != self.rank]
+        self.matmul_fn(a_slab, b, out=full[lo:hi], peer_outs=peers, **kwargs)
     token = torch.zeros(1, device=a_slab.device)
-    dist.all_reduce(token, group=self.group)        # enqueued behind the GEMM: completes when every rank's GEMM has
-    return buffers.full[: self.M]
+    # enqueued behind the GEMM: completes when every rank's GEMM (and its peer stores) has
+    work = dist.all_reduce(token, group=self.group, async_op=True)
+    self._await(work, "the closing all-reduce of the fused gather")
+    return full[: self.M]
 
 
 MShardedMatmul.gathered_fused = _gathered_fused

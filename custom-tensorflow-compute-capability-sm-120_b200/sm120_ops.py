@@ -192,14 +192,98 @@ _WORKSPACES: Dict[Any, torch.Tensor] = {}
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """A per-device scratch buffer of at least `nbytes`, reused by later calls on the
-    same device (launches that use it are ordered by the stream they run on)."""
-    key = (device.type, device.index)
+    """A scratch buffer of at least `nbytes` for the current stream of `device`, reused by
+    later calls on that stream (which orders the launches that use it).  Streams do not
+    share a buffer, and a buffer that is replaced by a larger one stays reserved until
+    the work already queued on its stream has finished."""
+    stream = torch.cuda.current_stream(device)
+    key = (device.type, device.index, stream.cuda_stream)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            ws.record_stream(stream)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = ws
     return ws
+
+
+class _HostPipeline:
+    """Per-device state of the host-operand path: one stream per copy direction and
+    device staging buffers that are kept between calls."""
+
+    CHUNKS = 8            # row chunks of A (and C) per call
+    MIN_ROWS = 256        # a chunk is a whole number of 256-row tiles
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.h2d = torch.cuda.Stream(device=device)
+        self.d2h = torch.cuda.Stream(device=device)
+        self._staging: Dict[str, torch.Tensor] = {}
+
+    def staging(self, role: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A device tensor of `shape` / `dtype` carved from this role's buffer, which grows on demand."""
+        nbytes = 1
+        for e in shape:
+            nbytes *= int(e)
+        nbytes = max(16, nbytes * torch.empty((), dtype=dtype).element_size())
+        buf = self._staging.get(role)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self._staging[role] = buf
+        return buf[:nbytes].view(dtype).view(*shape)
+
+
+_HOST_PIPELINES: Dict[int, _HostPipeline] = {}
+
+
+def _host_pipelined(a: torch.Tensor, b: torch.Tensor, bias, host_out: Optional[torch.Tensor], out_dtype, kwargs) -> torch.Tensor:
+    """C = op for HOST operands a [M, K] and b, as a three-stage pipeline over row chunks of A:
+    B travels first; then chunk i+1 of A goes to the device on one copy stream while chunk i is
+    multiplied on the caller's stream and chunk i-1 of C returns on a second copy stream (PCIe is
+    full duplex).  Every copy is one plain asynchronous memcpy.  Returns the host result (pinned)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    pipe = _HOST_PIPELINES.get(dev.index)
+    if pipe is None:
+        pipe = _HOST_PIPELINES[dev.index] = _HostPipeline(dev)
+    M, K = a.shape
+    N = b.shape[0] if kwargs.get("transpose_b") else b.shape[1]
+    if out_dtype is None:
+        out_dtype = torch.bfloat16 if a.dtype == torch.float8_e4m3fn else a.dtype
+    if host_out is None:
+        host_out = torch.empty((M, N), dtype=out_dtype, pin_memory=True)
+    elif tuple(host_out.shape) != (M, N) or host_out.dtype != out_dtype or not host_out.is_contiguous():
+        raise ValueError(f"host `out` must be a contiguous {out_dtype} tensor of shape {(M, N)}")
+    a = a.contiguous()
+    b = b.contiguous()
+    a_dev = pipe.staging("a", a.shape, a.dtype)
+    b_dev = pipe.staging("b", b.shape, b.dtype)
+    c_dev = pipe.staging("c", (M, N), out_dtype)
+    main = torch.cuda.current_stream(dev)
+    rows = -(-M // _HostPipeline.CHUNKS)
+    rows = max(_HostPipeline.MIN_ROWS, -(-rows // _HostPipeline.MIN_ROWS) * _HostPipeline.MIN_ROWS)
+    pipe.h2d.wait_stream(main)              # earlier work on the caller's stream may still read the staging buffers
+    pipe.d2h.wait_stream(main)
+    with torch.cuda.stream(pipe.h2d):
+        b_dev.copy_(b, non_blocking=True)
+        if isinstance(bias, torch.Tensor) and not bias.is_cuda:
+            bias_dev = pipe.staging("bias", bias.shape, bias.dtype)
+            bias_dev.copy_(bias, non_blocking=True)
+            bias = bias_dev
+    for r0 in range(0, M, rows):
+        r1 = min(M, r0 + rows)
+        with torch.cuda.stream(pipe.h2d):
+            a_dev[r0:r1].copy_(a[r0:r1], non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(pipe.h2d)
+        main.wait_event(arrived)            # also orders B and the bias, copied earlier on the same stream
+        fused_matmul(a_dev[r0:r1], b_dev, bias=bias, out=c_dev[r0:r1], out_dtype=out_dtype, **kwargs)
+        computed = torch.cuda.Event()
+        computed.record(main)
+        with torch.cuda.stream(pipe.d2h):
+            pipe.d2h.wait_event(computed)
+            host_out[r0:r1].copy_(c_dev[r0:r1], non_blocking=True)
+    pipe.d2h.synchronize()                  # the host result is complete when the call returns
+    return host_out
 
 
 def fused_matmul(
@@ -293,6 +377,15 @@ def fused_matmul(
         if beta != 0.0:
             raise ValueError("beta != 0 is not supported with host operands")
         host_out, out = out, None
+    if (host_kind is not None and not a.is_cuda and not b.is_cuda and a.dim() == 2 and b.dim() == 2 and not transpose_a
+            and out is None and beta == 0.0 and not peer_outs and trace is None and not fp32_tensor_cores
+            and not isinstance(scale_a, torch.Tensor) and not isinstance(scale_b, torch.Tensor)
+            and M >= 2 * _HostPipeline.MIN_ROWS and N >= 1 and K >= 1):
+        # large host operands: copies and products overlap chunk by chunk
+        host = _host_pipelined(a, b, bias, host_out, out_dtype,
+                               dict(transpose_b=transpose_b, activation=activation, alpha=alpha, scale_a=scale_a, scale_b=scale_b,
+                                    use_tensor_cores=use_tensor_cores, optimization_level=optimization_level, tuning=tuning))
+        return _torch_to_numpy(host) if host_kind == "numpy" else host
     if host_kind is not None:
         dev = torch.device("cuda", torch.cuda.current_device())
         a = a.to(dev, non_blocking=True)
@@ -470,13 +563,116 @@ def matmul_grad(grad_c, a, b):
     return (fused_matmul(grad_c, b, transpose_b=True), fused_matmul(a, grad_c, transpose_a=True))
 
 
-def quantize_fp8(x: torch.Tensor):
+def fused_activation(x: torch.Tensor, activation: Union[None, str, int], bias: Optional[torch.Tensor] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(x + bias) as one HBM-bound pass: the op ``SM120FusedActivation``
+    (src/tensorflow_ops/sm120_ops.cc:251-326) over ``sm120_launch_activation``
+    (src/cuda_kernels/sm120_c_interface.cu:139-164), with the bias add of
+    ``tf.nn.bias_add`` (python/sm120_keras_layers.py:169) folded into the same kernel
+    when a bias is given.  `x` is a contiguous CUDA tensor (float32, float16 or
+    bfloat16); `bias` has x.shape[-1] entries; `out` may be `x` itself."""
+    _require_available()
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise TypeError("fused_activation needs a CUDA tensor")
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"dtype {x.dtype} is not supported (float32, float16, bfloat16)")
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    elif not (out.is_cuda and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype and out.device == x.device):
+        raise ValueError("`out` must be a contiguous CUDA tensor with x's shape, dtype and device")
+    code = activation_code(activation)
+    cols = x.shape[-1] if x.dim() >= 1 else 1
+    rows = x.numel() // cols if cols else 0
+    bias_ptr, bias_code = None, 0
+    if bias is not None:
+        if not (isinstance(bias, torch.Tensor) and bias.is_cuda and bias.dim() == 1 and bias.shape[0] == cols):
+            raise InvalidArgumentError(f"bias must be a CUDA tensor of shape [{cols}]")
+        if bias.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            raise ValueError(f"bias dtype {bias.dtype} is not supported")
+        bias = bias.contiguous()
+        bias_ptr, bias_code = bias.data_ptr(), _TORCH_TO_SM120[bias.dtype]
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    with torch.cuda.device(x.device):
+        rc = _b.load_library().sm120_launch_bias_activation(x.data_ptr(), bias_ptr, bias_code, out.data_ptr(), rows, cols, code,
+                                                            _TORCH_TO_SM120[x.dtype], stream)
+    if rc == _b.CUDA_ERROR_INVALID_VALUE:
+        raise InvalidArgumentError("fused_activation rejected its arguments (cudaErrorInvalidValue)")
+    if rc != _b.CUDA_SUCCESS:
+        raise InternalError(f"fused_activation failed: {_b.error_string(rc)}")
+    return out
+
+
+def bias_grad(grad_c: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Gradient of a Dense bias: the column sums of `grad_c` (any leading
+    dimensions are flattened into rows), accumulated in fp32 in a fixed order
+    (``sm120_launch_bias_grad``).  Result dtype: grad_c's, or float32 on request."""
+    _require_available()
+    if not isinstance(grad_c, torch.Tensor) or not grad_c.is_cuda or grad_c.dim() < 1:
+        raise TypeError("bias_grad needs a CUDA tensor of rank >= 1")
+    if grad_c.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"dtype {grad_c.dtype} is not supported (float32, float16, bfloat16)")
+    out_dtype = out_dtype or grad_c.dtype
+    if out_dtype not in (torch.float32, grad_c.dtype):
+        raise ValueError("out_dtype must be float32 or grad_c's dtype")
+    n = grad_c.shape[-1]
+    g = grad_c.reshape(-1, n)
+    if g.stride(-1) != 1 or (g.shape[0] > 1 and g.stride(0) < n):
+        g = g.contiguous()
+    out = torch.empty(n, dtype=out_dtype, device=g.device)
+    ld = g.stride(0) if g.shape[0] > 1 else n
+    with torch.cuda.device(g.device):
+        rc = _b.load_library().sm120_launch_bias_grad(g.data_ptr(), out.data_ptr(), g.shape[0], n, ld, _TORCH_TO_SM120[g.dtype],
+                                                      _TORCH_TO_SM120[out_dtype], torch.cuda.current_stream(g.device).cuda_stream)
+    if rc == _b.CUDA_ERROR_INVALID_VALUE:
+        raise InvalidArgumentError("bias_grad rejected its arguments (cudaErrorInvalidValue)")
+    if rc != _b.CUDA_SUCCESS:
+        raise InternalError(f"bias_grad failed: {_b.error_string(rc)}")
+    return out
+
+
+class _DenseFunction(torch.autograd.Function):
+    """y = relu?(x @ kernel + bias) with this library's kernels in both directions:
+    the fused GEMM forward, SM120MatMulGradA / GradB
+    (src/tensorflow_ops/sm120_gradients.cc:22-55) and the bias column sum backward."""
+
+    @staticmethod
+    def forward(ctx, x, kernel, bias, relu):
+        y = fused_matmul(x, kernel, bias=bias, activation="relu" if relu else None)
+        ctx.save_for_backward(x, kernel, y if relu else None)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, kernel, y = ctx.saved_tensors
+        g = grad_y.contiguous()
+        if y is not None:
+            g = g * (y > 0).to(g.dtype)
+        dx, dk = matmul_grad(g, x, kernel)
+        db = bias_grad(g) if ctx.has_bias else None
+        return dx, dk, db, None
+
+
+def dense_trainable(x: torch.Tensor, kernel: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                    activation: Union[None, str] = None) -> torch.Tensor:
+    """A Dense forward that torch autograd can differentiate through, for training
+    loops like the reference's (tests/integration/test_comprehensive_validation.py:346-434):
+    x [M, in], kernel [in, units], bias [units]; activation None / "linear" / "relu"."""
+    if activation not in (None, "linear", "relu"):
+        raise NotImplementedError("dense_trainable differentiates the linear and relu forms only")
+    return _DenseFunction.apply(x, kernel, bias, activation == "relu")
+
+
+def quantize_fp8(x: torch.Tensor, scale: Optional[torch.Tensor] = None):
     """Per-tensor FP8 quantisation for FP8 matmuls, on the device: returns
     (q, scale) with scale = 448 / amax(x) as a one-element float32 CUDA tensor and
     q = x * scale rounded to e4m3 with saturation
     (type and conversion: src/cuda_kernels/sm120_datatype_support.h:71-82,168-171).
     `scale` can be passed to ``fused_matmul(scale_a=...)`` as it is: nothing is
-    copied to the host."""
+    copied to the host.  When `scale` is given (a one-element float32 CUDA tensor,
+    e.g. 448 / the maximum over every shard of a tensor that is split across GPUs),
+    only the cast runs and that scale is returned."""
     _require_available()
     if not isinstance(x, torch.Tensor) or not x.is_cuda:
         raise TypeError("quantize_fp8 needs a CUDA tensor")
@@ -486,6 +682,18 @@ def quantize_fp8(x: torch.Tensor):
     lib = _b.load_library()
     n = x.numel()
     q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    if scale is not None:
+        if not (isinstance(scale, torch.Tensor) and scale.is_cuda and scale.dtype == torch.float32 and scale.numel() == 1
+                and scale.device == x.device):
+            raise ValueError("scale must be a one-element float32 CUDA tensor on x's device")
+        with torch.cuda.device(x.device):
+            rc = lib.sm120_launch_cast_fp8(x.data_ptr(), _TORCH_TO_SM120[x.dtype], n, scale.data_ptr(), q.data_ptr(),
+                                           torch.cuda.current_stream(x.device).cuda_stream)
+        if rc == _b.CUDA_ERROR_INVALID_VALUE:
+            raise InvalidArgumentError("quantize_fp8 rejected its arguments (cudaErrorInvalidValue)")
+        if rc != _b.CUDA_SUCCESS:
+            raise InternalError(f"quantize_fp8 failed: {_b.error_string(rc)}")
+        return q, scale
     scale = torch.empty(1, dtype=torch.float32, device=x.device)
     nbytes = int(lib.sm120_quantize_fp8_scratch_bytes(n))
     scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)     # the caller's allocator, not the library's
@@ -644,6 +852,9 @@ __all__ = [
     "batched_matmul",
     "fused_matmul",
     "matmul_grad",
+    "bias_grad",
+    "dense_trainable",
+    "fused_activation",
     "quantize_fp8",
     "quantize_fp8_into",
     "SM120Profiler",

@@ -267,9 +267,63 @@ cudaError_t sm120_launch_matmul_grad_b(
     SM120DataType dtype, cudaStream_t stream);
 
 /*
+ * Replaces sm120_launch_activation (src/cuda_kernels/sm120_c_interface.h:95-100,
+ * body src/cuda_kernels/sm120_c_interface.cu:139-164, kernel
+ * src/cuda_kernels/sm120_pure_kernels.cu:128-176) with the same signature:
+ * output[i] = act(input[i]) for `size` elements of `dtype` (FLOAT32 or FLOAT16 as
+ * in the reference, plus BFLOAT16), computed in fp32 and rounded to nearest.
+ * Codes 0..8 are the reference's formulas, 9 is the erf GELU, and any other code
+ * leaves the values unchanged, as the reference kernel's `default:` does.  A
+ * dtype it does not know returns cudaErrorInvalidValue (:160-162).  In place
+ * (output == input) is allowed.  This is the part of a Dense layer that remains
+ * when its activation cannot be fused into the GEMM epilogue; it is bound by
+ * HBM bandwidth (one read and one write of the tensor).
+ */
+cudaError_t sm120_launch_activation(
+    const void* input, void* output,
+    int size,
+    SM120ActivationType activation_type,
+    SM120DataType dtype,
+    cudaStream_t stream);
+
+/*
+ * output[r, c] = act(input[r, c] + bias[c]) over a dense [rows, cols] matrix in one
+ * pass: tf.nn.bias_add followed by the activation
+ * (python/sm120_keras_layers.py:169-172) as ONE HBM-bound kernel, for outputs of
+ * a matmul that was not launched with the fused epilogue.  bias has `cols`
+ * entries of bias_dtype (FLOAT32 / FLOAT16 / BFLOAT16) or is null; sizes are 64-bit.
+ * The reference has the activation launcher only (see above).
+ */
+cudaError_t sm120_launch_bias_activation(
+    const void* input, const void* bias, SM120DataType bias_dtype, void* output,
+    int64_t rows, int64_t cols,
+    SM120ActivationType activation_type,
+    SM120DataType dtype,
+    cudaStream_t stream);
+
+/*
+ * Bias gradient of the Dense layer: grad_bias[n] = sum over m of grad_c[m, n] for a
+ * row-major [M, N] matrix with row pitch ld (elements; 0 = N), accumulated in fp32
+ * in a fixed order (bitwise reproducible; no atomics, no scratch) and written as
+ * out_dtype (FLOAT32, or the same type as grad_c).  It completes the backward
+ * pass next to sm120_launch_matmul_grad_a / _b: the reference's layer adds its
+ * bias with tf.nn.bias_add (python/sm120_keras_layers.py:169), whose gradient is
+ * this column sum; the reference's own gradient ops
+ * (src/tensorflow_ops/sm120_gradients.cc:22-212) cover the two matmuls only.
+ */
+cudaError_t sm120_launch_bias_grad(
+    const void* grad_c, void* grad_bias,
+    int64_t M, int64_t N, int64_t ld,
+    SM120DataType dtype, SM120DataType out_dtype,
+    cudaStream_t stream);
+
+/*
  * Per-tensor FP8 quantisation, the producer of FP8 matmul operands:
  *   *scale_out = 448 / max|x|   (1 for an all-zero tensor)
  *   q[i] = saturate_e4m3(x[i] * *scale_out)      (round-to-nearest-even, finite)
+ * Non-finite input: an infinity enters the maximum as the largest finite float, so
+ * the scale stays positive and finite (the infinity saturates to +-448, finite
+ * values become 0); a NaN is ignored by the maximum and comes out as the e4m3 NaN.
  * x has n elements of x_dtype (FLOAT32, FLOAT16 or BFLOAT16); q receives n bytes;
  * scale_out is one float in device memory and can be passed straight to
  * SM120GemmDesc::scale_a_dev / scale_b_dev.  `scratch` is device memory of at
@@ -286,6 +340,18 @@ cudaError_t sm120_launch_quantize_fp8(
     const void* x, SM120DataType x_dtype, int64_t n,
     void* q, float* scale_out,
     void* scratch, size_t scratch_bytes,
+    cudaStream_t stream);
+
+/*
+ * Only the cast of the quantisation above, with a scale the caller already has:
+ * q[i] = saturate_e4m3(x[i] * *scale), `scale` one float in device memory.  For a
+ * tensor that is sharded over several GPUs, whose scale comes from the maximum
+ * over all shards, so that every rank quantises with the same number.  Needs no
+ * scratch.  No counterpart in the reference (see sm120_launch_quantize_fp8).
+ */
+cudaError_t sm120_launch_cast_fp8(
+    const void* x, SM120DataType x_dtype, int64_t n,
+    const float* scale, void* q,
     cudaStream_t stream);
 
 /*

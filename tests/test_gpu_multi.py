@@ -51,9 +51,19 @@ def _worker(rank, world, port, ret):
             local = sh.local(slab, b_local, **kw)
             full = sh.gathered(slab, b_local, out_dtype=torch.bfloat16, chunks=chunks, **kw)
             bufs = ms.PeerBuffers(sh, torch.bfloat16, torch.device("cuda", rank))
-            fused = sh.gathered_fused(slab, b_local, bufs, **kw).clone()
+            # three steps in a row with different A, none separated by a host synchronisation: each
+            # result is copied out (stream-ordered) before the next call, which is the rule for the
+            # two alternating peer buffers
+            fused = []
+            for step in range(3):
+                a_step = a if step == 0 else (a.float() * 0.5 ** step).to(a.dtype)
+                fused.append(sh.gathered_fused(a_step[sh.start:sh.stop], b_local, bufs, **kw).clone())
             torch.cuda.synchronize()
-            results[name + "_fused"] = bool(tuple(fused.shape) == (M, N) and torch.equal(fused, whole))
+            ok = tuple(fused[0].shape) == (M, N) and torch.equal(fused[0], whole)
+            for step in (1, 2):
+                a_step = (a.float() * 0.5 ** step).to(a.dtype)
+                ok = ok and torch.equal(fused[step], ops.fused_matmul(a_step, b, **kw))
+            results[name + "_fused"] = bool(ok)
             bufs.close()
             del bufs
             results[name] = bool(torch.equal(b_local, b) and torch.equal(local, whole[sh.start:sh.stop])

@@ -88,3 +88,60 @@ def test_two_gloo_ranks_local_and_gathered(M, N, K, chunks):
         p.join(120)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert dict(ret) == {0: True, 1: True}
+
+
+# ----- failure handling, on the host only: a rank that leaves, and a rank that silently stops -----
+def _leaving_worker(rank, world, port, announce, ret):
+    import importlib
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ms = importlib.import_module(PACKAGE_NAME).mshard
+    M, N, K = 256, 32, 16
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randn(M, K, generator=g), torch.randn(K, N, generator=g)
+    sh = ms.MShardedMatmul(M, N, matmul_fn=_cpu_matmul, deadline_s=2.0)
+    slab = a[sh.start:sh.stop]
+    full = sh.gathered(slab, b, out_dtype=torch.float32)                 # step 1: everybody takes part
+    ok1 = torch.equal(full, (a.double() @ b.double()).float())
+    if rank == 1:
+        # step 2 never happens on this rank: with an announcement, or silently
+        if announce:
+            sh.leave()
+        time.sleep(6.0)                                                   # stay alive past rank 0's deadline, then go
+        ret[rank] = ("left", ok1)
+        os._exit(0)
+    t0 = time.perf_counter()
+    outcome = "finished"
+    try:
+        if announce:
+            while not sh.departed() and time.perf_counter() - t0 < 5.0:  # the announcement is a store write away
+                time.sleep(0.01)
+        sh.gathered(slab, b, out_dtype=torch.float32)                    # step 2
+    except ms.PeerLeft:
+        outcome = "peer_left"
+    except ms.CollectiveTimeout:
+        outcome = "timeout"
+    ret[rank] = (outcome, ok1, time.perf_counter() - t0)
+    os._exit(0)                                                           # the group is broken on purpose: skip its teardown
+
+
+@pytest.mark.parametrize("announce", [True, False])
+def test_a_rank_that_leaves_between_steps_is_reported_within_the_deadline(announce):
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, world, port, announce, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    outcome, ok1, elapsed = ret[0]
+    assert ok1 and ret[1] == ("left", True)
+    if announce:
+        assert outcome == "peer_left" and elapsed < 2.0          # seen in the store before anything was launched
+    else:
+        assert outcome == "timeout" and 1.5 < elapsed < 5.5       # the 2 s deadline, not a hang
