@@ -23,7 +23,7 @@ benchmark workload.  `--impl reference` times only the CPU product.
 
 Other workloads (`--workload`): f32_1024, f16_4096_tn, bf16_4096_tn,
 bf16_dense_gelu, bf16_batched_qk, fp8_65536 (M split over the ranks), fp8_8192,
-f32_1024_tf32x3, f32_4096, and the HBM-bound kernels quant_fp8_64m,
+f32_1024_ffma, f32_4096, f32_4096_ffma, and the HBM-bound kernels quant_fp8_64m,
 activation_gelu_64m, bias_grad_8192x11008.  `--trace FILE` also writes the
 launch timeline (SM120_TUNE_TRACE) of one launch of the workload to FILE.
 """
@@ -56,8 +56,9 @@ WORKLOADS = {
     "bf16_batched_qk": dict(M=2048, N=2048, K=128, batch=64, dtype="bf16", layout="nn", oracle_idx=4),
     "fp8_65536":       dict(M=65536, N=8192, K=8192, batch=1, dtype="f8e4m3", layout="tn", sharded=True, oracle_idx=5),
     "fp8_8192":        dict(M=8192, N=8192, K=8192, batch=1, dtype="f8e4m3", layout="tn", oracle_idx=5),
-    "f32_1024_tf32x3": dict(M=1024, N=1024, K=1024, batch=1, dtype="f32", layout="nn", tf32x3=True, oracle_idx=1),
+    "f32_1024_ffma":   dict(M=1024, N=1024, K=1024, batch=1, dtype="f32", layout="nn", ffma=True, oracle_idx=1),
     "f32_4096":        dict(M=4096, N=4096, K=4096, batch=1, dtype="f32", layout="nn", oracle_idx=1),
+    "f32_4096_ffma":   dict(M=4096, N=4096, K=4096, batch=1, dtype="f32", layout="nn", ffma=True, oracle_idx=1),
 }
 AUX_WORKLOADS = ("quant_fp8_64m", "activation_gelu_64m", "bias_grad_8192x11008")
 ALIASES = {"cfg1": "f32_1024", "cfg2": "f16_4096_tn", "cfg2bf16": "bf16_4096_tn", "cfg3": "bf16_dense_gelu",
@@ -122,8 +123,8 @@ def make_device_operands(spec, seed, device, ops, reduce_max=None):
     if dt == "f32":
         a = torch.rand(M, K, generator=g, device=device) * 2 - 1
         b = torch.rand(K, N, generator=g, device=device) * 2 - 1
-        if spec.get("tf32x3"):
-            kw["fp32_tensor_cores"] = True
+        if spec.get("ffma"):
+            kw["use_tensor_cores"] = False          # the exact FFMA kernel instead of 3xTF32 on the tensor cores
     elif spec["name"] in ("f16_4096_tn", "bf16_4096_tn"):
         tdt = torch.float16 if dt == "f16" else torch.bfloat16
         a = (torch.randn(M, K, generator=g, device=device) / K ** 0.5).to(tdt)
@@ -379,6 +380,64 @@ def measure_e2e(torch, ops, spec, sets, kw, steps, warmup):
     return time.perf_counter() - t0, h2d, d2h
 
 
+def pcie_probe(torch, device, nbytes=64 << 20):
+    """Raw copy rates of this GPU's PCIe link with pinned memory (GB/s): host->device alone, device->host
+    alone, and both at once on two streams (each direction's own rate while the other runs)."""
+    h_in = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    h_out = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    d_out = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    s1, s2 = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+
+    def run(up, down, reps=4):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            if up:
+                with torch.cuda.stream(s1):
+                    d_in.copy_(h_in, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s2):
+                    h_out.copy_(d_out, non_blocking=True)
+        torch.cuda.synchronize()
+        return reps * nbytes / (time.perf_counter() - t0) / 1e9
+
+    run(True, True, 1)
+    return {"h2d_gbs": run(True, False), "d2h_gbs": run(False, True), "each_direction_when_both_gbs": run(True, True),
+            "bytes_per_copy": nbytes}
+
+
+def host_overhead(torch, ops, binding, device):
+    """Host time of one launch (microseconds) on a product so small that the GPU is never the bottleneck:
+    through the Python API, and through the C ABI alone (ctypes call with a prepared descriptor)."""
+    import ctypes
+    a = torch.randn(256, 64, device=device).bfloat16()
+    b = torch.randn(64, 256, device=device).bfloat16()
+    out = torch.empty(256, 256, dtype=torch.bfloat16, device=device)
+    n = 2000
+    for _ in range(50):
+        ops.fused_matmul(a, b, out=out)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(n):
+        ops.fused_matmul(a, b, out=out)
+    t_api = time.perf_counter() - t0
+    torch.cuda.synchronize()
+    d = binding.new_desc()
+    d.in_dtype = d.out_dtype = binding.DTYPE_BFLOAT16
+    d.A, d.B, d.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    d.M, d.N, d.K = 256, 256, 64
+    d.stream = torch.cuda.current_stream(device).cuda_stream
+    fn, ref_d = binding.load_library().sm120_launch_matmul_ex, ctypes.byref(d)
+    t0 = time.perf_counter()
+    for _ in range(n):
+        fn(ref_d)
+    t_abi = time.perf_counter() - t0
+    torch.cuda.synchronize()
+    return {"python_api_us": 1e6 * t_api / n, "c_abi_us": 1e6 * t_abi / n,
+            "what": "bf16 256x256x64, 2000 back-to-back launches, host wall-clock of the enqueue loop"}
+
+
 def cublas_yardstick(torch, spec, sets, kw, steps, warmup):
     """torch.matmul (cuBLAS) on the same buffers, same rotation, same events: TFLOP/s, or None where
     torch has no plain matmul for the type.  A yardstick for the bench only; the package never calls it."""
@@ -404,7 +463,7 @@ def side_table(torch, ops, binding, device):
     """Single-GPU TFLOP/s of every benchmark workload (after 3 warm-ups, CUDA events),
     reported beside the headline."""
     table = {}
-    for name in ("f32_1024", "f16_4096_tn", "bf16_4096_tn", "bf16_dense_gelu", "bf16_batched_qk", "fp8_8192", "f32_1024_tf32x3"):
+    for name in ("f32_1024", "f16_4096_tn", "bf16_4096_tn", "bf16_dense_gelu", "bf16_batched_qk", "fp8_8192", "f32_1024_ffma"):
         spec = workload_spec(name, 1)
         try:
             sets, kw = build_sets(torch, ops, spec, device)
@@ -633,9 +692,7 @@ def run_gpu(args, rank, world, local_rank):
     maps0 = binding.tensor_map_stats()
     if sampler:
         sampler.start()
-    t_host0 = time.perf_counter()
     secs = time_device_steps(torch, step_fn, sets, args.steps, args.warmup, barrier)
-    host_secs = time.perf_counter() - t_host0
     if sampler:
         sampler.stop()
     launches = binding.launch_count() - launches0
@@ -667,6 +724,10 @@ def run_gpu(args, rank, world, local_rank):
                "per_rank_ms": e2e_per_rank, "steps": e2e_steps,
                "pcie_gbs_per_gpu": (h2d + d2h) / (e2e_secs / e2e_steps) / 1e9,
                "how": "fused_matmul on pinned host operands: B first, then row chunks of A in / product / C out on three streams"}
+
+    probes = None
+    if not args.lean and rank == 0:
+        probes = {"pcie": pcie_probe(torch, device), "host_overhead": host_overhead(torch, ops, binding, device)}
 
     trace_summary = None
     if args.trace and rank == 0 and kernel.startswith("tc_"):
@@ -730,7 +791,8 @@ def run_gpu(args, rank, world, local_rank):
                              "ms_per_step": cpu_ms},
             "e2e": e2e,
             "gpu_launches": int(launches),
-            "host_us_per_call": 1e6 * host_secs / (args.steps + args.warmup),
+            "host_overhead": probes["host_overhead"] if probes else None,
+            "pcie_probe": probes["pcie"] if probes else None,
             "tensor_maps": {"encoded": maps1[0] - maps0[0], "reused": maps1[1] - maps0[1]},
             "clocks": dict(sampler.summary(), sm_mhz_in_kernel=kernel_mhz) if sampler else None,
             "kernel_status": int(status.value),

@@ -38,6 +38,92 @@ template <> __device__ __forceinline__ float ew_from_float<float>(float v) { ret
 template <> __device__ __forceinline__ __half ew_from_float<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 ew_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// Activation of VEC values with the switch outside the element loop (one formula's code runs per
+// vector).  FAST16: the result will be rounded to a 16-bit type (8 or 11 significand bits), so the
+// exponential-based forms with the hardware exponential and reciprocal (relative error ~1e-6) are
+// exact after rounding in all but a vanishing fraction of cases, and an order of magnitude cheaper
+// than tanhf / expf / logf: without them the transcendental activations are bound by the SM's
+// instruction rate instead of HBM.  fp32 tensors keep the accurate functions.
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+template <int VEC, bool FAST16>
+__device__ __forceinline__ void activate_vec(float (&x)[VEC], int act) {
+    if constexpr (!FAST16) {
+        switch (act) {
+#define SM120_ACT_CASE(CODE) case CODE: _Pragma("unroll") for (int k = 0; k < VEC; ++k) x[k] = apply_activation(x[k], CODE); break;
+            SM120_ACT_CASE(SM120_ACTIVATION_RELU) SM120_ACT_CASE(SM120_ACTIVATION_LEAKY_RELU) SM120_ACT_CASE(SM120_ACTIVATION_ELU)
+            SM120_ACT_CASE(SM120_ACTIVATION_SELU) SM120_ACT_CASE(SM120_ACTIVATION_GELU) SM120_ACT_CASE(SM120_ACTIVATION_SWISH)
+            SM120_ACT_CASE(SM120_ACTIVATION_MISH) SM120_ACT_CASE(SM120_ACTIVATION_TANH) SM120_ACT_CASE(SM120_ACTIVATION_SIGMOID)
+            SM120_ACT_CASE(SM120_ACTIVATION_GELU_ERF)
+#undef SM120_ACT_CASE
+            default: break;
+        }
+    } else {
+        switch (act) {
+            case SM120_ACTIVATION_RELU:
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = fmaxf(0.0f, x[k]);
+                break;
+            case SM120_ACTIVATION_LEAKY_RELU:
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = x[k] > 0.0f ? x[k] : 0.01f * x[k];
+                break;
+            case SM120_ACTIVATION_ELU:
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = x[k] > 0.0f ? x[k] : (__expf(x[k]) - 1.0f);
+                break;
+            case SM120_ACTIVATION_SELU:
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = x[k] > 0.0f ? 1.0507f * x[k] : 1.0507f * 1.67326f * (__expf(x[k]) - 1.0f);
+                break;
+            case SM120_ACTIVATION_GELU:        // 0.5 x (1 + tanh(u)) = x sigmoid(2u)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    const float u = 0.7978845608f * (x[k] + 0.044715f * x[k] * x[k] * x[k]);
+                    x[k] = x[k] * fast_sigmoid(2.0f * u);
+                }
+                break;
+            case SM120_ACTIVATION_SWISH:
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = x[k] * fast_sigmoid(x[k]);
+                break;
+            case SM120_ACTIVATION_MISH:        // tanh(log(1 + e^x)) = n / (n + 2) with n = e^x (e^x + 2)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    const float w = __expf(fminf(x[k], 20.0f));
+                    const float n = w * (w + 2.0f);
+                    x[k] = x[k] * __fdividef(n, n + 2.0f);
+                }
+                break;
+            case SM120_ACTIVATION_TANH:        // tanh(x) = 2 sigmoid(2x) - 1
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = fmaf(2.0f, fast_sigmoid(2.0f * x[k]), -1.0f);
+                break;
+            case SM120_ACTIVATION_SIGMOID:
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = fast_sigmoid(x[k]);
+                break;
+            case SM120_ACTIVATION_GELU_ERF:    // Abramowitz-Stegun 7.1.26 erf, |error| <= 1.5e-7
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    const float z = x[k] * 0.70710678118654752440f;
+                    const float az = fabsf(z);
+                    const float t = __fdividef(1.0f, fmaf(0.3275911f, az, 1.0f));
+                    float poly = 1.061405429f;
+                    poly = fmaf(poly, t, -1.453152027f);
+                    poly = fmaf(poly, t, 1.421413741f);
+                    poly = fmaf(poly, t, -0.284496736f);
+                    poly = fmaf(poly, t, 0.254829592f);
+                    poly *= t;
+                    const float erf_abs = fmaf(-poly, __expf(-az * az), 1.0f);
+                    x[k] = 0.5f * x[k] * (1.0f + copysignf(erf_abs, z));
+                }
+                break;
+            default: break;
+        }
+    }
+}
+
 // out[i] = act(in[i] + bias[i % cols]) over n elements; bias may be null (then cols is unused).
 // The vector path needs in/out 16-byte aligned and, with a bias, cols a multiple of the
 // vector length (so a vector never straddles a row); the launcher checks and passes vec = 0 otherwise.
@@ -72,21 +158,25 @@ sm120_activation_kernel(const T* __restrict__ in, T* __restrict__ out, long long
                 if (col >= cols) col -= cols;
                 if (i >= nvec) continue;
                 T* e = reinterpret_cast<T*>(&w[u]);
+                float x[VEC];
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
-                    float x = ew_to_float<T>(e[k]);
-                    if (bias != nullptr) x += ew_to_float<TB>(__ldg(bias + col0 + k));
-                    e[k] = ew_from_float<T>(apply_activation(x, act));
+                    x[k] = ew_to_float<T>(e[k]);
+                    if (bias != nullptr) x[k] += ew_to_float<TB>(__ldg(bias + col0 + k));
                 }
+                activate_vec<VEC, sizeof(T) == 2>(x, act);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) e[k] = ew_from_float<T>(x[k]);
                 __stcs(ov + i, w[u]);
             }
         }
         done = nvec * VEC;
     }
     for (long long i = done + tid; i < n; i += nthreads) {
-        float x = ew_to_float<T>(in[i]);
-        if (bias != nullptr) x += ew_to_float<TB>(bias[i % cols]);
-        out[i] = ew_from_float<T>(apply_activation(x, act));
+        float x[1] = {ew_to_float<T>(in[i])};
+        if (bias != nullptr) x[0] += ew_to_float<TB>(bias[i % cols]);
+        activate_vec<1, sizeof(T) == 2>(x, act);
+        out[i] = ew_from_float<T>(x[0]);
     }
 }
 
@@ -131,32 +221,54 @@ cudaError_t activation_launch(const void* in, void* out, long long n, const void
 // ---------------------------------------------------------------------------
 // Bias gradient: grad_bias[n] = sum over m of grad_c[m, n], fp32 accumulation in a
 // fixed order (bitwise reproducible, no atomics, no scratch memory).
-// One block owns a strip of STRIP columns for all rows.  A strip row is STRIP * sizeof(T)
-// contiguous bytes, fetched by LANES threads with one 16-byte load each; the block's 256
-// threads therefore cover 256 / LANES rows per step, each thread keeps 16 / sizeof(T) fp32
-// partial sums, and the row groups are added in shared memory at the end.
+// A thread-block CLUSTER of up to 8 CTAs owns a strip of STRIP columns: CTA r of the
+// cluster sums the rows r * M / csize .. (r + 1) * M / csize of the strip, the partial sums
+// meet in distributed shared memory, and CTA 0 adds them in rank order and writes the
+// result.  The row split is what puts enough CTAs (strips x 8) and loads in flight to
+// approach HBM bandwidth on a matrix with few column strips; the fixed order keeps it
+// deterministic.  Inside a CTA a strip row is STRIP * sizeof(T) contiguous bytes fetched by
+// LANES threads with one 16-byte load each; the 256 threads cover 256 / LANES rows per step.
 // ---------------------------------------------------------------------------
+constexpr int BG_LANES = 8;                       // threads per strip row
+constexpr int BG_ROWS = EW_THREADS / BG_LANES;    // 32 rows per step
+constexpr int BG_MAX_CLUSTER = 8;
+
+__device__ __forceinline__ uint32_t bg_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t bg_cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(EW_THREADS)
 sm120_bias_grad_kernel(const T* __restrict__ g, long long M, long long N, long long ld, float* __restrict__ out_f32,
                        T* __restrict__ out_t, int vec) {
     constexpr int VEC = 16 / sizeof(T);
-    constexpr int LANES = 8;                        // threads per strip row
-    constexpr int STRIP = LANES * VEC;              // columns per block: 32 fp32 or 64 16-bit
-    constexpr int ROWS = EW_THREADS / LANES;        // 32 rows per step
-    __shared__ float part[ROWS][STRIP + 1];
-    const int lane = threadIdx.x % LANES;
-    const int rgrp = threadIdx.x / LANES;
+    constexpr int STRIP = BG_LANES * VEC;           // columns per cluster: 32 fp32 or 64 16-bit
+    __shared__ float part[BG_ROWS][STRIP + 1];
+    __shared__ float strip_sum[STRIP];              // this CTA's partial column sums, read by CTA 0 of the cluster
+    const uint32_t crank = bg_cluster_rank(), csize = bg_cluster_size();
+    const int lane = threadIdx.x % BG_LANES;
+    const int rgrp = threadIdx.x / BG_LANES;
     const long long col0 = static_cast<long long>(blockIdx.x) * STRIP + lane * VEC;
+    // this CTA's rows: a contiguous share, in whole steps of BG_ROWS
+    const long long steps = (M + BG_ROWS - 1) / BG_ROWS;
+    const long long m_begin = (steps * crank / csize) * BG_ROWS;
+    const long long m_end = min(M, (steps * (crank + 1) / csize) * BG_ROWS);
     float acc[VEC];
 #pragma unroll
     for (int k = 0; k < VEC; ++k) acc[k] = 0.0f;
     if (vec && col0 + VEC <= N) {
-        long long m = rgrp;
-        for (; m + 7 * ROWS < M; m += 8 * ROWS) {                      // eight rows in flight per thread
+        long long m = m_begin + rgrp;
+        for (; m + 7 * BG_ROWS < m_end; m += 8 * BG_ROWS) {                      // eight rows in flight per thread
             uint4 w[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) w[u] = __ldcs(reinterpret_cast<const uint4*>(g + (m + u * ROWS) * ld + col0));
+            for (int u = 0; u < 8; ++u) w[u] = __ldcs(reinterpret_cast<const uint4*>(g + (m + u * BG_ROWS) * ld + col0));
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const T* e = reinterpret_cast<const T*>(&w[u]);
@@ -164,14 +276,14 @@ sm120_bias_grad_kernel(const T* __restrict__ g, long long M, long long N, long l
                 for (int k = 0; k < VEC; ++k) acc[k] += ew_to_float<T>(e[k]);
             }
         }
-        for (; m < M; m += ROWS) {
+        for (; m < m_end; m += BG_ROWS) {
             const uint4 w = __ldcs(reinterpret_cast<const uint4*>(g + m * ld + col0));
             const T* e = reinterpret_cast<const T*>(&w);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) acc[k] += ew_to_float<T>(e[k]);
         }
     } else {
-        for (long long m = rgrp; m < M; m += ROWS) {
+        for (long long m = m_begin + rgrp; m < m_end; m += BG_ROWS) {
 #pragma unroll
             for (int k = 0; k < VEC; ++k)
                 if (col0 + k < N) acc[k] += ew_to_float<T>(g[m * ld + col0 + k]);
@@ -181,28 +293,59 @@ sm120_bias_grad_kernel(const T* __restrict__ g, long long M, long long N, long l
     for (int k = 0; k < VEC; ++k) part[rgrp][lane * VEC + k] = acc[k];
     __syncthreads();
     if (threadIdx.x < STRIP) {
-        const long long col = static_cast<long long>(blockIdx.x) * STRIP + threadIdx.x;
-        if (col < N) {
-            float s = 0.0f;
+        float s = 0.0f;
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) s += part[r][threadIdx.x];
+        for (int r = 0; r < BG_ROWS; ++r) s += part[r][threadIdx.x];
+        strip_sum[threadIdx.x] = s;
+    }
+    // every CTA's strip_sum is complete and visible cluster-wide after this barrier
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (crank == 0 && threadIdx.x < STRIP) {
+        const long long col = static_cast<long long>(blockIdx.x) * STRIP + threadIdx.x;
+        float s = strip_sum[threadIdx.x];
+        const uint32_t mine = static_cast<uint32_t>(__cvta_generic_to_shared(&strip_sum[threadIdx.x]));
+        for (uint32_t r = 1; r < csize; ++r) {          // rank order: a fixed summation order
+            uint32_t remote;
+            float v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(r));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+            s += v;
+        }
+        if (col < N) {
             if (out_f32 != nullptr) out_f32[col] = s;
             else out_t[col] = ew_from_float<T>(s);
         }
     }
+    // no CTA may exit while CTA 0 still reads its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 template <typename T>
 static cudaError_t bias_grad_typed(const void* g, long long M, long long N, long long ld, void* out, int out_dtype, cudaStream_t stream) {
     constexpr int VEC = 16 / sizeof(T);
-    constexpr int STRIP = 8 * VEC;
+    constexpr int STRIP = BG_LANES * VEC;
     const int vec = ((reinterpret_cast<uintptr_t>(g) & 15u) == 0 && (ld * sizeof(T)) % 16 == 0) ? 1 : 0;
-    const long long blocks = (N + STRIP - 1) / STRIP;
-    if (blocks > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+    const long long strips = (N + STRIP - 1) / STRIP;
+    if (strips > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+    // rows are split over a cluster when there are enough of them to give every CTA several steps
+    int csize = 1;
+    while (csize < BG_MAX_CLUSTER && M >= static_cast<long long>(csize) * 2 * 8 * BG_ROWS) csize *= 2;
     float* of = out_dtype == SM120_DTYPE_FLOAT32 ? static_cast<float*>(out) : nullptr;
     T* ot = out_dtype == SM120_DTYPE_FLOAT32 ? nullptr : static_cast<T*>(out);
-    sm120_bias_grad_kernel<T><<<static_cast<unsigned>(blocks), EW_THREADS, 0, stream>>>(static_cast<const T*>(g), M, N, ld, of, ot, vec);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(strips), static_cast<unsigned>(csize), 1);
+    cfg.blockDim = dim3(EW_THREADS, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = static_cast<unsigned>(csize);
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, sm120_bias_grad_kernel<T>, static_cast<const T*>(g), M, N, ld, of, ot, vec);
 }
 
 // out_dtype is FLOAT32 or the input dtype.

@@ -22,16 +22,16 @@ __device__ unsigned long long g_sm120_probe[2];
 
 // the variants are compiled in gemm_tcgen05_inst_*.cu
 #define SM120_TC_EXTERN(KIND_, BN_, ST_, CG_) \
-    extern template cudaError_t launch_variant<KIND_, BN_, ST_, CG_>(const CUtensorMap&, const CUtensorMap&, const DestMaps&, \
+    extern template cudaError_t launch_variant<KIND_, BN_, ST_, CG_>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&, \
                                                                      const TcParams&, int, int, cudaStream_t, bool);
 SM120_TC_EXTERN(KIND_F16, 256, 6, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
 SM120_TC_EXTERN(KIND_F8, 256, 6, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
-SM120_TC_EXTERN(KIND_TF32, 256, 6, 2) SM120_TC_EXTERN(KIND_TF32, 256, 4, 1) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
+SM120_TC_EXTERN(KIND_TF32, 128, 8, 2) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
 #undef SM120_TC_EXTERN
 // the pair tile with 16 epilogue warps, for short-K (store-bound) problems
-extern template cudaError_t launch_variant<KIND_F16, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+extern template cudaError_t launch_variant<KIND_F16, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
                                                                     const TcParams&, int, int, cudaStream_t, bool);
-extern template cudaError_t launch_variant<KIND_F8, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+extern template cudaError_t launch_variant<KIND_F8, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
                                                                    const TcParams&, int, int, cudaStream_t, bool);
 
 // ---------------------------------------------------------------------------
@@ -174,6 +174,9 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     // 128 x 128.  An MN-major operand is loaded in boxes of 128 bytes of M/N, so a
     // CTA's share of the B tile cannot be narrower than one box (128 fp8 elements).
     const int min_bn = (b_mn && es == 1) ? 128 : 64;
+    // fp32 (3xTF32) tiles are at most 128 columns wide: the epilogue keeps a tile's running sums in registers
+    const bool fp32 = p.in_dtype == SM120_DTYPE_FLOAT32;
+    const int pair_bn = fp32 ? 128 : 256;
     auto tiles_for = [&](int bm, int bn) { return ((p.M + bm - 1) / bm) * ((p.N + bn - 1) / bn) * p.batch; };
     int cg = 1, bn = min_bn;
     // per-call overrides (SM120GemmDesc::tuning): 0 = choose, 1 / 2 = force
@@ -181,11 +184,12 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     if (p.optimization_level == 0) {
         bn = p.N > 64 ? 128 : min_bn;
     } else {
-        if (force != 1 && p.M > 128 && p.N > 128 && (force == 2 || tiles_for(256, 256) * 6 >= p.sm_count)) {
-            cg = 2; bn = 256;
+        if (force != 1 && p.M > 128 && p.N > pair_bn / 2 && (force == 2 || tiles_for(256, pair_bn) * 6 >= p.sm_count)) {
+            cg = 2; bn = pair_bn;
         } else {
             const int wide[2] = {256, 128};
             for (int cand : wide) {
+                if (cand > pair_bn) continue;
                 if (p.N > cand / 2 && tiles_for(BM, cand) >= p.sm_count) { bn = cand; break; }
             }
         }
@@ -197,6 +201,9 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.tiles_m = static_cast<int>((p.M + BM * cg - 1) / (BM * cg));
     tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
     tp.k_blocks = static_cast<int>((p.K + bk - 1) / bk);
+    // fp32 path: the tensor cores' fp32 accumulation truncates, so a sum is carried in TMEM for 8 k-blocks
+    // (256 tf32 products) only and the runs are added in registers with round-to-nearest (see epilogue_role)
+    tp.kb_per_run = fp32 ? 8 : tp.k_blocks;
     // Epilogue warps: with at most 8 k-blocks per tile the MMAs of a tile take less time than
     // its epilogue, and 16 epilogue warps (pair tiles only) hide the epilogue's latencies.
     // The same variant also serves the transcendental activations at any K: with GELU fused, 16 warps of 96
@@ -273,7 +280,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 
     tp.idesc_half = (tp.idesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>((bn / 2) >> 3) << 17);
 
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tb_half;
     DestMaps tc;
     const int64_t nb_a = tp.a_batched ? p.batch : 1;
     const int64_t nb_b = tp.b_batched ? p.batch : 1;
@@ -285,6 +292,21 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     if (!b_mn) ok = encode_3d(&tb, p.B, p.in_dtype, p.K, p.N, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.N * p.ldb, bk, bn_cta, CU_TENSOR_MAP_SWIZZLE_128B);
     else       ok = encode_3d(&tb, p.B, p.in_dtype, p.N, p.K, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.K * p.ldb, epb, bk, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
+    // Half-width tiles of a short last wave (pair tiles only) load half of a CTA's share of B
+    tb_half = tb;
+    tp.b_bytes_half = bn_cta * 128u;
+    tp.b_boxes_half = static_cast<int>(bn_cta) / epb;
+    if (cg == 2) {
+        if (!b_mn) {
+            ok = encode_3d(&tb_half, p.B, p.in_dtype, p.K, p.N, nb_b, p.ldb, tp.b_batched ? p.stride_b : p.N * p.ldb, bk, bn_cta / 2,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+            if (!ok) return cudaErrorInvalidValue;
+            tp.b_bytes_half = (bn_cta / 2) * 128u;
+        } else if (static_cast<int>(bn_cta) / 2 >= epb) {
+            tp.b_boxes_half = static_cast<int>(bn_cta) / 2 / epb;
+            tp.b_bytes_half = static_cast<uint32_t>(tp.b_boxes_half) * static_cast<uint32_t>(bk) * 128u;
+        }
+    }
     // One TMA store writes the 32 rows of one epilogue warp x epi_cols columns: as many columns
     // as fit a 128-byte staging row, but not more than one epilogue warp owns (bn / 2, or bn / 4 with 16 warps).
     tp.epi_cols = (bn / (ew / 4) >= 64 && out_es == 2) ? 64 : 32;
@@ -312,20 +334,19 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 #define SM120_TC_CASE(KIND_, BN_, ST_, CG_, NAME_)                                                       \
     do {                                                                                                 \
         if (kernel_name) *kernel_name = NAME_;                                                           \
-        return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tc, tp, p.sm_count, p.device, p.stream, split_tail);       \
+        return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail);       \
     } while (0)
 
     if (p.in_dtype == SM120_DTYPE_FLOAT32) {
         // operands already split into tf32 pieces (see split_tf32.cu)
-        if (cg == 2) SM120_TC_CASE(KIND_TF32, 256, 6, 2, "tc_tf32x3_2cta_256x256x32_s6");
-        if (bn == 256) SM120_TC_CASE(KIND_TF32, 256, 4, 1, "tc_tf32x3_128x256x32_s4");
+        if (cg == 2) SM120_TC_CASE(KIND_TF32, 128, 8, 2, "tc_tf32x3_2cta_256x128x32_s8");
         if (bn == 128) SM120_TC_CASE(KIND_TF32, 128, 6, 1, "tc_tf32x3_128x128x32_s6");
         SM120_TC_CASE(KIND_TF32, 64, 8, 1, "tc_tf32x3_128x64x32_s8");
     } else if (!fp8) {
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
         if (cg == 2 && ew == 16) {
             if (kernel_name) *kernel_name = bf ? "tc_bf16_2cta_256x256x64_s5_e16" : "tc_f16_2cta_256x256x64_s5_e16";
-            return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream, split_tail);
+            return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail);
         }
         if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 6, 2, bf ? "tc_bf16_2cta_256x256x64_s6" : "tc_f16_2cta_256x256x64_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
@@ -334,7 +355,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     } else {
         if (cg == 2 && ew == 16) {
             if (kernel_name) *kernel_name = "tc_e4m3_2cta_256x256x128_s5_e16";
-            return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tc, tp, p.sm_count, p.device, p.stream, split_tail);
+            return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail);
         }
         if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 6, 2, "tc_e4m3_2cta_256x256x128_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, 1, "tc_e4m3_128x256x128_s4");

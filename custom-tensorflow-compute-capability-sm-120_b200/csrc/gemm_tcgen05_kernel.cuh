@@ -104,6 +104,7 @@ __device__ __forceinline__ int fast_div(int n, const FastDiv& f) {
 struct TcParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, k_blocks, num_tiles;   // tiles are (CG*128) x BN
+    int kb_per_run;                 // k-blocks summed in TMEM before the epilogue takes the partial sum (k_blocks: one run per tile)
     int group_m;                    // row tiles per raster group (tiles of a group share their B columns in L2)
     FastDiv div_per_batch;          // tiles_m * tiles_n
     FastDiv div_group_span;         // group_m * tiles_n
@@ -112,6 +113,8 @@ struct TcParams {
     int num_work, full_work;        // work items: [0, full_work) are whole tiles, the rest are half-width tiles (two per tile)
     uint32_t idesc;
     uint32_t idesc_half;            // instruction descriptor of a half-width tile (N = BN / 2)
+    uint32_t b_bytes_half;          // bytes of B one CTA loads per k-block of a half-width tile
+    int b_boxes_half;               // MN-major B: 128-byte boxes of N per CTA in a half-width tile
     int a_mn_major, b_mn_major;
     int a_batched, b_batched;
     void* C;
@@ -650,6 +653,11 @@ struct TileCfg {
     static_assert(SMEM > 116224, "one CTA per SM is assumed: shared memory must exceed half of an SM's");
 };
 
+// General epilogue: any N, beta, output alignment; and the run-wise accumulation of the fp32
+// (3xTF32) path.  There a tile's K range is cut into runs of TcParams::kb_per_run k-blocks; the
+// tensor cores sum one run in TMEM (their fp32 accumulation truncates, so the error of a run grows
+// with its length), this role adds the runs in registers with round-to-nearest fp32 adds, and
+// the two TMEM buffers alternate between runs so the adds overlap the next run's MMAs.
 template <int KIND, int BN, int STAGES, int CG, int EW, int ACTC>
 __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps* dests, const WaitCtx& wctx,
                                               uint32_t tmem_base, uint32_t acc_full_bar, uint32_t acc_empty_addr,
@@ -657,9 +665,11 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
                                               int tile_step) {
     constexpr int EPI_BUFS = TileCfg<KIND, BN, STAGES, CG, EW>::EPI_BUFS;
     constexpr int NSPLIT = EW / 4;
+    constexpr bool RUNS = KIND == KIND_TF32;  // several accumulation runs per tile, summed here
     const int lane_group = warp & 3;          // TMEM lanes [32*lane_group, +32) belong to this warp
     const int half = (warp - 2) >> 2;         // which part (half or quarter) of the tile's columns
     constexpr int CHUNKS = BN / (32 * NSPLIT); // 32-column chunks per warp in a whole tile
+    static_assert(!RUNS || CHUNKS <= 2, "the run sums of the fp32 path live in registers: at most 64 columns per thread");
     float alpha = p.alpha;
     if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
     if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
@@ -667,12 +677,10 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
     const int spg = p.epi_cols >> 5;                    // 32-column chunks per TMA store: 1 or 2
     const int chunk16_per_sub = (p.out_dtype == SM120_DTYPE_FLOAT32) ? 8 : 4;
     uint32_t stores = 0;                                // TMA stores committed by this warp: picks the staging buffer
-    int local = 0;
-    for (int tile = first_tile; tile < p.num_work; tile += tile_step, ++local) {
+    uint32_t acc_iter = 0;                              // accumulation runs consumed so far: picks the TMEM buffer and the phase
+    for (int tile = first_tile; tile < p.num_work; tile += tile_step) {
         int bz, tm, n0, width;
         decode_work(tile, p, BN, bz, tm, n0, width);
-        const uint32_t buf = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
         const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
         const int row = row0 + lane;
         const int cols_per_warp = width / NSPLIT;
@@ -683,23 +691,49 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
         // the first chunk's bias is fetched before the wait for the accumulator
         if (has_bias && p.bias_vec_ok && nvalid > 0 && colbase + 32 <= p.N) bias_prefetch32(p, colbase, braw);
 
-        bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
-        ok = __all_sync(0xFFFFFFFFu, ok);
-        if (!ok) break;
-        tcgen05_fence_after();
+        constexpr int SUMC = RUNS ? CHUNKS : 1;
+        float sum[SUMC][32];
+        uint32_t buf = acc_iter & 1u;
+        if constexpr (RUNS) {
+            bool ok = true;
+            for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.kb_per_run, ++acc_iter) {
+                buf = acc_iter & 1u;
+                ok = mbar_wait(acc_full_bar + 8 * buf, (acc_iter >> 1) & 1u, wctx, 0x31000000u);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t t_run = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * cols_per_warp;
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) {
+                    if (c < nvalid) {
+                        uint32_t part[32];
+                        __syncwarp();
+                        tmem_ld_32x32_sync(t_run + c * 32, part);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            sum[c][j] = (kb0 == 0) ? __uint_as_float(part[j]) : __fadd_rn(sum[c][j], __uint_as_float(part[j]));
+                    }
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
+            }
+            if (!ok) break;
+        } else {
+            bool ok = mbar_wait(acc_full_bar + 8 * buf, (acc_iter >> 1) & 1u, wctx, 0x31000000u);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            ++acc_iter;
+        }
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + half * cols_per_warp;
 
-        // Drain: up to PRE loads of 32 columns are in flight at once, so the TMEM latency is
-        // paid about once per tile, and the buffer goes back to the MMA role as soon as the
-        // last load has landed (before the values are processed).
-        constexpr int PRE = 0;                  // this path is register-heavy: load and wait in one step
-        constexpr int MODP = PRE > 0 ? PRE : 1;
-        uint32_t acc[MODP][32];
+        // (this path is register-heavy: every TMEM load and its wait are one step)
+        uint32_t acc[1][32];
+        constexpr int MODP = 1;
+        constexpr int PRE = 0;
         __syncwarp();
-#pragma unroll
-        for (int c = 0; c < PRE; ++c)
-            if (c < nvalid) tmem_ld_32x32(t_row + c * 32, acc[c]);
-        if (nvalid == 0) {
+        if (!RUNS && nvalid == 0) {
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
@@ -710,8 +744,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
             if (c < nvalid) {                               // warp-uniform
                 const int col0 = colbase + c * 32;
                 const int ncols = min(32, p.N - col0);
-                // loads were issued before step 0 and at every step s with s + PRE < nvalid
-                if constexpr (PRE == 0) {
+                if constexpr (!RUNS) {
                     __syncwarp();
                     tmem_ld_32x32_sync(t_row + c * 32, acc[0]);
                     if (c == nvalid - 1) {                  // nothing more to load: hand the TMEM buffer back
@@ -719,22 +752,16 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
                     }
-                } else if (c == 0 || (c - 1 + PRE < CHUNKS && c - 1 + PRE < nvalid)) {
-#pragma unroll
-                    for (int q = 0; q < PRE; ++q) tmem_ld_wait_regs(acc[q]);
-                    if (c + PRE >= nvalid) {                // nothing more to load: hand the TMEM buffer back
-                        tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
-                    }
                 }
                 float v[32];
+                if constexpr (RUNS) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[c % MODP][j]);
-                if (PRE > 0 && c + PRE < CHUNKS && c + PRE < nvalid) {
-                    __syncwarp();
-                    tmem_ld_32x32(t_row + (c + PRE) * 32, acc[c % MODP]);    // in flight while this chunk is processed
+                    for (int j = 0; j < 32; ++j) v[j] = alpha * sum[c < SUMC ? c : 0][j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[c % MODP][j]);
                 }
+                (void)PRE;
                 const long long off = static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0;
                 if (p.beta != 0.0f && row < p.M) {
 #pragma unroll
@@ -949,6 +976,7 @@ template <int KIND, int BN, int STAGES, int CG, int EW>
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                           const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_b_half,
                           const __grid_constant__ DestMaps dests,
                           const TcParams p) {
     using Cfg = TileCfg<KIND, BN, STAGES, CG, EW>;
@@ -995,6 +1023,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fence_proxy_async_smem();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        if (p.num_work > p.full_work) prefetch_tmap(&tmap_b_half);
         prefetch_tmap(&dests.m[0]);
     }
     if (warp == 1) {
@@ -1038,9 +1067,12 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int za = p.a_batched ? bz : 0;
             const int zb = p.b_batched ? bz : 0;
             const int m0 = (tm * CG + static_cast<int>(cta_rank)) * BM;
-            // this CTA's share of the tile's columns (a half-width tile still loads a full
-            // box of BN_CTA rows of B; the MMA reads only the first width / CG of them)
+            // this CTA's share of the tile's columns; a half-width tile loads only the rows of B that its
+            // MMAs read (a box of half the height, or fewer boxes), which is what keeps the short last
+            // wave from being bound by the bytes it pulls out of L2
             const int n0 = nt + static_cast<int>(cta_rank) * (width / CG);
+            const bool half_item = tile >= p.full_work;
+            const uint32_t stage_tx = half_item ? (A_BYTES + p.b_bytes_half) : STAGE_BYTES;
             for (int kb = 0; kb < p.k_blocks; ++kb) {
                 if (first && kb == p.stall_kblock) { ok = false; break; }
                 bool w = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u);
@@ -1048,7 +1080,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (!w) { ok = false; break; }
                 if (elect_one_sync()) {
                     // transaction bytes of the whole pair are expected on the leader's barrier
-                    if (leader) mbar_expect_tx(full_bar + 8 * stage, STAGE_BYTES * CG);
+                    if (leader) mbar_expect_tx(full_bar + 8 * stage, stage_tx * CG);
                     const uint32_t fb = full_for_tma + 8 * stage;
                     const uint32_t a_dst = smem_u32(smem) + stage * STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_BYTES;
@@ -1061,11 +1093,12 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             tma_load_3d<CG>(a_dst + j * MN_BOX_BYTES, &tmap_a, fb, m0 + j * EPB, k0, za);
                     }
                     if (!p.b_mn_major) {
-                        tma_load_3d<CG>(b_dst, &tmap_b, fb, k0, n0, zb);
+                        tma_load_3d<CG>(b_dst, half_item ? &tmap_b_half : &tmap_b, fb, k0, n0, zb);
                     } else {
+                        const int boxes = half_item ? p.b_boxes_half : BN_CTA / EPB;
 #pragma unroll
                         for (int j = 0; j < BN_CTA / EPB; ++j)
-                            tma_load_3d<CG>(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, n0 + j * EPB, k0, zb);
+                            if (j < boxes) tma_load_3d<CG>(b_dst + j * MN_BOX_BYTES, &tmap_b, fb, n0 + j * EPB, k0, zb);
                     }
                 }
                 __syncwarp();
@@ -1101,16 +1134,34 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             bool ok = true;
             bool issued_any = false;
             int local = 0;
+            uint32_t acc_iter = 0;                          // accumulation runs issued so far: picks the TMEM buffer and the phase
             for (int tile = first_tile; ok && tile < p.num_work; tile += tile_step, ++local) {
                 const uint32_t idesc = tile < p.full_work ? p.idesc : p.idesc_half;
-                const uint32_t buf = local & 1;
-                const uint32_t acc_phase = (local >> 1) & 1;
-                bool w = mbar_wait(acc_empty_bar + 8 * buf, acc_phase ^ 1u, wctx, 0x21000000u);
-                w = __all_sync(0xFFFFFFFFu, w);
-                if (!w) { ok = false; break; }
-                tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                uint32_t buf = acc_iter & 1u;
+                uint32_t d_tmem = tmem_base + buf * BN;
+                int run_left = 0;                           // k-blocks left in the current accumulation run
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    bool w;
+                    if (run_left == 0) {
+                        // a new run (the only one of the tile, except on the fp32 path): its TMEM buffer must be free
+                        if (kb != 0) {
+                            if (elect_one_sync()) {         // the previous run is complete, in both CTAs of a pair
+                                umma_commit<CG>(acc_full_bar + 8 * buf);
+                                if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
+                            }
+                            __syncwarp();
+                            ++acc_iter;
+                        }
+                        buf = acc_iter & 1u;
+                        d_tmem = tmem_base + buf * BN;
+                        w = mbar_wait(acc_empty_bar + 8 * buf, ((acc_iter >> 1) & 1u) ^ 1u, wctx, 0x21000000u);
+                        w = __all_sync(0xFFFFFFFFu, w);
+                        if (!w) { ok = false; break; }
+                        tcgen05_fence_after();
+                        run_left = p.kb_per_run;
+                    }
+                    const bool run_start = run_left == p.kb_per_run;
+                    --run_left;
                     w = mbar_wait(full_bar + 8 * stage, phase, wctx, 0x22000000u);
                     w = __all_sync(0xFFFFFFFFu, w);
                     if (!w) { ok = false; break; }
@@ -1123,7 +1174,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                             const uint64_t a_desc = desc_hi | (a_lo0 + soff + kk * a_kstep);
                             const uint64_t b_desc = desc_hi | (b_lo0 + soff + kk * b_kstep);
-                            umma_ss<KIND, CG>(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            umma_ss<KIND, CG>(d_tmem, a_desc, b_desc, idesc, (run_start && kk == 0) ? 0u : 1u);
                         }
                         // free the stage, in both CTAs of a pair, when these MMAs retire
                         umma_commit<CG>(empty_bar + 8 * stage);
@@ -1138,6 +1189,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
                 }
                 __syncwarp();
+                ++acc_iter;
                 if (p.trace != nullptr && lane == 0 && local < TRACE_TILES)
                     p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 1] = clock64();
             }
@@ -1160,7 +1212,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         case SM120_ACTIVATION_GELU_ERF: epilogue_fast<KIND, BN, STAGES, CG, EW, ACTC_GELU_ERF, OUTK>(SM120_EPI_ARGS); break; \
         default:                        epilogue_fast<KIND, BN, STAGES, CG, EW, ACTC_DYNAMIC, OUTK>(SM120_EPI_ARGS); break;  \
     }
-        if (p.fast_epi) {
+        if (p.fast_epi && KIND != KIND_TF32) {
             if (p.out_dtype == SM120_DTYPE_FLOAT32) { SM120_EPI_FAST(OUT32) } else { SM120_EPI_FAST(OUT16) }
         } else {
             epilogue_role<KIND, BN, STAGES, CG, EW, ACTC_DYNAMIC>(SM120_EPI_ARGS);
@@ -1201,8 +1253,8 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // parallel; gemm_tcgen05.cu only declares them.
 // ---------------------------------------------------------------------------
 template <int KIND, int BN, int STAGES, int CG, int EW = 8>
-cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DestMaps& tc, const TcParams& tp,
-                                  int sm_count, int device, cudaStream_t stream, bool split_tail) {
+cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb_half, const DestMaps& tc,
+                           const TcParams& tp, int sm_count, int device, cudaStream_t stream, bool split_tail) {
     using Cfg = TileCfg<KIND, BN, STAGES, CG, EW>;
     static std::atomic<uint64_t> attr_done{0};     // one bit per device
     static std::atomic<int> max_clusters[64];      // CG == 2: co-resident clusters per device (0 = not asked yet)
@@ -1248,12 +1300,12 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const D
             t.full_work = tp.num_tiles - rest;
             t.num_work = t.full_work + 2 * rest;
         }
-        return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, t);
+        return cudaLaunchKernelEx(&cfg, kern, ta, tb, tb_half, tc, t);
     } else {
         const int want = tp.num_tiles < sm_count ? tp.num_tiles : sm_count;
         cfg.gridDim = dim3(static_cast<unsigned>(want), 1, 1);
     }
-    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tp);
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tb_half, tc, tp);
 }
 
 

@@ -155,14 +155,24 @@ cudaError_t launch_resolved(GemmProblem& p, int path, void* workspace = nullptr,
 
     const char* why = nullptr;
     const char* name = "";
-    if (p.in_dtype == SM120_DTYPE_FLOAT32 && path == SM120_PATH_TENSOR_CORE) {
-        // FP32 on the tensor cores is opt-in only: the tensor core's fp32 accumulation truncates, so the
-        // 3xTF32 result drifts from the exact one by about K * 2^-27 (1.2e-5 at K = 1024), which is
-        // outside the op's 1e-5 gate.  AUTO therefore keeps FP32 on the exact FFMA kernel.
-        const bool have_ws = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 &&
-                             workspace_bytes >= tf32x3_workspace_bytes(p);
-        if (!have_ws || p.K < 1) return cudaErrorInvalidValue;
+    // FP32 on the tensor cores (3xTF32) needs workspace for the split operands.  A forced tensor-core launch
+    // without it is rejected; AUTO takes the tensor cores when the caller supplied enough workspace and the
+    // product is large enough to repay the two split passes, and the exact FFMA kernel otherwise.
+    const bool fp32_ws = p.in_dtype == SM120_DTYPE_FLOAT32 && p.trace == nullptr && p.K >= 1 && workspace != nullptr &&
+                         (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0 && workspace_bytes >= tf32x3_workspace_bytes(p);
+    const bool fp32_big = static_cast<double>(p.M) * static_cast<double>(p.N) * static_cast<double>(p.K) * static_cast<double>(p.batch) >= 16777216.0;
+    if (p.in_dtype == SM120_DTYPE_FLOAT32 && (path == SM120_PATH_TENSOR_CORE || (path == SM120_PATH_AUTO && fp32_ws && fp32_big))) {
+        if (!fp32_ws) return cudaErrorInvalidValue;
         e = tf32x3_launch(p, workspace, wait_limit_ns(), &name);
+        if (e == cudaErrorInvalidValue && path == SM120_PATH_AUTO) {
+            // the split operands cannot be described to TMA (extents beyond its limits): nothing was enqueued
+            e = simt_launch(p, &name);
+            if (e == cudaSuccess) {
+                g_launch_count.fetch_add(1, std::memory_order_relaxed);
+                t_last_kernel = name;
+            }
+            return e;
+        }
         if (e == cudaSuccess) {
             g_launch_count.fetch_add(3, std::memory_order_relaxed);
             t_last_kernel = name;

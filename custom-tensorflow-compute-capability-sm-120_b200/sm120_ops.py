@@ -300,7 +300,7 @@ def fused_matmul(
     scale_b: Union[float, torch.Tensor, None] = None,
     use_tensor_cores: Optional[bool] = None,
     optimization_level: Optional[int] = None,
-    fp32_tensor_cores: bool = False,
+    fp32_tensor_cores: Optional[bool] = None,
     peer_outs: Optional[Sequence[torch.Tensor]] = None,
     tuning: int = 0,
     trace: Optional[torch.Tensor] = None,
@@ -314,10 +314,11 @@ def fused_matmul(
     per-tensor quantisation scales (floats, or one-element CUDA float32 tensors
     that a producer kernel wrote).
 
-    float32 operands run on the exact FFMA kernel.  ``fp32_tensor_cores=True`` opts into
-    the 3xTF32 tensor-core path instead: several times faster on large products, but
-    the tensor cores' truncating accumulation leaves a relative error of about
-    K * 2^-27 (1.2e-5 at K = 1024), outside the op's 1e-5 gate.
+    float32 operands of a large product (at least 2^24 multiply-adds) run on the tensor
+    cores by the 3xTF32 split, whose partial sums are promoted to round-to-nearest fp32
+    every 256 products so that the result stays inside the op's 1e-5 gate; smaller ones,
+    and everything with ``use_tensor_cores=False`` or ``fp32_tensor_cores=False``, run on
+    the exact FFMA kernel.  ``fp32_tensor_cores=True`` forces the tensor cores.
 
     ``peer_outs`` (used by ``mshard``): up to 7 more destinations, tensors or raw device
     addresses (other GPUs' memory opened through CUDA IPC), that receive the same
@@ -378,13 +379,14 @@ def fused_matmul(
             raise ValueError("beta != 0 is not supported with host operands")
         host_out, out = out, None
     if (host_kind is not None and not a.is_cuda and not b.is_cuda and a.dim() == 2 and b.dim() == 2 and not transpose_a
-            and out is None and beta == 0.0 and not peer_outs and trace is None and not fp32_tensor_cores
+            and out is None and beta == 0.0 and not peer_outs and trace is None
             and not isinstance(scale_a, torch.Tensor) and not isinstance(scale_b, torch.Tensor)
             and M >= 2 * _HostPipeline.MIN_ROWS and N >= 1 and K >= 1):
         # large host operands: copies and products overlap chunk by chunk
         host = _host_pipelined(a, b, bias, host_out, out_dtype,
                                dict(transpose_b=transpose_b, activation=activation, alpha=alpha, scale_a=scale_a, scale_b=scale_b,
-                                    use_tensor_cores=use_tensor_cores, optimization_level=optimization_level, tuning=tuning))
+                                    use_tensor_cores=use_tensor_cores, optimization_level=optimization_level, tuning=tuning,
+                                    fp32_tensor_cores=fp32_tensor_cores))
         return _torch_to_numpy(host) if host_kind == "numpy" else host
     if host_kind is not None:
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -471,14 +473,16 @@ def fused_matmul(
         d.tuning |= _b.TUNE_TRACE
         d.workspace, d.workspace_bytes = trace.data_ptr(), trace.numel() * 8
     d.stream = torch.cuda.current_stream(a.device).cuda_stream
-    if fp32_tensor_cores and a.dtype == torch.float32 and K >= 1:
-        # opt-in 3xTF32: scratch for the split operands comes from the caller's allocator (torch),
-        # is kept per device and grows to the largest request
+    if a.dtype == torch.float32 and K >= 1 and trace is None and use_tensor_cores and fp32_tensor_cores is not False and (
+            fp32_tensor_cores or M * N * K * batch >= 1 << 24):
+        # 3xTF32: scratch for the split operands comes from the caller's allocator (torch), is kept per
+        # stream and grows to the largest request; with it the launcher's AUTO takes the tensor cores
         need = int(_b.load_library().sm120_matmul_workspace_bytes(ctypes.byref(d)))
         ws = _workspace(a.device, max(need, 16))
         keep.append(ws)
         d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
-        d.path = _b.PATH_TENSOR_CORE
+        if fp32_tensor_cores:
+            d.path = _b.PATH_TENSOR_CORE
 
     if peer_outs:
         if host_kind is not None or beta != 0.0:

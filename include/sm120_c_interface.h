@@ -80,7 +80,8 @@ typedef enum {
  * C[M,N] = alpha * A[M,K] * B[K,N] + beta * C, all three row-major and dense,
  * inputs and output of type `dtype`, fp32 accumulation, C read only when
  * beta != 0 (src/cuda_kernels/sm120_pure_kernels.cu:58-63).
- * dtype FLOAT32 runs the exact FFMA kernel; FLOAT16 / BFLOAT16 run the tcgen05
+ * dtype FLOAT32 runs the exact FFMA kernel (this signature carries no
+ * workspace for the tensor-core route); FLOAT16 / BFLOAT16 run the tcgen05
  * kernel.  An unknown dtype returns cudaErrorInvalidValue as the reference does.
  */
 cudaError_t sm120_launch_matmul(
@@ -234,17 +235,20 @@ cudaError_t sm120_ipc_import(const void* handle, void** base_out);
 cudaError_t sm120_ipc_close(void* base);
 
 /*
- * Workspace for the opt-in FP32-on-tensor-cores path (3xTF32: each operand is
- * split into two tf32 pieces and three partial products are accumulated by the
- * tensor cores).  It is used only when desc->path == SM120_PATH_TENSOR_CORE and
- * the input type is FLOAT32; desc->workspace must then hold at least the
- * returned number of bytes (16-byte aligned), else the launch is rejected.
- * Accuracy: the tensor cores truncate when they accumulate in fp32, so the
- * result drifts from the exact product by about K * 2^-27 relative (1.2e-5 at
- * K = 1024).  That is why AUTO keeps FP32 on the exact FFMA kernel, whose error
- * stays below 1e-6.  Returns 0 when the descriptor's types need no workspace.
- * The workspace can be reused by later calls on the same stream.
- * No counterpart in the reference.
+ * Workspace for FP32 on the tensor cores (3xTF32: each operand is split into
+ * two tf32 pieces by a pre-pass and three partial products are accumulated by
+ * the tensor cores).  FLOAT32 inputs take this path when desc->workspace holds
+ * at least the returned number of bytes (16-byte aligned) and either
+ * desc->path == SM120_PATH_TENSOR_CORE (rejected without the workspace) or the
+ * path is AUTO and the product has at least 2^24 multiply-adds; without
+ * workspace AUTO runs the exact FFMA kernel.
+ * Accuracy: the tensor cores truncate when they add into their fp32
+ * accumulator, so a sum is carried there for 256 products only; the partial
+ * sums are added in registers with round-to-nearest.  The relative Frobenius
+ * error against float64 stays below 1e-5 (the op's fp32 gate) for K up to 8192,
+ * same-sign data included; the FFMA kernel's stays below 1e-6.
+ * Returns 0 when the descriptor's types need no workspace.  The workspace can
+ * be reused by later calls on the same stream.  No counterpart in the reference.
  */
 size_t sm120_matmul_workspace_bytes(const SM120GemmDesc* desc);
 

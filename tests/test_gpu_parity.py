@@ -544,8 +544,8 @@ def test_kernel_status_is_clean(binding):
     assert status.value == 0
 
 
-# ----- FP32 on the tensor cores (3xTF32 split): opt-in, because its accuracy is outside the 1e-5 gate -----
-def test_fp32_tensor_core_path_is_opt_in(ops, binding):
+# ----- FP32 on the tensor cores (3xTF32 split with run-wise promotion) -----
+def test_fp32_tensor_core_path(ops, binding):
     rng = np.random.default_rng(123)
     for (M, N, K, batch, ta, tb) in ((1024, 1024, 1024, 1, False, False), (520, 776, 1000, 1, True, False),
                                      (1000, 520, 333, 1, False, True), (513, 257, 1031, 1, True, True),
@@ -553,17 +553,18 @@ def test_fp32_tensor_core_path_is_opt_in(ops, binding):
         a, b, _, _ = U.random_operands(rng, M, N, K, batch, ta, tb, "float32")
         bias = rng.standard_normal((N,), dtype=np.float32)
         want = ref.matmul_oracle(a, b, transpose_a=ta, transpose_b=tb, bias=bias, act=0)
-        # default: the exact FFMA kernel, inside the gate
-        exact = run(ops, a, b, ta=ta, tb=tb, bias=bias, act=0)
-        assert binding.last_kernel_name().startswith("simt_f32")
-        check(exact, want, "float32", "ffma")
-        # opt-in: tensor cores; error ~ K * 2^-27 from the truncating fp32 accumulation of the MMA
-        got = U.to_numpy(ops.fused_matmul(U.to_cuda(a), U.to_cuda(b), transpose_a=ta, transpose_b=tb,
-                                          bias=U.to_cuda(bias), activation=0, fp32_tensor_cores=True))
+        # large products take the tensor cores by default and stay inside the 1e-5 gate
+        got = run(ops, a, b, ta=ta, tb=tb, bias=bias, act=0)
         assert binding.last_kernel_name().startswith("tc_tf32x3"), binding.last_kernel_name()
-        err = ref.rel_frobenius(got, want)
-        assert err <= 4.0 * K * 2.0 ** -27, (M, N, K, err)
-        assert err <= 5e-5
+        check(got, want, "float32", "3xTF32")
+        # the exact FFMA kernel on request
+        exact = run(ops, a, b, ta=ta, tb=tb, bias=bias, act=0, use_tensor_cores=False)
+        assert binding.last_kernel_name().startswith("simt_f32")
+        assert ref.rel_frobenius(exact, want) <= 2e-6
+    # small products stay on the FFMA kernel
+    a, b, _, _ = U.random_operands(rng, 100, 90, 80, 1, False, False, "float32")
+    run(ops, a, b)
+    assert binding.last_kernel_name().startswith("simt_f32")
     # forcing the tensor-core path without workspace is rejected, not silently rerouted
     lib = binding.load_library()
     d = binding.new_desc()
@@ -573,6 +574,30 @@ def test_fp32_tensor_core_path_is_opt_in(ops, binding):
     d.path = binding.PATH_TENSOR_CORE
     assert lib.sm120_matmul_workspace_bytes(ctypes.byref(d)) == 2 * 256 * 3 * 256 * 4
     assert lib.sm120_launch_matmul_ex(ctypes.byref(d)) == 1
+    # AUTO without workspace: the FFMA kernel (the reference-signature entry point carries none)
+    d.path = binding.PATH_AUTO
+    assert lib.sm120_launch_matmul_ex(ctypes.byref(d)) == 0
+    assert binding.last_kernel_name().startswith("simt_f32")
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("K", [1024, 4096, 8192])
+@pytest.mark.parametrize("dist", ["uniform_pm1", "uniform_01", "normal"])
+def test_fp32_tensor_core_accuracy_gate(ops, binding, K, dist):
+    """rel-Frobenius <= 1e-5 against float64 for long inner dimensions; same-sign data (U[0,1]) is the worst case
+    for the tensor cores' truncating accumulation, which the run-wise promotion bounds."""
+    rng = np.random.default_rng(K)
+    M, N = 384, 512
+    draw = {"uniform_pm1": lambda s: rng.uniform(-1, 1, s), "uniform_01": lambda s: rng.uniform(0, 1, s),
+            "normal": lambda s: rng.standard_normal(s)}[dist]
+    a = draw((M, K)).astype(np.float32)
+    b = draw((K, N)).astype(np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    got = run(ops, a, b)
+    assert binding.last_kernel_name().startswith("tc_tf32x3"), binding.last_kernel_name()
+    err = ref.rel_frobenius(got, want)
+    assert err <= ref.TOLERANCE["float32"], (K, dist, err)
+    assert np.array_equal(got, run(ops, a, b))                      # and reproducible bit for bit
 
 
 def test_empty_and_zero_inner_dimension(ops, binding):
