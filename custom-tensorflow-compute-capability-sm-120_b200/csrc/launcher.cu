@@ -24,6 +24,9 @@ cudaError_t quant_launch_static(const void* x, int x_dtype, void* q, float* scal
 cudaError_t quant_cast_launch(const void* x, int x_dtype, void* q, const float* scale, long long n, cudaStream_t stream);
 cudaError_t activation_launch(const void* in, void* out, long long n, const void* bias, int bias_dtype, long long cols,
                               int act, int dtype, int sm_count, cudaStream_t stream);
+cudaError_t softmax_launch(const void* in, void* out, long long outer, long long axis, long long inner, int dtype, int out_dtype,
+                           float scale, const float* mask, long long mask_rows, float mask_factor, int causal, long long seq_q,
+                           cudaStream_t stream);
 cudaError_t bias_grad_launch(const void* g, int dtype, long long M, long long N, long long ld, void* out, int out_dtype,
                              cudaStream_t stream);
 
@@ -480,6 +483,44 @@ cudaError_t sm120_launch_bias_grad(const void* grad_c, void* grad_bias, int64_t 
         t_last_kernel = "bias_grad_colsum";
     }
     return e;
+}
+
+namespace {
+cudaError_t softmax_common(const void* logits, void* output, int64_t outer, int64_t axis, int64_t inner, int dtype, int out_dtype, float scale,
+                           const float* mask, int64_t mask_rows, float mask_factor, int causal, int64_t seq_q, cudaStream_t stream) {
+    if (outer < 0 || axis < 0 || inner < 0) return cudaErrorInvalidValue;
+    if (dtype != SM120_DTYPE_FLOAT32 && dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (out_dtype != dtype && !(dtype == SM120_DTYPE_FLOAT32 && (out_dtype == SM120_DTYPE_FLOAT16 || out_dtype == SM120_DTYPE_BFLOAT16)))
+        return cudaErrorInvalidValue;
+    if ((mask != nullptr || causal) && inner != 1) return cudaErrorInvalidValue;
+    if (mask != nullptr && (mask_rows < 1 || (reinterpret_cast<uintptr_t>(mask) & 3u) != 0)) return cudaErrorInvalidValue;
+    if (causal && (seq_q < 1 || seq_q > axis || (outer % seq_q) != 0)) return cudaErrorInvalidValue;
+    if (outer == 0 || axis == 0 || inner == 0) return cudaSuccess;
+    if (logits == nullptr || output == nullptr) return cudaErrorInvalidValue;
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    e = softmax_launch(logits, output, outer, axis, inner, dtype, out_dtype, scale, mask, mask_rows, mask_factor, causal, seq_q, stream);
+    if (e == cudaSuccess) {
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+        t_last_kernel = "softmax_rows";
+    }
+    return e;
+}
+}  // namespace
+
+cudaError_t sm120_launch_softmax(const void* logits, void* output, int outer_size, int axis_size, int inner_size,
+                                 SM120DataType dtype, cudaStream_t stream) {
+    return softmax_common(logits, output, outer_size, axis_size, inner_size, static_cast<int>(dtype), static_cast<int>(dtype), 1.0f, nullptr, 0, 0.0f, 0, 0, stream);
+}
+
+cudaError_t sm120_launch_softmax_ex(const void* logits, void* output, int64_t rows, int64_t cols, SM120DataType dtype,
+                                    SM120DataType out_dtype, float scale, const float* mask, int64_t mask_rows, float mask_factor,
+                                    int causal, int64_t seq_q, cudaStream_t stream) {
+    return softmax_common(logits, output, rows, cols, 1, static_cast<int>(dtype), static_cast<int>(out_dtype), scale, mask, mask_rows, mask_factor, causal, seq_q, stream);
 }
 
 bool sm120_is_supported(int device_id) {

@@ -306,6 +306,42 @@ cudaError_t sm120_launch_bias_activation(
     cudaStream_t stream);
 
 /*
+ * Replaces sm120_launch_softmax (src/cuda_kernels/sm120_c_interface.h:189-195,
+ * body src/cuda_kernels/sm120_c_interface.cu:374-400, kernel
+ * src/cuda_kernels/sm120_pure_kernels.cu:471-550) with the same signature: softmax
+ * over the middle extent of a dense [outer_size, axis_size, inner_size] tensor of
+ * `dtype` (FLOAT32 / FLOAT16 as in the reference, plus BFLOAT16), fp32 math with
+ * the maximum subtracted, in place allowed.  Rows of up to 8192 contiguous
+ * elements (inner_size == 1) are read once and written once: the kernel is bound
+ * by HBM bandwidth.
+ */
+cudaError_t sm120_launch_softmax(
+    const void* logits, void* output,
+    int outer_size, int axis_size, int inner_size,
+    SM120DataType dtype,
+    cudaStream_t stream);
+
+/*
+ * Row softmax with what the attention layer applies before it folded in
+ * (python/sm120_ops.py:385-402, python/sm120_keras_layers.py:815-822):
+ *   output[r, :] = softmax_c( scale * logits[r, c] + mask_factor * mask[r % mask_rows, c] )
+ * over a dense [rows, cols] matrix of `dtype`, written as out_dtype (the same type,
+ * or FLOAT16 / BFLOAT16 for FLOAT32 logits: fp32 scores in, 16-bit probabilities out
+ * for the P.V product); `mask` (fp32, mask_rows x cols, device) may be
+ * null; with causal != 0 column c of row r is excluded when
+ * c > (r % seq_q) + cols - seq_q (rows are seq_q queries per batch entry, aligned
+ * to the end of the cols keys).  A row with every column excluded comes out as
+ * zeros.  No counterpart in the reference, which masks with separate TensorFlow ops.
+ */
+cudaError_t sm120_launch_softmax_ex(
+    const void* logits, void* output,
+    int64_t rows, int64_t cols,
+    SM120DataType dtype, SM120DataType out_dtype, float scale,
+    const float* mask, int64_t mask_rows, float mask_factor,
+    int causal, int64_t seq_q,
+    cudaStream_t stream);
+
+/*
  * Bias gradient of the Dense layer: grad_bias[n] = sum over m of grad_c[m, n] for a
  * row-major [M, N] matrix with row pitch ld (elements; 0 = N), accumulated in fp32
  * in a fixed order (bitwise reproducible; no atomics, no scratch) and written as
