@@ -24,7 +24,8 @@ benchmark workload.  `--impl reference` times only the CPU product.
 Other workloads (`--workload`): f32_1024, f16_4096_tn, bf16_4096_tn,
 bf16_dense_gelu, bf16_batched_qk, fp8_65536 (M split over the ranks), fp8_8192,
 f32_1024_ffma, f32_4096, f32_4096_ffma, and the HBM-bound kernels quant_fp8_64m,
-activation_gelu_64m, bias_grad_8192x11008.  `--trace FILE` also writes the
+activation_gelu_64m, bias_grad_8192x11008, softmax_131072x2048 and the fused attention
+attention_64x2048x128 (batch x heads = 64, sequence 2048, head 128, bf16).  `--trace FILE` also writes the
 launch timeline (SM120_TUNE_TRACE) of one launch of the workload to FILE.
 """
 import argparse
@@ -60,7 +61,7 @@ WORKLOADS = {
     "f32_4096":        dict(M=4096, N=4096, K=4096, batch=1, dtype="f32", layout="nn", oracle_idx=1),
     "f32_4096_ffma":   dict(M=4096, N=4096, K=4096, batch=1, dtype="f32", layout="nn", ffma=True, oracle_idx=1),
 }
-AUX_WORKLOADS = ("quant_fp8_64m", "activation_gelu_64m", "bias_grad_8192x11008")
+AUX_WORKLOADS = ("quant_fp8_64m", "activation_gelu_64m", "bias_grad_8192x11008", "softmax_131072x2048", "attention_64x2048x128")
 ALIASES = {"cfg1": "f32_1024", "cfg2": "f16_4096_tn", "cfg2bf16": "bf16_4096_tn", "cfg3": "bf16_dense_gelu",
            "cfg4": "bf16_batched_qk", "cfg5": "fp8_65536"}
 IN_BYTES = {"f32": 4, "f16": 2, "bf16": 2, "f8e4m3": 1}
@@ -573,6 +574,16 @@ def run_aux(args, torch, pkg, device, peaks, peak_kind):
 
         def step(i):
             ops.fused_activation(xs[i % 3], "gelu_tanh", out=outs[i % 3])
+    elif args.workload == "softmax_131072x2048":
+        xs = [torch.randn(131072, 2048, device=device).bfloat16() for _ in range(2)]
+        outs = [torch.empty_like(x) for x in xs]
+        nbytes = 131072 * 2048 * 4
+        what = "row softmax of a bf16 [64 x 2048, 2048] score matrix (sm120_launch_softmax)"
+
+        def step(i):
+            ops.softmax(xs[i % 2], out=outs[i % 2])
+    elif args.workload == "attention_64x2048x128":
+        return run_attention(args, torch, pkg, device, peaks, peak_kind)
     else:
         xs = [torch.randn(8192, 11008, device=device).bfloat16() for _ in range(3)]
         nbytes = 8192 * 11008 * 2
@@ -599,6 +610,49 @@ def run_aux(args, torch, pkg, device, peaks, peak_kind):
                          "frac": nbytes / secs / 1e9 / hbm, "traffic": None, "kernel": binding.last_kernel_name(),
                          "algorithmic_bytes_per_step": nbytes, "peak_source": f"{peak_kind}: hbm_gbs (copy)"},
             "gpu_launches": int(binding.launch_count() - launches0)}
+    print(json.dumps(line), flush=True)
+
+
+def run_attention(args, torch, pkg, device, peaks, peak_kind):
+    """Fused attention forward on the attention-score benchmark shape: batch x heads = 64, sequence 2048, head 128,
+    bf16.  4 S^2 D FLOPs per batch entry; beside it the same result as GEMM + softmax + GEMM (scores through HBM)."""
+    ops, binding = pkg.sm120_ops, pkg._binding
+    bh, s, d = 64, 2048, 128
+    sets = [tuple(torch.randn(bh, s, d, device=device).bfloat16() for _ in range(3)) for _ in range(3)]
+    flops = 4.0 * s * s * d * bh
+    zero_mask = torch.zeros(s, s, device=device)
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(*sets[i % 3])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(*sets[i % 3])
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / steps
+
+    launches0 = binding.launch_count()
+    secs = timed(lambda q, k, v: ops.scaled_dot_product_attention(q, k, v), args.steps, args.warmup)
+    launches = (binding.launch_count() - launches0) * args.steps // (args.steps + args.warmup)
+    kernel = binding.last_kernel_name()
+    unfused = timed(lambda q, k, v: ops.scaled_dot_product_attention(q, k, v, attention_mask=zero_mask), max(3, args.steps // 5), 2)
+    peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    tf = flops / secs / 1e12
+    line = {"metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "batch_x_heads": bh, "seq": s, "head_dim": d,
+                       "what": "softmax(Q K^T / sqrt(d)) V in one kernel", "l2": "three sets of Q, K, V rotate"},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                         "kernel": kernel, "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": 4 * bh * s * d * 2,
+                         "peak_source": f"{peak_kind}: bf16_tflops (cuBLAS bf16 8192^3 burst)"},
+            "pct_of_nominal_dense_peak": 100.0 * tf / NOMINAL_PEAK["bf16"],
+            "unfused_gemm_softmax_gemm": {"ms_per_step": unfused * 1e3, "tflops": flops / unfused / 1e12,
+                                          "hbm_bytes_of_scores": bh * s * s * (4 + 4 + 2 + 2)},
+            "gpu_launches": int(launches)}
     print(json.dumps(line), flush=True)
 
 

@@ -95,6 +95,9 @@ EXPORTS = {
     "sm120_launch_softmax": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "sm120_launch_softmax_ex": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_int64, c_float,
                                         c_int, c_int64, c_void_p]),
+    "sm120_launch_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "sm120_launch_attention_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                          c_float, c_int, c_int, c_void_p]),
     "sm120_launch_bias_grad": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "sm120_is_supported": (c_bool, [c_int]),
     "sm120_get_error_string": (c_char_p, [c_int]),

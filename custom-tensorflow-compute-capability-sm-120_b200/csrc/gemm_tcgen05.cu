@@ -134,6 +134,24 @@ static bool encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inne
     return true;
 }
 
+bool tc_encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch, int64_t pitch,
+                  int64_t bstride, uint32_t box_inner, uint32_t box_outer) {
+    return encode_3d(map, ptr, dtype, inner, outer, nbatch, pitch, bstride, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// Device address of `device`'s status words (looked up once per device, with that device current).
+unsigned int* tc_status_address(int device) {
+    static std::atomic<unsigned int*> status_addr[64];
+    unsigned int* st = status_addr[device & 63].load(std::memory_order_acquire);
+    if (st == nullptr) {
+        void* a = nullptr;
+        if (cudaGetSymbolAddress(&a, g_sm120_status) != cudaSuccess) return nullptr;
+        st = static_cast<unsigned int*>(a);
+        status_addr[device & 63].store(st, std::memory_order_release);
+    }
+    return st;
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 bool tc_supported(const GemmProblem& p, const char** why) {
@@ -252,20 +270,16 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     const bool split_tail = (p.tuning & SM120_TUNE_NO_SPLIT_TAIL) == 0;
     {
         // device addresses of this device's status / probe words (looked up once per device)
-        static std::atomic<unsigned int*> status_addr[64];
         static std::atomic<unsigned long long*> probe_addr[64];
-        unsigned int* st = status_addr[p.device & 63].load(std::memory_order_acquire);
         unsigned long long* pr = probe_addr[p.device & 63].load(std::memory_order_acquire);
-        if (st == nullptr || pr == nullptr) {
-            void *a = nullptr, *b = nullptr;
-            if (cudaGetSymbolAddress(&a, g_sm120_status) != cudaSuccess || cudaGetSymbolAddress(&b, g_sm120_probe) != cudaSuccess)
-                return cudaErrorInvalidSymbol;
-            st = static_cast<unsigned int*>(a);
+        if (pr == nullptr) {
+            void* b = nullptr;
+            if (cudaGetSymbolAddress(&b, g_sm120_probe) != cudaSuccess) return cudaErrorInvalidSymbol;
             pr = static_cast<unsigned long long*>(b);
-            status_addr[p.device & 63].store(st, std::memory_order_release);
             probe_addr[p.device & 63].store(pr, std::memory_order_release);
         }
-        tp.status = st;
+        tp.status = tc_status_address(p.device);
+        if (tp.status == nullptr) return cudaErrorInvalidSymbol;
         tp.probe = pr;
     }
 

@@ -1247,6 +1247,12 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 
+// Host helpers defined in gemm_tcgen05.cu, shared with the attention kernel: a cached 3-D tensor map with the
+// 128-byte swizzle (extents, pitch and batch stride in elements), and the device's status words.
+bool tc_encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch, int64_t pitch,
+                  int64_t bstride, uint32_t box_inner, uint32_t box_outer);
+unsigned int* tc_status_address(int device);
+
 // ---------------------------------------------------------------------------
 // Host-side launch of one kernel variant.  Each variant is instantiated in its
 // own translation unit (gemm_tcgen05_inst_*.cu) so that the variants compile in

@@ -27,6 +27,11 @@ cudaError_t activation_launch(const void* in, void* out, long long n, const void
 cudaError_t softmax_launch(const void* in, void* out, long long outer, long long axis, long long inner, int dtype, int out_dtype,
                            float scale, const float* mask, long long mask_rows, float mask_factor, int causal, long long seq_q,
                            cudaStream_t stream);
+bool attention_fused_supported(int dtype, long long batch, long long seq_q, long long seq_k, long long head_dim, const void* q,
+                               const void* k, const void* v, const void* out);
+cudaError_t attention_fused_launch(const void* q, const void* k, const void* v, void* out, long long batch, long long seq_q,
+                                   long long seq_k, long long head_dim, float scale, int causal, int dtype, int device,
+                                   uint64_t wait_limit_ns, cudaStream_t stream);
 cudaError_t bias_grad_launch(const void* g, int dtype, long long M, long long N, long long ld, void* out, int out_dtype,
                              cudaStream_t stream);
 
@@ -521,6 +526,72 @@ cudaError_t sm120_launch_softmax_ex(const void* logits, void* output, int64_t ro
                                     SM120DataType out_dtype, float scale, const float* mask, int64_t mask_rows, float mask_factor,
                                     int causal, int64_t seq_q, cudaStream_t stream) {
     return softmax_common(logits, output, rows, cols, 1, static_cast<int>(dtype), static_cast<int>(out_dtype), scale, mask, mask_rows, mask_factor, causal, seq_q, stream);
+}
+
+cudaError_t sm120_launch_attention_ex(const void* queries, const void* keys, const void* values, void* output,
+                                      float* attention_weights, int64_t batch_size, int64_t seq_q, int64_t seq_k, int64_t head_dim,
+                                      float scale, int causal, SM120DataType dtype, cudaStream_t stream) {
+    if (batch_size < 0 || seq_q < 0 || seq_k < 0 || head_dim < 1) return cudaErrorInvalidValue;
+    if (dtype != SM120_DTYPE_FLOAT32 && dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16)
+        return cudaErrorInvalidValue;
+    if (causal && seq_q > seq_k) return cudaErrorInvalidValue;
+    if (batch_size == 0 || seq_q == 0) return cudaSuccess;
+    if (queries == nullptr || output == nullptr || (seq_k > 0 && (keys == nullptr || values == nullptr))) return cudaErrorInvalidValue;
+    if (seq_k == 0) return cudaErrorInvalidValue;                     // a softmax over no keys is undefined
+    int device = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = query_device(device, &sms);
+    if (e != cudaSuccess) return e;
+    const bool fused = attention_fused_supported(dtype, batch_size, seq_q, seq_k, head_dim, queries, keys, values, output);
+    // 16-bit tensors with a head dimension the fused kernel lacks have no route: the unfused one would need a
+    // 16-bit [seq_q, seq_k] buffer for P that this signature does not carry
+    if (!fused && dtype != SM120_DTYPE_FLOAT32) return cudaErrorInvalidValue;
+    // fp32 runs unfused and needs the attention_weights buffer as its score matrix
+    if (!fused && attention_weights == nullptr) return cudaErrorInvalidValue;
+    if (attention_weights != nullptr) {
+        // weights[b] = softmax(scale * Q[b] K[b]^T): one batched GEMM with fp32 output, then the row softmax in place
+        SM120GemmDesc d;
+        sm120_gemm_desc_init(&d);
+        d.A = queries; d.B = keys; d.C = attention_weights;
+        d.M = seq_q; d.N = seq_k; d.K = head_dim;
+        d.transpose_b = 1;
+        d.batch = batch_size;
+        d.stride_a = seq_q * head_dim; d.stride_b = seq_k * head_dim; d.stride_c = seq_q * seq_k;
+        d.in_dtype = dtype; d.out_dtype = SM120_DTYPE_FLOAT32;
+        d.stream = stream;
+        e = sm120_launch_matmul_ex(&d);
+        if (e != cudaSuccess) return e;
+        e = sm120_launch_softmax_ex(attention_weights, attention_weights, batch_size * seq_q, seq_k, SM120_DTYPE_FLOAT32,
+                                    SM120_DTYPE_FLOAT32, scale, nullptr, 0, 0.0f, causal, seq_q, stream);
+        if (e != cudaSuccess) return e;
+    }
+    if (fused) {
+        e = attention_fused_launch(queries, keys, values, output, batch_size, seq_q, seq_k, head_dim, scale, causal, dtype, device,
+                                   wait_limit_ns(), stream);
+        if (e == cudaSuccess) {
+            g_launch_count.fetch_add(1, std::memory_order_relaxed);
+            t_last_kernel = head_dim == 128 ? "attention_tcgen05_d128" : "attention_tcgen05_d64";
+        }
+        return e;
+    }
+    // fp32: output[b] = weights[b] V[b]
+    SM120GemmDesc d;
+    sm120_gemm_desc_init(&d);
+    d.A = attention_weights; d.B = values; d.C = output;
+    d.M = seq_q; d.N = head_dim; d.K = seq_k;
+    d.batch = batch_size;
+    d.stride_a = seq_q * seq_k; d.stride_b = seq_k * head_dim; d.stride_c = seq_q * head_dim;
+    d.in_dtype = dtype; d.out_dtype = dtype;
+    d.stream = stream;
+    return sm120_launch_matmul_ex(&d);
+}
+
+cudaError_t sm120_launch_attention(const void* queries, const void* keys, const void* values, void* output,
+                                   float* attention_weights, int batch_size, int seq_len, int head_dim, float scale,
+                                   SM120DataType dtype, cudaStream_t stream) {
+    return sm120_launch_attention_ex(queries, keys, values, output, attention_weights, batch_size, seq_len, seq_len, head_dim, scale,
+                                     0, dtype, stream);
 }
 
 bool sm120_is_supported(int device_id) {

@@ -1,4 +1,4 @@
-"""``SM120Layer`` and ``SM120Dense`` for the B200 build.
+"""``SM120Layer``, ``SM120Dense`` and ``SM120MultiHeadAttention`` for the B200 build.
 
 Constructor arguments, weight names and shapes, ``build`` / ``call`` /
 ``compute_output_shape`` / ``get_config`` and the registered custom-object name
@@ -235,6 +235,123 @@ class SM120Dense(SM120Layer):
         return config
 
 
-_CUSTOM_OBJECTS.update({"SM120Dense": SM120Dense})
+class SM120MultiHeadAttention(SM120Layer):
+    """Multi-head attention on the SM120 ops (python/sm120_keras_layers.py:636-886):
+    four ``SM120Dense`` projections (query, key, value: num_heads * key_dim / value_dim
+    units; output: ``output_shape`` or the query's last dimension) around
+    ``sm120_ops.scaled_dot_product_attention``, which for float16 / bfloat16 heads of 64 or
+    128 is one fused tcgen05 kernel.  Constructor arguments and ``get_config`` keys are the
+    reference's (:643-684, :858-886).  ``call(inputs, attention_mask=None,
+    return_attention_scores=False, training=None)`` takes one tensor [batch, seq, dim]
+    (self-attention) or a list [query, key, value]; the mask marks EXCLUDED positions with
+    non-zero entries, as in the reference (:815-816).  Dropout is not implemented: a
+    non-zero rate raises when ``training`` is true."""
 
-__all__ = ["SM120Layer", "SM120Dense", "get_custom_objects", "SM120_AVAILABLE"]
+    def __init__(self, num_heads: int, key_dim: int, value_dim: Optional[int] = None, dropout: float = 0.0, use_bias: bool = True,
+                 output_shape=None, attention_axes=None, kernel_initializer: str = "glorot_uniform",
+                 bias_initializer: str = "zeros", kernel_regularizer=None, bias_regularizer=None, activity_regularizer=None,
+                 kernel_constraint=None, bias_constraint=None, use_sm120: bool = True, fallback_on_error: bool = True,
+                 use_flash_attention: bool = True, **kwargs):
+        super().__init__(use_sm120=use_sm120, fallback_on_error=fallback_on_error, **kwargs)
+        if num_heads < 1 or key_dim < 1:
+            raise ValueError("num_heads and key_dim must be positive")
+        self.num_heads = int(num_heads)
+        self.key_dim = int(key_dim)
+        self.value_dim = int(value_dim) if value_dim is not None else int(key_dim)
+        self.dropout = float(dropout)
+        self.use_bias = use_bias
+        self.output_shape = output_shape
+        self.attention_axes = attention_axes
+        self.kernel_initializer = kernel_initializer
+        self.bias_initializer = bias_initializer
+        self.kernel_regularizer = kernel_regularizer
+        self.bias_regularizer = bias_regularizer
+        self.activity_regularizer = activity_regularizer
+        self.kernel_constraint = kernel_constraint
+        self.bias_constraint = bias_constraint
+        self.use_flash_attention = use_flash_attention
+        self.supports_masking = True
+        self.query_dense = self.key_dense = self.value_dense = self.output_dense = None
+
+    def _dense(self, units: int, name: str) -> SM120Dense:
+        return SM120Dense(units, use_bias=self.use_bias, kernel_initializer=self.kernel_initializer,
+                          bias_initializer=self.bias_initializer, kernel_regularizer=self.kernel_regularizer,
+                          bias_regularizer=self.bias_regularizer, kernel_constraint=self.kernel_constraint,
+                          bias_constraint=self.bias_constraint, use_sm120=self.use_sm120,
+                          fallback_on_error=self.fallback_on_error, name=f"{self.name}/{name}", dtype=self.dtype)
+
+    def build(self, input_shape, device=None, seed: Optional[int] = None):
+        if isinstance(input_shape, list):
+            if len(input_shape) != 3:
+                raise ValueError("MultiHeadAttention expects exactly 3 inputs: [query, key, value]")
+            query_shape, key_shape, value_shape = (tuple(s) for s in input_shape)
+        else:
+            query_shape = key_shape = value_shape = tuple(input_shape)
+        self.query_dense = self._dense(self.num_heads * self.key_dim, "query")
+        self.key_dense = self._dense(self.num_heads * self.key_dim, "key")
+        self.value_dense = self._dense(self.num_heads * self.value_dim, "value")
+        output_dim = self.output_shape if self.output_shape is not None else query_shape[-1]
+        self.output_dense = self._dense(int(output_dim), "output")
+        seeds = [None] * 4 if seed is None else [seed, seed + 1, seed + 2, seed + 3]
+        self.query_dense.build(query_shape, device=device, seed=seeds[0])
+        self.key_dense.build(key_shape, device=device, seed=seeds[1])
+        self.value_dense.build(value_shape, device=device, seed=seeds[2])
+        self.output_dense.build(tuple(query_shape[:-1]) + (self.num_heads * self.value_dim,), device=device, seed=seeds[3])
+        self.built = True
+
+    @property
+    def weights(self):
+        return [w for layer in (self.query_dense, self.key_dense, self.value_dense, self.output_dense) for w in layer.weights]
+
+    def __call__(self, inputs, attention_mask=None, return_attention_scores=False, training=None):
+        if not self.built:
+            self.build([tuple(t.shape) for t in inputs] if isinstance(inputs, list) else tuple(inputs.shape))
+        return self.call(inputs, attention_mask=attention_mask, return_attention_scores=return_attention_scores, training=training)
+
+    def call(self, inputs, attention_mask=None, return_attention_scores=False, training=None):
+        if isinstance(inputs, list):
+            if len(inputs) != 3:
+                raise ValueError("MultiHeadAttention expects exactly 3 inputs: [query, key, value]")
+            query, key, value = inputs
+        else:
+            query = key = value = inputs
+        if query.dim() != 3 or key.dim() != 3 or value.dim() != 3:
+            raise ValueError("MultiHeadAttention expects [batch, seq, dim] tensors")
+        if value.shape[-1] != self.num_heads * self.value_dim and self.value_dense is None:
+            raise ValueError("layer is not built")
+        batch, seq_q, seq_k = query.shape[0], query.shape[1], key.shape[1]
+        # projections, then [batch, seq, heads, dim] -> [batch, heads, seq, dim] (:780-794)
+        q = self.query_dense(query).reshape(batch, seq_q, self.num_heads, self.key_dim).permute(0, 2, 1, 3)
+        k = self.key_dense(key).reshape(batch, seq_k, self.num_heads, self.key_dim).permute(0, 2, 1, 3)
+        v = self.value_dense(value).reshape(batch, seq_k, self.num_heads, self.value_dim).permute(0, 2, 1, 3)
+        if self.value_dim != self.key_dim:
+            raise NotImplementedError("value_dim != key_dim is not implemented by the attention kernels")
+
+        def sm120_attention():
+            return sm120_ops.scaled_dot_product_attention(
+                q, k, v, scale=1.0 / float(self.key_dim) ** 0.5, dropout_rate=self.dropout if training else 0.0,
+                attention_mask=attention_mask, return_attention_scores=return_attention_scores)
+
+        result = self._try_sm120_operation(sm120_attention, None)
+        attention_output, attention_weights = result if return_attention_scores else (result, None)
+        attention_output = attention_output.permute(0, 2, 1, 3).reshape(batch, seq_q, self.num_heads * self.value_dim)
+        output = self.output_dense(attention_output)
+        return (output, attention_weights) if return_attention_scores else output
+
+    def get_config(self) -> Dict[str, Any]:
+        config = super().get_config()
+        config.update({
+            "num_heads": self.num_heads, "key_dim": self.key_dim, "value_dim": self.value_dim, "dropout": self.dropout,
+            "use_bias": self.use_bias, "output_shape": self.output_shape, "attention_axes": self.attention_axes,
+            "kernel_initializer": self.kernel_initializer, "bias_initializer": self.bias_initializer,
+            "kernel_regularizer": self.kernel_regularizer, "bias_regularizer": self.bias_regularizer,
+            "activity_regularizer": self.activity_regularizer, "kernel_constraint": self.kernel_constraint,
+            "bias_constraint": self.bias_constraint, "use_sm120": self.use_sm120, "fallback_on_error": self.fallback_on_error,
+            "use_flash_attention": self.use_flash_attention,
+        })
+        return config
+
+
+_CUSTOM_OBJECTS.update({"SM120Dense": SM120Dense, "SM120MultiHeadAttention": SM120MultiHeadAttention})
+
+__all__ = ["SM120Layer", "SM120Dense", "SM120MultiHeadAttention", "get_custom_objects", "SM120_AVAILABLE"]

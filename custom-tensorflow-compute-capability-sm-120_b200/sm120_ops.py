@@ -635,6 +635,137 @@ def bias_grad(grad_c: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> 
     return out
 
 
+def softmax(x: torch.Tensor, axis: int = -1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Softmax along `axis` (``sm120_launch_softmax``; the reference kernel is
+    src/cuda_kernels/sm120_pure_kernels.cu:471-550).  fp32 math, result in x's dtype."""
+    _require_available()
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise TypeError("softmax needs a CUDA tensor")
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"dtype {x.dtype} is not supported (float32, float16, bfloat16)")
+    x = x.contiguous()
+    axis = axis % x.dim()
+    outer = 1
+    for e in x.shape[:axis]:
+        outer *= int(e)
+    inner = 1
+    for e in x.shape[axis + 1:]:
+        inner *= int(e)
+    if max(outer, x.shape[axis], inner) >= 1 << 31:
+        raise InvalidArgumentError("softmax extents must fit in 31 bits")
+    if out is None:
+        out = torch.empty_like(x)
+    elif not (out.is_cuda and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype):
+        raise ValueError("`out` must be a contiguous CUDA tensor with x's shape and dtype")
+    with torch.cuda.device(x.device):
+        rc = _b.load_library().sm120_launch_softmax(x.data_ptr(), out.data_ptr(), outer, int(x.shape[axis]), inner,
+                                                    _TORCH_TO_SM120[x.dtype], torch.cuda.current_stream(x.device).cuda_stream)
+    if rc != _b.CUDA_SUCCESS:
+        raise (InvalidArgumentError if rc == _b.CUDA_ERROR_INVALID_VALUE else InternalError)(f"softmax failed: {_b.error_string(rc)}")
+    return out
+
+
+def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, scale: Optional[float] = None,
+                                 dropout_rate: float = 0.0, attention_mask: Optional[torch.Tensor] = None,
+                                 causal_mask: bool = False, return_attention_scores: bool = False):
+    """softmax(scale * Q K^T + mask) V over the last two dimensions: the attention core
+    that ``SM120MultiHeadAttention`` calls (python/sm120_keras_layers.py:796-806) and
+    ``flash_attention`` wraps (python/sm120_ops.py:315-407).
+
+    query [..., Sq, D], key and value [..., Sk, D] (the same leading dimensions, e.g.
+    [batch, heads]).  ``attention_mask`` follows the layer's convention
+    (python/sm120_keras_layers.py:815-816): a tensor broadcastable to [..., Sq, Sk] whose
+    non-zero entries mark positions to EXCLUDE (it is multiplied by -1e9 and added to the
+    scores).  ``causal_mask`` drops keys after the query position (aligned to the end).
+
+    float16 / bfloat16 with D = 64 or 128 and no explicit mask run ONE fused tcgen05
+    kernel: the scores never reach HBM.  A mask, float32 tensors, other head sizes and
+    ``return_attention_scores`` run as batched GEMM + softmax + batched GEMM on this
+    library's kernels.  Returns the output (in the inputs' dtype), or (output, weights)
+    with fp32 weights.  Dropout is a training-time feature this build does not have."""
+    _require_available()
+    if dropout_rate and dropout_rate > 0.0:
+        raise NotImplementedError("attention dropout is not implemented in this build")
+    for t in (query, key, value):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise TypeError("query, key and value must be CUDA tensors")
+    if not (query.dtype == key.dtype == value.dtype):
+        raise ValueError("query, key and value must have the same dtype")
+    if query.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"dtype {query.dtype} is not supported (float32, float16, bfloat16)")
+    if query.dim() < 2 or key.dim() != query.dim() or value.dim() != query.dim():
+        raise ValueError("query, key and value must have the same rank (at least 2)")
+    lead = tuple(query.shape[:-2])
+    sq, d = int(query.shape[-2]), int(query.shape[-1])
+    sk = int(key.shape[-2])
+    if tuple(key.shape[:-2]) != lead or tuple(value.shape[:-2]) != lead or key.shape[-1] != d or tuple(value.shape[-2:]) != (sk, d):
+        raise InvalidArgumentError("query [..., Sq, D], key [..., Sk, D] and value [..., Sk, D] are required")
+    if causal_mask and sq > sk:
+        raise InvalidArgumentError("causal attention needs at least as many keys as queries")
+    if scale is None:
+        scale = 1.0 / float(d) ** 0.5
+    bh = 1
+    for e in lead:
+        bh *= int(e)
+    q3, k3, v3 = (t.reshape(bh, -1, d).contiguous() for t in (query, key, value))
+    lib = _b.load_library()
+    stream = torch.cuda.current_stream(query.device).cuda_stream
+    code = _TORCH_TO_SM120[query.dtype]
+    out = torch.empty((bh, sq, d), dtype=query.dtype, device=query.device)
+    fused_ok = query.dtype != torch.float32 and d in (64, 128) and bh <= 65535
+    if attention_mask is None and (fused_ok or query.dtype == torch.float32):
+        weights = None
+        if return_attention_scores or not fused_ok:
+            weights = torch.empty((bh, sq, sk), dtype=torch.float32, device=query.device)
+        with torch.cuda.device(query.device):
+            rc = lib.sm120_launch_attention_ex(q3.data_ptr(), k3.data_ptr(), v3.data_ptr(), out.data_ptr(),
+                                               None if weights is None else weights.data_ptr(), bh, sq, sk, d, float(scale),
+                                               int(bool(causal_mask)), code, stream)
+        if rc != _b.CUDA_SUCCESS:
+            raise (InvalidArgumentError if rc == _b.CUDA_ERROR_INVALID_VALUE else InternalError)(
+                f"attention failed: {_b.error_string(rc)}")
+        out = out.reshape(*lead, sq, d)
+        return (out, weights.reshape(*lead, sq, sk)) if return_attention_scores else out
+    # unfused: scores (fp32) = Q K^T, probabilities = softmax(scale * scores + mask) in the inputs' dtype, out = P V
+    scores = fused_matmul(q3, k3, transpose_b=True, out_dtype=torch.float32)
+    mask_ptr, mask_rows = None, 0
+    if attention_mask is not None:
+        m = attention_mask.to(device=query.device, dtype=torch.float32)
+        m = torch.broadcast_to(m, (*lead, sq, sk)).reshape(-1, sk) if m.dim() > 2 else torch.broadcast_to(m, (sq, sk))
+        m = m.contiguous()                                     # [sq, sk] is shared by every batch entry: row r uses r % sq
+        mask_ptr, mask_rows = m.data_ptr(), int(m.shape[0])
+    p_dtype = query.dtype
+    probs = scores if p_dtype == torch.float32 else torch.empty((bh, sq, sk), dtype=p_dtype, device=query.device)
+    with torch.cuda.device(query.device):
+        rc = lib.sm120_launch_softmax_ex(scores.data_ptr(), probs.data_ptr(), bh * sq, sk, _b.DTYPE_FLOAT32, _TORCH_TO_SM120[p_dtype],
+                                         float(scale), mask_ptr, mask_rows, -1e9, int(bool(causal_mask)), sq, stream)
+    if rc != _b.CUDA_SUCCESS:
+        raise (InvalidArgumentError if rc == _b.CUDA_ERROR_INVALID_VALUE else InternalError)(f"softmax failed: {_b.error_string(rc)}")
+    fused_matmul(probs, v3, out=out)
+    out = out.reshape(*lead, sq, d)
+    if return_attention_scores:
+        return out, probs.float().reshape(*lead, sq, sk)
+    return out
+
+
+def flash_attention(queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                    scale: Optional[float] = None, causal_mask: bool = False, dropout_rate: float = 0.0,
+                    name: Optional[str] = None):
+    """Signature of python/sm120_ops.py:315-324: 4-dimensional [batch, heads, seq_len, head_dim]
+    tensors, returns (attention_output, attention_weights).  Here ``attention_mask`` is ADDED to
+    the scaled scores as it is (:400-401), unlike the layer's 0/1 convention."""
+    del name
+    if queries.dim() != 4 or keys.dim() != 4 or values.dim() != 4:
+        raise ValueError("Queries, keys, and values must be 4-dimensional")
+    if attention_mask is not None and attention_mask.numel() == 0:
+        attention_mask = None
+    if attention_mask is not None:
+        # an additive mask: hand it to the softmax as (mask / -1e9) * -1e9
+        attention_mask = attention_mask.to(torch.float32) / -1e9
+    return scaled_dot_product_attention(queries, keys, values, scale=scale, dropout_rate=dropout_rate,
+                                        attention_mask=attention_mask, causal_mask=causal_mask, return_attention_scores=True)
+
+
 class _DenseFunction(torch.autograd.Function):
     """y = relu?(x @ kernel + bias) with this library's kernels in both directions:
     the fused GEMM forward, SM120MatMulGradA / GradB
@@ -859,6 +990,9 @@ __all__ = [
     "bias_grad",
     "dense_trainable",
     "fused_activation",
+    "softmax",
+    "scaled_dot_product_attention",
+    "flash_attention",
     "quantize_fp8",
     "quantize_fp8_into",
     "SM120Profiler",

@@ -342,6 +342,37 @@ cudaError_t sm120_launch_softmax_ex(
     cudaStream_t stream);
 
 /*
+ * Replaces sm120_launch_attention (src/cuda_kernels/sm120_c_interface.h:138-144,
+ * body src/cuda_kernels/sm120_c_interface.cu:232-268, kernel
+ * src/cuda_kernels/sm120_pure_kernels.cu:352-430) with the same signature:
+ *   output[b] = softmax(scale * Q[b] K[b]^T) V[b],   b < batch_size (batch x heads)
+ * Q, K, V and output are dense [batch_size, seq_len, head_dim] tensors of `dtype`;
+ * attention_weights is null or receives the fp32 [batch_size, seq_len, seq_len]
+ * softmax.  FLOAT16 / BFLOAT16 with head_dim 64 or 128 run ONE fused tcgen05
+ * kernel (scores and probabilities never reach HBM; when attention_weights is
+ * requested it is produced beside it by a GEMM and a softmax pass).  FLOAT32
+ * runs as GEMM + softmax + GEMM and uses attention_weights as its score matrix,
+ * so it must be given; other combinations return cudaErrorInvalidValue.
+ * The _ex form adds separate query and key lengths and the causal mask
+ * (python/sm120_ops.py:388-398): key k of query q takes part when
+ * k <= q + seq_k - seq_q.
+ */
+cudaError_t sm120_launch_attention(
+    const void* queries, const void* keys, const void* values,
+    void* output, float* attention_weights,
+    int batch_size, int seq_len, int head_dim,
+    float scale,
+    SM120DataType dtype,
+    cudaStream_t stream);
+cudaError_t sm120_launch_attention_ex(
+    const void* queries, const void* keys, const void* values,
+    void* output, float* attention_weights,
+    int64_t batch_size, int64_t seq_q, int64_t seq_k, int64_t head_dim,
+    float scale, int causal,
+    SM120DataType dtype,
+    cudaStream_t stream);
+
+/*
  * Bias gradient of the Dense layer: grad_bias[n] = sum over m of grad_c[m, n] for a
  * row-major [M, N] matrix with row pitch ld (elements; 0 = N), accumulated in fp32
  * in a fixed order (bitwise reproducible; no atomics, no scratch) and written as

@@ -138,6 +138,35 @@ def matmul_oracle(a, b, *, transpose_a=False, transpose_b=False, alpha=1.0, beta
     return quantize(v, out_dtype)
 
 
+def softmax_oracle(x: np.ndarray, axis: int = -1) -> np.ndarray:
+    """float64 softmax with the maximum subtracted (src/cuda_kernels/sm120_pure_kernels.cu:489-549)."""
+    x = np.asarray(x).astype(np.float64)
+    m = np.max(x, axis=axis, keepdims=True)
+    m = np.where(np.isfinite(m), m, 0.0)
+    e = np.exp(x - m)
+    s = np.sum(e, axis=axis, keepdims=True)
+    return np.divide(e, s, out=np.zeros_like(e), where=s > 0)
+
+
+def attention_oracle(q, k, v, scale=None, mask=None, causal=False, return_weights=False):
+    """softmax(scale * Q K^T + mask * -1e9 [causal]) V in float64 over the last two dimensions: the layer's
+    standard attention (python/sm120_keras_layers.py:810-826; causal as python/sm120_ops.py:388-398, aligned
+    to the end of the keys).  `mask` marks excluded positions with non-zero entries."""
+    q, k, v = (np.asarray(t).astype(np.float64) for t in (q, k, v))
+    d = q.shape[-1]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    s = np.matmul(q, np.swapaxes(k, -1, -2)) * scale
+    if mask is not None:
+        s = s + np.asarray(mask).astype(np.float64) * -1e9
+    if causal:
+        sq, sk = s.shape[-2], s.shape[-1]
+        keep = np.arange(sk)[None, :] <= (np.arange(sq)[:, None] + sk - sq)
+        s = np.where(keep, s, -np.inf)
+    w = softmax_oracle(s, axis=-1)
+    out = np.matmul(w, v)
+    return (out, w) if return_weights else out
+
+
 def rel_frobenius(x, ref) -> float:
     """||x - ref||_F / ||ref||_F in float64 (BASELINE's parity metric)."""
     x = np.asarray(x).astype(np.float64)

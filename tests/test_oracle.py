@@ -130,3 +130,24 @@ def test_cpu_baseline_matches_oracle():
     out, secs, threads = ref.cpu_baseline_fp32(cfg["a"], cfg["b"], bias=cfg["bias"], act=cfg["act"], repeats=1)
     assert secs > 0 and threads >= 1
     assert ref.rel_frobenius(out, ref.oracle_for_config(cfg, round_output=False)) < 1e-5
+
+
+def test_softmax_and_attention_oracle():
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((4, 9))
+    w = ref.softmax_oracle(x)
+    assert np.allclose(w.sum(-1), 1.0) and np.all(w > 0)
+    assert np.allclose(ref.softmax_oracle(x + 100.0), w)                     # shift invariance
+    assert np.array_equal(ref.softmax_oracle(np.full((2, 3), -np.inf)), np.zeros((2, 3)))
+    q, k, v = rng.standard_normal((2, 5, 8)), rng.standard_normal((2, 7, 8)), rng.standard_normal((2, 7, 8))
+    out, wts = ref.attention_oracle(q, k, v, return_weights=True)
+    assert out.shape == (2, 5, 8) and np.allclose(wts.sum(-1), 1.0)
+    # one key only: the output is that key's value
+    assert np.allclose(ref.attention_oracle(q, k[:, :1], v[:, :1]), np.repeat(v[:, :1], 5, axis=1))
+    # causal, aligned to the end: query i of 5 sees keys 0 .. i + 2 of 7
+    _, wc = ref.attention_oracle(q, k, v, causal=True, return_weights=True)
+    assert np.all(wc[:, 0, 3:] == 0) and np.all(wc[:, 0, :3] > 0) and np.all(wc[:, 4] > 0)
+    # a mask entry excludes its position
+    mask = np.zeros((5, 7)); mask[:, 2] = 1
+    _, wm = ref.attention_oracle(q, k, v, mask=mask, return_weights=True)
+    assert np.all(wm[..., 2] < 1e-300)
