@@ -67,7 +67,9 @@ struct AttCfg {
     static constexpr uint32_t V_BYTES = ATT_BN * D * 2;              // [ATT_BN/64 key blocks][D/64 boxes][64 keys x 128 B]
     static constexpr uint32_t P_BYTES = ATT_BM * ATT_BN * 2;         // ATT_BN/64 blocks of [128 rows x 128 B]
     static constexpr uint32_t BAR_BYTES = 256;
-    static constexpr size_t SMEM = Q_BYTES + ATT_KV_STAGES * (K_BYTES + V_BYTES) + P_BYTES + BAR_BYTES + 1024;
+    static constexpr size_t SMEM_USED = Q_BYTES + ATT_KV_STAGES * (K_BYTES + V_BYTES) + P_BYTES + BAR_BYTES + 1024;
+    // every CTA allocates all 512 TMEM columns, so two CTAs must never share an SM: request more than half of its shared memory
+    static constexpr size_t SMEM = SMEM_USED > 118784 ? SMEM_USED : 118784;
     static constexpr uint32_t TMEM_COLS = 512;                        // S: 2 x 128 columns, PV: D columns at 256
     static_assert(SMEM <= 232448, "shared memory budget exceeded");
 };
