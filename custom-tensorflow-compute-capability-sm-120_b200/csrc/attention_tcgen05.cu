@@ -9,16 +9,19 @@
 // src/cuda_kernels/sm120_c_interface.cu:232-268).
 //
 // One CTA owns 128 query rows of one batch entry and walks over the keys in tiles
-// of 128.  192 threads:
+// of 128.  320 threads:
 //   warp 0     TMA producer: Q once, then K and V tiles through two-stage rings
 //   warp 1     tcgen05.mma issuer and TMEM owner:
 //                S_j  = Q K_j^T        (128 x 128, K-major operands)       -> TMEM, double buffered
 //                PV_j = P_j V_j        (128 x D; P from shared memory, V as stored: D contiguous) -> TMEM
-//   warps 2-5  softmax: thread t owns query row t (TMEM lane t).  Per key tile:
-//                pass 1 over S_j: row maximum;  pass 2: p = exp2(s - m) -> bf16/fp16 into shared
-//                memory as the A operand of P_j V_j; then O = O * alpha + PV_{j-1} in registers
-//                (the running output row lives in the thread's registers, so nothing in TMEM is
-//                ever rescaled).  At the end O / l is written to global memory.
+//   warps 2-9  softmax: query row r (TMEM lane r) belongs to a PAIR of threads, one in warp w and one in
+//              warp w + 4 (both may read TMEM lanes 32 (w % 4) ..).  Each takes 64 of a tile's 128 keys
+//              and D / 2 of the output row.  Per key tile: the 64 scores are read from TMEM in one go,
+//              the two partial row maxima are exchanged through shared memory (a bounded wait on the
+//              partner's sequence word), p = exp2(s - m) goes as bf16/fp16 into shared memory as the A operand of
+//              P_j V_j, and O = O * alpha + PV_{j-1} is accumulated in registers (the running output
+//              row lives in registers, so nothing in TMEM is ever rescaled).  Two warps per scheduler
+//              hide each other's TMEM, MUFU and shared-memory latencies.  At the end O / l is written.
 // The score of tile j+1 is computed while P_j V_j runs and while the softmax warps work on
 // tile j; the exponentials (one MUFU op per score) are what bounds the kernel.
 //
@@ -39,7 +42,7 @@ namespace sm120 {
 
 constexpr int ATT_BM = 128;          // query rows per CTA
 constexpr int ATT_BN = 128;          // keys per tile
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;
 constexpr int ATT_KV_STAGES = 2;
 
 // 2^x by the hardware unit (MUFU.EX2); -inf gives 0
@@ -47,6 +50,33 @@ __device__ __forceinline__ float att_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// The two threads that share a query row hand each other one float per step (the partial row maximum of a key
+// tile; at the end the partial row sum).  Thread `mine` publishes value and step number; it then waits, bounded like
+// every other wait of the kernel, until its partner has published the same step.  Values alternate between two
+// slots, so a thread that is one step ahead never overwrites what its partner still has to read.
+__device__ __forceinline__ bool pair_exchange(volatile float* vals, volatile int* seq, int mine, int other, int step, float v,
+                                              float& from_partner, const WaitCtx& w) {
+    vals[(step & 1) * (2 * ATT_BM) + mine] = v;
+    __threadfence_block();
+    seq[mine] = step;
+    if (seq[other] < step) {
+        const unsigned long long t0 = global_timer_ns();
+        uint32_t spins = 0;
+        while (seq[other] < step) {
+            if ((++spins & 63u) == 0u) {
+                if (*w.abort_flag != 0u) return false;
+                if (global_timer_ns() - t0 > w.limit_ns) {
+                    raise_abort(w, 0x65000000u);
+                    return false;
+                }
+            }
+        }
+    }
+    __threadfence_block();
+    from_partner = vals[(step & 1) * (2 * ATT_BM) + other];
+    return true;
 }
 
 struct AttParams {
@@ -66,7 +96,8 @@ struct AttCfg {
     static constexpr uint32_t K_BYTES = ATT_BN * D * 2;              // the same layout, ATT_BN rows
     static constexpr uint32_t V_BYTES = ATT_BN * D * 2;              // [ATT_BN/64 key blocks][D/64 boxes][64 keys x 128 B]
     static constexpr uint32_t P_BYTES = ATT_BM * ATT_BN * 2;         // ATT_BN/64 blocks of [128 rows x 128 B]
-    static constexpr uint32_t BAR_BYTES = 256;
+    // barriers + the pair exchange: values [parity][half][row] and sequence words [half][row]
+    static constexpr uint32_t BAR_BYTES = 256 + 2 * 2 * ATT_BM * 4 + 2 * ATT_BM * 4;
     static constexpr size_t SMEM_USED = Q_BYTES + ATT_KV_STAGES * (K_BYTES + V_BYTES) + P_BYTES + BAR_BYTES + 1024;
     // every CTA allocates all 512 TMEM columns, so two CTAs must never share an SM: request more than half of its shared memory
     static constexpr size_t SMEM = SMEM_USED > 118784 ? SMEM_USED : 118784;
@@ -105,6 +136,9 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t drain_bar = smem_u32(bars + 17);
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
     volatile uint32_t* abort_flag = tmem_holder + 1;
+    volatile float* xchg = reinterpret_cast<volatile float*>(reinterpret_cast<uint8_t*>(bars) + 256);      // [2][2][ATT_BM]
+    volatile int* xseq = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 256 + 2 * 2 * ATT_BM * 4);   // [2][ATT_BM]
+    if (threadIdx.x < 2 * ATT_BM) xseq[threadIdx.x] = 0;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -127,12 +161,12 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             mbar_init(v_full + 8 * s, 1);
             mbar_init(v_empty + 8 * s, 1);
             mbar_init(s_full + 8 * s, 1);
-            mbar_init(s_empty + 8 * s, 4);          // one arrival per softmax warp
+            mbar_init(s_empty + 8 * s, 8);          // one arrival per softmax warp
         }
-        mbar_init(p_full, 4);
+        mbar_init(p_full, 8);
         mbar_init(p_empty, 1);
         mbar_init(pv_full, 1);
-        mbar_init(pv_empty, 4);
+        mbar_init(pv_empty, 8);
         mbar_init(drain_bar, 1);
         *abort_flag = 0u;
         fence_barrier_init();
@@ -274,64 +308,70 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     } else {
         // ------------------------------ softmax and output ------------------------------
+        constexpr int HD = D / 2;                              // output columns per thread
         const int lane_group = warp & 3;                       // TMEM lanes [32 * lane_group, +32)
+        const int half = (warp - 2) >> 2;                      // which 64 keys of a tile, which half of the output row
         const int row = lane_group * 32 + lane;                // this thread's query row inside the tile
         const int q = q0 + row;
         const int key_limit = p.causal ? min(p.seq_k, q + p.seq_k - p.seq_q + 1) : p.seq_k;   // keys [0, key_limit) count
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
-        const uint32_t p_row = p_smem + static_cast<uint32_t>(row) * 128u;
+        // this thread's 64 keys are the 128-byte row `row` of 64-key block `half` of P
+        const uint32_t p_row = p_smem + static_cast<uint32_t>(half) * (128 * 128) + static_cast<uint32_t>(row) * 128u;
         const uint32_t swz = static_cast<uint32_t>(row & 7);
-        float o[D];
+        const int xmine = half * ATT_BM + row, xother = (half ^ 1) * ATT_BM + row;   // this thread's and its partner's exchange slots
+        float o[HD];
 #pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.0f;
+        for (int i = 0; i < HD; ++i) o[i] = 0.0f;
         float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 1.0f;
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
             const uint32_t st = j & 1, ph = (j >> 1) & 1;
-            const int key0 = j * ATT_BN;
+            const int key0 = j * ATT_BN + half * 64;
             ok = mbar_wait(s_full + 8 * st, ph, wctx, 0x61000000u);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            const uint32_t t_s = t_lane + st * ATT_BN;
-            const bool edge = key0 + ATT_BN > key_limit;        // some keys of this tile do not count for this row
-            // pass 1: row maximum
-            float m_tile = -CUDART_INF_F;
+            const uint32_t t_s = t_lane + st * ATT_BN + half * 64;
+            uint32_t s0[32], s1[32];
+            __syncwarp();
+            tmem_ld_32x32(t_s, s0);
+            tmem_ld_32x32(t_s + 32, s1);
+            tmem_ld_wait_regs(s0);
+            tmem_ld_wait_regs(s1);
+            tcgen05_fence_before();                             // S_j is in registers: the buffer may take S_{j+2}
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty + 8 * st);
+            const bool edge = key0 + 64 > key_limit;            // some of this thread's keys do not count for this row
+            float m_part = -CUDART_INF_F;
 #pragma unroll
-            for (int c = 0; c < ATT_BN / 32; ++c) {
-                uint32_t s[32];
-                __syncwarp();
-                tmem_ld_32x32_sync(t_s + c * 32, s);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float v = __uint_as_float(s[i]);
-                    if (!edge || key0 + c * 32 + i < key_limit) m_tile = fmaxf(m_tile, v);
-                }
+            for (int i = 0; i < 32; ++i) {
+                if (!edge || key0 + i < key_limit) m_part = fmaxf(m_part, __uint_as_float(s0[i]));
+                if (!edge || key0 + 32 + i < key_limit) m_part = fmaxf(m_part, __uint_as_float(s1[i]));
             }
+            // the row maximum of the tile: this thread's 64 keys and its partner's
+            float m_other = -CUDART_INF_F;
+            ok = pair_exchange(xchg, xseq, xmine, xother, j + 1, m_part, m_other, wctx);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            const float m_tile = fmaxf(m_part, m_other);
             const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
             const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;      // a row without any key so far
-            const float alpha = att_exp2(m_run - m_use);                        // 0 for the first tile (m_run = -inf)
-            // the P buffer is free once P_{j-1} V_{j-1} has been issued AND completed
+            const float alpha = att_exp2(m_run - m_use);                     // 0 for the first tile (m_run = -inf)
+            // the P buffer is free once P_{j-1} V_{j-1} has completed
             ok = mbar_wait(p_empty, (j & 1) ^ 1u, wctx, 0x62000000u);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
-            // pass 2: p = exp2(s * scale_log2 - m), row sum, P -> shared memory (16-bit, 128-byte swizzle)
-            float l_tile = 0.0f;
+            // p = exp2(s * scale_log2 - m), partial row sum, P -> shared memory (16-bit, 128-byte swizzle)
+            float l_part = 0.0f;
 #pragma unroll
-            for (int c = 0; c < ATT_BN / 32; ++c) {
-                uint32_t s[32];
-                __syncwarp();
-                tmem_ld_32x32_sync(t_s + c * 32, s);
-                if (c == ATT_BN / 32 - 1) {                     // S_j is in registers: the buffer may take S_{j+2}
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(s_empty + 8 * st);
-                }
+            for (int c = 0; c < 2; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = att_exp2(fmaf(__uint_as_float(s[i]), p.scale_log2, -m_use));
-                    float p1 = att_exp2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -m_use));
+                    const float x0 = __uint_as_float(c == 0 ? s0[i] : s1[i]);
+                    const float x1 = __uint_as_float(c == 0 ? s0[i + 1] : s1[i + 1]);
+                    float p0 = att_exp2(fmaf(x0, p.scale_log2, -m_use));
+                    float p1 = att_exp2(fmaf(x1, p.scale_log2, -m_use));
                     if (edge) {
                         if (key0 + c * 32 + i >= key_limit) p0 = 0.0f;
                         if (key0 + c * 32 + i + 1 >= key_limit) p1 = 0.0f;
@@ -339,37 +379,35 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     if (p.out_bf16) {
                         const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                         packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                        l_tile += __low2float(h) + __high2float(h);     // the sum of what the tensor cores will multiply
+                        l_part += __low2float(h) + __high2float(h);     // the sum of what the tensor cores will multiply
                     } else {
                         const __half2 h = __floats2half2_rn(p0, p1);
                         packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                        l_tile += __low2float(h) + __high2float(h);
+                        l_part += __low2float(h) + __high2float(h);
                     }
                 }
-                // 32 keys = 64 bytes = four 16-byte pieces of this row in 64-key block c / 2
-                const uint32_t blk = p_row + static_cast<uint32_t>(c >> 1) * (128 * 128);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const uint32_t piece = static_cast<uint32_t>((c & 1) * 4 + k);
-                    st_shared_v4(blk + ((piece ^ swz) << 4), packed[4 * k], packed[4 * k + 1], packed[4 * k + 2], packed[4 * k + 3]);
+                    const uint32_t piece = static_cast<uint32_t>(c * 4 + k);
+                    st_shared_v4(p_row + ((piece ^ swz) << 4), packed[4 * k], packed[4 * k + 1], packed[4 * k + 2], packed[4 * k + 3]);
                 }
             }
-            l_run = fmaf(l_run, alpha, l_tile);
+            l_run = fmaf(l_run, alpha, l_part);
             m_run = m_new;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
-            // O_{j-1} = O_{j-2} * alpha_{j-1} + P_{j-1} V_{j-1}: the product finished long ago
+            // O_{j-1} = O_{j-2} * alpha_{j-1} + P_{j-1} V_{j-1}: that product finished long ago
             if (j > 0) {
                 ok = mbar_wait(pv_full, (j - 1) & 1, wctx, 0x63000000u);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tcgen05_fence_after();
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int c = 0; c < HD / 32; ++c) {
                     uint32_t pv[32];
                     __syncwarp();
-                    tmem_ld_32x32_sync(t_lane + 2 * ATT_BN + c * 32, pv);
+                    tmem_ld_32x32_sync(t_lane + 2 * ATT_BN + half * HD + c * 32, pv);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(pv[i]));
                 }
@@ -385,21 +423,25 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (ok) {
                 tcgen05_fence_after();
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int c = 0; c < HD / 32; ++c) {
                     uint32_t pv[32];
                     __syncwarp();
-                    tmem_ld_32x32_sync(t_lane + 2 * ATT_BN + c * 32, pv);
+                    tmem_ld_32x32_sync(t_lane + 2 * ATT_BN + half * HD + c * 32, pv);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(pv[i]));
                 }
                 tcgen05_fence_before();
             }
         }
+        // the row sum is the sum of the pair's partial sums (both used the same maxima)
+        float l_other = 0.0f;
+        if (ok) ok = pair_exchange(xchg, xseq, xmine, xother, n_kv + 1, l_run, l_other, wctx);
+        const float l_row = l_run + l_other;
         if (ok && q < p.seq_q) {
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * p.seq_q + q) * D);
+            const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * p.seq_q + q) * D + half * HD);
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
+            for (int c = 0; c < HD / 8; ++c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {

@@ -26,7 +26,7 @@ cudaError_t activation_launch(const void* in, void* out, long long n, const void
                               int act, int dtype, int sm_count, cudaStream_t stream);
 cudaError_t softmax_launch(const void* in, void* out, long long outer, long long axis, long long inner, int dtype, int out_dtype,
                            float scale, const float* mask, long long mask_rows, float mask_factor, int causal, long long seq_q,
-                           cudaStream_t stream);
+                           int sm_count, cudaStream_t stream);
 bool attention_fused_supported(int dtype, long long batch, long long seq_q, long long seq_k, long long head_dim, const void* q,
                                const void* k, const void* v, const void* out);
 cudaError_t attention_fused_launch(const void* q, const void* k, const void* v, void* out, long long batch, long long seq_q,
@@ -508,7 +508,7 @@ cudaError_t softmax_common(const void* logits, void* output, int64_t outer, int6
     if (e != cudaSuccess) return e;
     e = query_device(device, &sms);
     if (e != cudaSuccess) return e;
-    e = softmax_launch(logits, output, outer, axis, inner, dtype, out_dtype, scale, mask, mask_rows, mask_factor, causal, seq_q, stream);
+    e = softmax_launch(logits, output, outer, axis, inner, dtype, out_dtype, scale, mask, mask_rows, mask_factor, causal, seq_q, sms, stream);
     if (e == cudaSuccess) {
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
         t_last_kernel = "softmax_rows";

@@ -63,66 +63,83 @@ __device__ __forceinline__ float logit_of(const SoftmaxParams& p, float raw, lon
 constexpr int SM_WARPS = 8;
 
 // One warp per row; NV 16-byte vectors per lane hold the whole row (cols <= 32 * VEC * NV, cols % VEC == 0,
-// rows 16-byte aligned).
+// rows 16-byte aligned).  The grid is persistent (a few CTAs per SM) and every warp walks over rows
+// row, row + W, ...: the raw vectors of its NEXT row are requested before the current row is reduced, so
+// loads are in flight all the time instead of only at the start of a short-lived CTA.
 // TO is T, or a 16-bit type when T is float (fp32 scores in, 16-bit probabilities out for the P.V product).
 template <typename T, typename TO, int NV>
 __global__ void __launch_bounds__(32 * SM_WARPS)
 sm120_softmax_rows_kernel(const SoftmaxParams p) {
     constexpr int VEC = 16 / sizeof(T);
     const int lane = threadIdx.x & 31;
-    const long long row = static_cast<long long>(blockIdx.x) * SM_WARPS + (threadIdx.x >> 5);
-    if (row >= p.rows) return;
-    const T* in = static_cast<const T*>(p.in) + row * p.cols;
-    TO* out = static_cast<TO*>(p.out) + row * p.cols;
+    const long long nwarps = static_cast<long long>(gridDim.x) * SM_WARPS;
     const long long nvec = p.cols / VEC;
-    float v[NV][VEC];
-    float m = -CUDART_INF_F;
+    long long row = static_cast<long long>(blockIdx.x) * SM_WARPS + (threadIdx.x >> 5);
+    uint4 raw[NV];
+    if (row < p.rows) {
+        const uint4* in = reinterpret_cast<const uint4*>(static_cast<const T*>(p.in) + row * p.cols);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const long long iv = lane + 32ll * i;
-        if (iv < nvec) {
-            const uint4 w = __ldcs(reinterpret_cast<const uint4*>(in) + iv);
-            const T* e = reinterpret_cast<const T*>(&w);
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32ll * i < nvec) raw[i] = __ldcs(in + lane + 32 * i);
+    }
+    for (; row < p.rows; row += nwarps) {
+        float v[NV][VEC];
+        float m = -CUDART_INF_F;
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                v[i][k] = logit_of(p, sm_to_float<T>(e[k]), row, iv * VEC + k);
-                m = fmaxf(m, v[i][k]);
+        for (int i = 0; i < NV; ++i) {
+            const long long iv = lane + 32ll * i;
+            if (iv < nvec) {
+                const T* e = reinterpret_cast<const T*>(&raw[i]);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    v[i][k] = logit_of(p, sm_to_float<T>(e[k]), row, iv * VEC + k);
+                    m = fmaxf(m, v[i][k]);
+                }
             }
         }
-    }
+        // the next row's vectors travel while this row is reduced and written
+        const long long next = row + nwarps;
+        if (next < p.rows) {
+            const uint4* in = reinterpret_cast<const uint4*>(static_cast<const T*>(p.in) + next * p.cols);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if (m == -CUDART_INF_F) m = 0.0f;              // a fully masked row: every exponential is 0, handled below
-    float s = 0.0f;
+            for (int i = 0; i < NV; ++i)
+                if (lane + 32ll * i < nvec) raw[i] = __ldcs(in + lane + 32 * i);
+        }
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        if (lane + 32ll * i < nvec) {
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        if (m == -CUDART_INF_F) m = 0.0f;              // a fully masked row: every exponential is 0, handled below
+        float s = 0.0f;
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                v[i][k] = sm_exp<TO>(v[i][k] - m);
-                s += v[i][k];
+        for (int i = 0; i < NV; ++i) {
+            if (lane + 32ll * i < nvec) {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    v[i][k] = sm_exp<TO>(v[i][k] - m);
+                    s += v[i][k];
+                }
             }
         }
-    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-    const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+        TO* out = static_cast<TO*>(p.out) + row * p.cols;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const long long iv = lane + 32ll * i;
-        if (iv < nvec) {
-            if constexpr (sizeof(TO) == sizeof(T)) {
-                uint4 w;
-                TO* e = reinterpret_cast<TO*>(&w);
+        for (int i = 0; i < NV; ++i) {
+            const long long iv = lane + 32ll * i;
+            if (iv < nvec) {
+                if constexpr (sizeof(TO) == sizeof(T)) {
+                    uint4 w;
+                    TO* e = reinterpret_cast<TO*>(&w);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) e[k] = sm_from_float<TO>(v[i][k] * inv);
-                __stcs(reinterpret_cast<uint4*>(out) + iv, w);
-            } else {                                    // four fp32 in, four 16-bit values (8 bytes) out
-                uint2 w;
-                TO* e = reinterpret_cast<TO*>(&w);
+                    for (int k = 0; k < VEC; ++k) e[k] = sm_from_float<TO>(v[i][k] * inv);
+                    __stcs(reinterpret_cast<uint4*>(out) + iv, w);
+                } else {                                    // four fp32 in, four 16-bit values (8 bytes) out
+                    uint2 w;
+                    TO* e = reinterpret_cast<TO*>(&w);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) e[k] = sm_from_float<TO>(v[i][k] * inv);
-                __stcs(reinterpret_cast<uint2*>(out) + iv, w);
+                    for (int k = 0; k < VEC; ++k) e[k] = sm_from_float<TO>(v[i][k] * inv);
+                    __stcs(reinterpret_cast<uint2*>(out) + iv, w);
+                }
             }
         }
     }
@@ -164,14 +181,15 @@ sm120_softmax_strided_kernel(const SoftmaxParams p, long long axis, long long in
 }
 
 template <typename T, typename TO>
-static cudaError_t softmax_typed(const SoftmaxParams& p, long long outer, long long axis, long long inner, cudaStream_t stream) {
+static cudaError_t softmax_typed(const SoftmaxParams& p, long long outer, long long axis, long long inner, int sm_count, cudaStream_t stream) {
     constexpr int VEC = 16 / sizeof(T);
     const bool aligned = (reinterpret_cast<uintptr_t>(p.in) & 15u) == 0 &&
                          (reinterpret_cast<uintptr_t>(p.out) & (VEC * sizeof(TO) - 1)) == 0;
     if (inner == 1 && aligned && axis % VEC == 0 && axis <= 32ll * VEC * 16) {
         const long long nvec = axis / VEC;
-        const long long blocks = (outer + SM_WARPS - 1) / SM_WARPS;
-        if (blocks > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+        long long blocks = (outer + SM_WARPS - 1) / SM_WARPS;
+        const long long cap = static_cast<long long>(sm_count) * 4;       // persistent: the kernel strides over the rows
+        if (blocks > cap) blocks = cap;
         const unsigned grid = static_cast<unsigned>(blocks);
         if (nvec <= 32)       sm120_softmax_rows_kernel<T, TO, 1><<<grid, 32 * SM_WARPS, 0, stream>>>(p);
         else if (nvec <= 64)  sm120_softmax_rows_kernel<T, TO, 2><<<grid, 32 * SM_WARPS, 0, stream>>>(p);
@@ -190,20 +208,20 @@ static cudaError_t softmax_typed(const SoftmaxParams& p, long long outer, long l
 // out_dtype is dtype, or a 16-bit type for fp32 logits.
 cudaError_t softmax_launch(const void* in, void* out, long long outer, long long axis, long long inner, int dtype, int out_dtype,
                            float scale, const float* mask, long long mask_rows, float mask_factor, int causal, long long seq_q,
-                           cudaStream_t stream) {
+                           int sm_count, cudaStream_t stream) {
     SoftmaxParams p{};
     p.in = in; p.out = out;
     p.rows = outer * inner; p.cols = axis;
     p.scale = scale;
     p.mask = mask; p.mask_rows = mask_rows > 0 ? mask_rows : 1; p.mask_factor = mask_factor;
     p.causal = causal; p.seq_q = seq_q > 0 ? seq_q : 1;
-    if (dtype == SM120_DTYPE_FLOAT32 && out_dtype == SM120_DTYPE_FLOAT16) return softmax_typed<float, __half>(p, outer, axis, inner, stream);
-    if (dtype == SM120_DTYPE_FLOAT32 && out_dtype == SM120_DTYPE_BFLOAT16) return softmax_typed<float, __nv_bfloat16>(p, outer, axis, inner, stream);
+    if (dtype == SM120_DTYPE_FLOAT32 && out_dtype == SM120_DTYPE_FLOAT16) return softmax_typed<float, __half>(p, outer, axis, inner, sm_count, stream);
+    if (dtype == SM120_DTYPE_FLOAT32 && out_dtype == SM120_DTYPE_BFLOAT16) return softmax_typed<float, __nv_bfloat16>(p, outer, axis, inner, sm_count, stream);
     if (dtype != out_dtype) return cudaErrorInvalidValue;
     switch (dtype) {
-        case SM120_DTYPE_FLOAT32:  return softmax_typed<float, float>(p, outer, axis, inner, stream);
-        case SM120_DTYPE_FLOAT16:  return softmax_typed<__half, __half>(p, outer, axis, inner, stream);
-        case SM120_DTYPE_BFLOAT16: return softmax_typed<__nv_bfloat16, __nv_bfloat16>(p, outer, axis, inner, stream);
+        case SM120_DTYPE_FLOAT32:  return softmax_typed<float, float>(p, outer, axis, inner, sm_count, stream);
+        case SM120_DTYPE_FLOAT16:  return softmax_typed<__half, __half>(p, outer, axis, inner, sm_count, stream);
+        case SM120_DTYPE_BFLOAT16: return softmax_typed<__nv_bfloat16, __nv_bfloat16>(p, outer, axis, inner, sm_count, stream);
         default: return cudaErrorInvalidValue;
     }
 }
