@@ -79,6 +79,47 @@ __device__ __forceinline__ bool pair_exchange(volatile float* vals, volatile int
     return true;
 }
 
+// p = exp2(s * scale_log2 - m) for this thread's 64 keys, as 16-bit values into its 128-byte row of P (eight 16-byte
+// pieces under the 128-byte swizzle); returns the row-sum contribution.  EDGE: keys at or beyond key_limit count as 0
+// (only tiles that straddle the row's limit pay for the per-key tests).  The sum adds the unrounded exponentials:
+// rounding each to 16 bits first costs two conversions per pair and changes the sum by a relative 2^-9 / sqrt(keys),
+// far inside the output's own rounding.
+template <bool EDGE>
+__device__ __forceinline__ float att_exp_store(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float scale_log2, float m_use,
+                                               int key0, int key_limit, bool bf16, uint32_t p_row, uint32_t swz) {
+    float l_a = 0.0f, l_b = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float x0 = __uint_as_float(c == 0 ? s0[i] : s1[i]);
+            const float x1 = __uint_as_float(c == 0 ? s0[i + 1] : s1[i + 1]);
+            float p0 = att_exp2(fmaf(x0, scale_log2, -m_use));
+            float p1 = att_exp2(fmaf(x1, scale_log2, -m_use));
+            if constexpr (EDGE) {
+                if (key0 + c * 32 + i >= key_limit) p0 = 0.0f;
+                if (key0 + c * 32 + i + 1 >= key_limit) p1 = 0.0f;
+            }
+            l_a += p0;
+            l_b += p1;
+            if (bf16) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+                const __half2 h = __floats2half2_rn(p0, p1);
+                packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t piece = static_cast<uint32_t>(c * 4 + k);
+            st_shared_v4(p_row + ((piece ^ swz) << 4), packed[4 * k], packed[4 * k + 1], packed[4 * k + 2], packed[4 * k + 3]);
+        }
+    }
+    return l_a + l_b;
+}
+
 struct AttParams {
     int seq_q, seq_k, batch;         // batch = batch_size x heads
     int causal;                      // key k of query q is used when k <= q + seq_k - seq_q
@@ -342,11 +383,22 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty + 8 * st);
             const bool edge = key0 + 64 > key_limit;            // some of this thread's keys do not count for this row
+            // (the per-key tests exist only in the branch for tiles that straddle this row's key limit)
             float m_part = -CUDART_INF_F;
+            if (!edge) {
+                float ma = -CUDART_INF_F, mb = -CUDART_INF_F;       // two chains: the maxima do not depend on one another
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                if (!edge || key0 + i < key_limit) m_part = fmaxf(m_part, __uint_as_float(s0[i]));
-                if (!edge || key0 + 32 + i < key_limit) m_part = fmaxf(m_part, __uint_as_float(s1[i]));
+                for (int i = 0; i < 32; ++i) {
+                    ma = fmaxf(ma, __uint_as_float(s0[i]));
+                    mb = fmaxf(mb, __uint_as_float(s1[i]));
+                }
+                m_part = fmaxf(ma, mb);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (key0 + i < key_limit) m_part = fmaxf(m_part, __uint_as_float(s0[i]));
+                    if (key0 + 32 + i < key_limit) m_part = fmaxf(m_part, __uint_as_float(s1[i]));
+                }
             }
             // the row maximum of the tile: this thread's 64 keys and its partner's
             float m_other = -CUDART_INF_F;
@@ -362,37 +414,9 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             // p = exp2(s * scale_log2 - m), partial row sum, P -> shared memory (16-bit, 128-byte swizzle)
-            float l_part = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float x0 = __uint_as_float(c == 0 ? s0[i] : s1[i]);
-                    const float x1 = __uint_as_float(c == 0 ? s0[i + 1] : s1[i + 1]);
-                    float p0 = att_exp2(fmaf(x0, p.scale_log2, -m_use));
-                    float p1 = att_exp2(fmaf(x1, p.scale_log2, -m_use));
-                    if (edge) {
-                        if (key0 + c * 32 + i >= key_limit) p0 = 0.0f;
-                        if (key0 + c * 32 + i + 1 >= key_limit) p1 = 0.0f;
-                    }
-                    if (p.out_bf16) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                        l_part += __low2float(h) + __high2float(h);     // the sum of what the tensor cores will multiply
-                    } else {
-                        const __half2 h = __floats2half2_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                        l_part += __low2float(h) + __high2float(h);
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t piece = static_cast<uint32_t>(c * 4 + k);
-                    st_shared_v4(p_row + ((piece ^ swz) << 4), packed[4 * k], packed[4 * k + 1], packed[4 * k + 2], packed[4 * k + 3]);
-                }
-            }
-            l_run = fmaf(l_run, alpha, l_part);
+            const float l_tile = edge ? att_exp_store<true>(s0, s1, p.scale_log2, m_use, key0, key_limit, p.out_bf16 != 0, p_row, swz)
+                                      : att_exp_store<false>(s0, s1, p.scale_log2, m_use, key0, key_limit, p.out_bf16 != 0, p_row, swz);
+            l_run = fmaf(l_run, alpha, l_tile);
             m_run = m_new;
             fence_proxy_async_smem();
             __syncwarp();

@@ -67,7 +67,9 @@ constexpr int SM_WARPS = 8;
 // row, row + W, ...: the raw vectors of its NEXT row are requested before the current row is reduced, so
 // loads are in flight all the time instead of only at the start of a short-lived CTA.
 // TO is T, or a 16-bit type when T is float (fp32 scores in, 16-bit probabilities out for the P.V product).
-template <typename T, typename TO, int NV>
+// PLAIN: no mask and no causal cut (the per-element tests of the masked form are compiled out: fully unrolled
+// they make the kernel so large that it stalls on instruction fetch).
+template <typename T, typename TO, int NV, bool PLAIN>
 __global__ void __launch_bounds__(32 * SM_WARPS)
 sm120_softmax_rows_kernel(const SoftmaxParams p) {
     constexpr int VEC = 16 / sizeof(T);
@@ -92,7 +94,8 @@ sm120_softmax_rows_kernel(const SoftmaxParams p) {
                 const T* e = reinterpret_cast<const T*>(&raw[i]);
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
-                    v[i][k] = logit_of(p, sm_to_float<T>(e[k]), row, iv * VEC + k);
+                    if constexpr (PLAIN) v[i][k] = sm_to_float<T>(e[k]) * p.scale;
+                    else v[i][k] = logit_of(p, sm_to_float<T>(e[k]), row, iv * VEC + k);
                     m = fmaxf(m, v[i][k]);
                 }
             }
@@ -191,11 +194,18 @@ static cudaError_t softmax_typed(const SoftmaxParams& p, long long outer, long l
         const long long cap = static_cast<long long>(sm_count) * 4;       // persistent: the kernel strides over the rows
         if (blocks > cap) blocks = cap;
         const unsigned grid = static_cast<unsigned>(blocks);
-        if (nvec <= 32)       sm120_softmax_rows_kernel<T, TO, 1><<<grid, 32 * SM_WARPS, 0, stream>>>(p);
-        else if (nvec <= 64)  sm120_softmax_rows_kernel<T, TO, 2><<<grid, 32 * SM_WARPS, 0, stream>>>(p);
-        else if (nvec <= 128) sm120_softmax_rows_kernel<T, TO, 4><<<grid, 32 * SM_WARPS, 0, stream>>>(p);
-        else if (nvec <= 256) sm120_softmax_rows_kernel<T, TO, 8><<<grid, 32 * SM_WARPS, 0, stream>>>(p);
-        else                  sm120_softmax_rows_kernel<T, TO, 16><<<grid, 32 * SM_WARPS, 0, stream>>>(p);
+        const bool plain = p.mask == nullptr && !p.causal;
+#define SM120_SOFTMAX_ROWS(NV_)                                                                                   \
+    do {                                                                                                          \
+        if (plain) sm120_softmax_rows_kernel<T, TO, NV_, true><<<grid, 32 * SM_WARPS, 0, stream>>>(p);            \
+        else sm120_softmax_rows_kernel<T, TO, NV_, false><<<grid, 32 * SM_WARPS, 0, stream>>>(p);                 \
+    } while (0)
+        if (nvec <= 32)       SM120_SOFTMAX_ROWS(1);
+        else if (nvec <= 64)  SM120_SOFTMAX_ROWS(2);
+        else if (nvec <= 128) SM120_SOFTMAX_ROWS(4);
+        else if (nvec <= 256) SM120_SOFTMAX_ROWS(8);
+        else                  SM120_SOFTMAX_ROWS(16);
+#undef SM120_SOFTMAX_ROWS
         return cudaGetLastError();
     }
     const long long blocks = outer * inner;
