@@ -974,15 +974,14 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
     const uint32_t swz = static_cast<uint32_t>(ROWB == 128 ? (lane & 7) : ((lane >> 1) & 3)) << 4;
     uint32_t stores = 0;                                // TMA stores committed by this warp: picks the staging buffer
     int local = 0;
-    for (int tile = first_tile; tile < p.num_work; tile += tile_step, ++local) {
+    // K-range tail items (at most one per CTA, always its last item) are finished after this loop, out of line:
+    // a call inside the loop would make the compiler spill the loop's registers around it
+    const int hot_limit = p.tail_mode == 2 ? p.full_work : p.num_work;
+    int tile = first_tile;
+    bool aborted = false;
+    for (; tile < hot_limit; tile += tile_step, ++local) {
         const uint32_t buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        if (p.tail_mode == 2 && tile >= p.full_work) {          // a K-range tail item: at most one per CTA, the last
-            if (!splitk_tail_epilogue<BN, CG, EW>(p, wctx, tmem_base, acc_full_bar, acc_empty_addr, warp, lane, cta_rank, tile, buf,
-                                                  acc_phase))
-                break;
-            continue;
-        }
         int bz, tm, n0, width;
         decode_work(tile, p, BN, bz, tm, n0, width);
         const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
@@ -994,7 +993,7 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
 
         bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
         ok = __all_sync(0xFFFFFFFFu, ok);
-        if (!ok) break;
+        if (!ok) { aborted = true; break; }
         tcgen05_fence_after();
         if (p.trace != nullptr && warp == 2 && lane == 0 && local < TRACE_TILES)
             p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 2] = clock64();
@@ -1088,6 +1087,9 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
         if (p.trace != nullptr && warp == 2 && lane == 0 && local < TRACE_TILES)
             p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 3] = clock64();
     }
+    if (!aborted && tile < p.num_work)
+        splitk_tail_epilogue<BN, CG, EW>(p, wctx, tmem_base, acc_full_bar, acc_empty_addr, warp, lane, cta_rank, tile,
+                                         static_cast<uint32_t>(local & 1), static_cast<uint32_t>((local >> 1) & 1));
     if (lane == 0) {
         bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
         if (p.num_dests > 1) {
