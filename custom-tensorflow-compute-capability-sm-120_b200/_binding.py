@@ -29,7 +29,7 @@ QUANTIZE_FP8_STATIC_MAX_ELEMENTS = 268435456      # SM120_QUANTIZE_FP8_STATIC_MA
 
 # SM120_TUNE_* bits of SM120GemmDesc.tuning (per-call overrides for tests and tuning runs)
 TUNE_CTA_GROUP_1, TUNE_CTA_GROUP_2, TUNE_EPI_WARPS_8, TUNE_EPI_WARPS_16 = 0x1, 0x2, 0x4, 0x8
-TUNE_NO_SPLIT_TAIL, TUNE_TRACE, TUNE_NO_SPLIT_K = 0x10, 0x20, 0x40
+TUNE_NO_SPLIT_TAIL, TUNE_TRACE = 0x10, 0x20
 TRACE_WORDS_PER_CTA, TRACE_MAX_CTAS = 40, 160
 TRACE_BYTES = TRACE_MAX_CTAS * TRACE_WORDS_PER_CTA * 8
 

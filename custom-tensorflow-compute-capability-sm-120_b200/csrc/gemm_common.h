@@ -41,8 +41,6 @@ struct GemmProblem {
     int num_extra_dests;
     int tuning;                      // SM120GemmDesc::tuning (SM120_TUNE_* bits)
     void* trace;                     // null, or the caller's buffer for SM120_TUNE_TRACE
-    void* workspace;                 // null, or caller scratch that the tensor-core kernel may use (K-range tail cut)
-    uint64_t workspace_bytes;
 };
 
 __host__ __device__ inline int dtype_size(int dtype) {

@@ -10,7 +10,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
-#include <time.h>
 #include <atomic>
 
 #include "gemm_tcgen05_kernel.cuh"
@@ -24,16 +23,16 @@ __device__ unsigned long long g_sm120_probe[2];
 // the variants are compiled in gemm_tcgen05_inst_*.cu
 #define SM120_TC_EXTERN(KIND_, BN_, ST_, CG_) \
     extern template cudaError_t launch_variant<KIND_, BN_, ST_, CG_>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&, \
-                                                                     const TcParams&, int, int, cudaStream_t, bool, void*, uint64_t);
+                                                                     const TcParams&, int, int, cudaStream_t, bool);
 SM120_TC_EXTERN(KIND_F16, 256, 6, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
 SM120_TC_EXTERN(KIND_F8, 256, 6, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
 SM120_TC_EXTERN(KIND_TF32, 128, 8, 2) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
 #undef SM120_TC_EXTERN
 // the pair tile with 16 epilogue warps, for short-K (store-bound) problems
 extern template cudaError_t launch_variant<KIND_F16, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                                    const TcParams&, int, int, cudaStream_t, bool, void*, uint64_t);
+                                                                    const TcParams&, int, int, cudaStream_t, bool);
 extern template cudaError_t launch_variant<KIND_F8, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                                   const TcParams&, int, int, cudaStream_t, bool, void*, uint64_t);
+                                                                   const TcParams&, int, int, cudaStream_t, bool);
 
 // ---------------------------------------------------------------------------
 // Host side
@@ -138,22 +137,6 @@ static bool encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inne
 bool tc_encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch, int64_t pitch,
                   int64_t bstride, uint32_t box_inner, uint32_t box_outer) {
     return encode_3d(map, ptr, dtype, inner, outer, nbatch, pitch, bstride, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_128B);
-}
-
-unsigned long long tc_next_epoch() {
-    // starts at a value derived from the clock and this process's address space, then counts up
-    static std::atomic<unsigned long long> epoch{0};
-    unsigned long long e = epoch.load(std::memory_order_relaxed);
-    if (e == 0) {
-        timespec ts;
-        clock_gettime(CLOCK_REALTIME, &ts);
-        unsigned long long seed = (static_cast<unsigned long long>(ts.tv_sec) << 30) ^ static_cast<unsigned long long>(ts.tv_nsec) ^
-                                  (reinterpret_cast<uintptr_t>(&epoch) << 17);
-        seed = (seed * 0x9E3779B97F4A7C15ull) | 1ull;
-        unsigned long long expected = 0;
-        epoch.compare_exchange_strong(expected, seed);
-    }
-    return epoch.fetch_add(1, std::memory_order_relaxed) + 1;
 }
 
 // Device address of `device`'s status words (looked up once per device, with that device current).
@@ -285,13 +268,6 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.trace = static_cast<unsigned long long*>(p.trace);
     tp.wait_limit_ns = wait_limit_ns;
     const bool split_tail = (p.tuning & SM120_TUNE_NO_SPLIT_TAIL) == 0;
-    // workspace for the K-range cut of a short last wave (16-byte aligned), unless the call forbids that cut
-    void* split_k_ws = nullptr;
-    uint64_t split_k_ws_bytes = 0;
-    if ((p.tuning & SM120_TUNE_NO_SPLIT_K) == 0 && p.workspace != nullptr && (reinterpret_cast<uintptr_t>(p.workspace) & 15u) == 0) {
-        split_k_ws = p.workspace;
-        split_k_ws_bytes = p.workspace_bytes;
-    }
     {
         // device addresses of this device's status / probe words (looked up once per device)
         static std::atomic<unsigned long long*> probe_addr[64];
@@ -372,7 +348,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 #define SM120_TC_CASE(KIND_, BN_, ST_, CG_, NAME_)                                                       \
     do {                                                                                                 \
         if (kernel_name) *kernel_name = NAME_;                                                           \
-        return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail, split_k_ws, split_k_ws_bytes);       \
+        return launch_variant<KIND_, BN_, ST_, CG_>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail);       \
     } while (0)
 
     if (p.in_dtype == SM120_DTYPE_FLOAT32) {
@@ -384,7 +360,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
         if (cg == 2 && ew == 16) {
             if (kernel_name) *kernel_name = bf ? "tc_bf16_2cta_256x256x64_s5_e16" : "tc_f16_2cta_256x256x64_s5_e16";
-            return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail, split_k_ws, split_k_ws_bytes);
+            return launch_variant<KIND_F16, 256, 5, 2, 16>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail);
         }
         if (cg == 2) SM120_TC_CASE(KIND_F16, 256, 6, 2, bf ? "tc_bf16_2cta_256x256x64_s6" : "tc_f16_2cta_256x256x64_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F16, 256, 4, 1, bf ? "tc_bf16_128x256x64_s4" : "tc_f16_128x256x64_s4");
@@ -393,7 +369,7 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     } else {
         if (cg == 2 && ew == 16) {
             if (kernel_name) *kernel_name = "tc_e4m3_2cta_256x256x128_s5_e16";
-            return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail, split_k_ws, split_k_ws_bytes);
+            return launch_variant<KIND_F8, 256, 5, 2, 16>(ta, tb, tb_half, tc, tp, p.sm_count, p.device, p.stream, split_tail);
         }
         if (cg == 2) SM120_TC_CASE(KIND_F8, 256, 6, 2, "tc_e4m3_2cta_256x256x128_s6");
         if (bn == 256) SM120_TC_CASE(KIND_F8, 256, 4, 1, "tc_e4m3_128x256x128_s4");

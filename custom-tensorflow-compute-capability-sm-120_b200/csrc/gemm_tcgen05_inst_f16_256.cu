@@ -4,5 +4,5 @@
 
 namespace sm120 {
 template cudaError_t launch_variant<KIND_F16, 256, 4, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                        const TcParams&, int, int, cudaStream_t, bool, void*, uint64_t);
+                                                        const TcParams&, int, int, cudaStream_t, bool);
 }  // namespace sm120

@@ -4,7 +4,7 @@
 
 namespace sm120 {
 template cudaError_t launch_variant<KIND_F8, 128, 6, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                        const TcParams&, int, int, cudaStream_t, bool, void*, uint64_t);
+                                                        const TcParams&, int, int, cudaStream_t, bool);
 template cudaError_t launch_variant<KIND_F8, 64, 8, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                        const TcParams&, int, int, cudaStream_t, bool, void*, uint64_t);
+                                                        const TcParams&, int, int, cudaStream_t, bool);
 }  // namespace sm120

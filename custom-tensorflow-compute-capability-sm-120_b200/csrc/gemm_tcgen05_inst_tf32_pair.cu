@@ -4,5 +4,5 @@
 
 namespace sm120 {
 template cudaError_t launch_variant<KIND_TF32, 128, 8, 2>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
-                                                        const TcParams&, int, int, cudaStream_t, bool, void*, uint64_t);
+                                                        const TcParams&, int, int, cudaStream_t, bool);
 }  // namespace sm120

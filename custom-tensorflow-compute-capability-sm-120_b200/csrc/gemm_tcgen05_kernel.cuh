@@ -110,12 +110,7 @@ struct TcParams {
     FastDiv div_group_span;         // group_m * tiles_n
     FastDiv div_group_m;            // rows of a whole group
     FastDiv div_group_last;         // rows of the last (possibly shorter) group
-    int num_work, full_work;        // work items: [0, full_work) are whole tiles, the rest are tail items (two per tile)
-    int tail_mode;                  // how a short last wave is cut: 1 = two column halves per tile, 2 = two K ranges per tile
-    int tail_kb_split;              // tail_mode 2: item 0 (the owner) multiplies k-blocks [0, split), item 1 (the helper) the rest
-    float* tail_ws;                 // tail_mode 2: the helpers' fp32 partial tiles, in caller workspace
-    unsigned long long* tail_flags; // tail_mode 2: one word per (tile, CTA of the pair, epilogue warp), set to tail_epoch by the helper
-    unsigned long long tail_epoch;  // a value no earlier launch has used
+    int num_work, full_work;        // work items: [0, full_work) are whole tiles, the rest are half-width tiles (two per tile)
     uint32_t idesc;
     uint32_t idesc_half;            // instruction descriptor of a half-width tile (N = BN / 2)
     uint32_t b_bytes_half;          // bytes of B one CTA loads per k-block of a half-width tile
@@ -420,42 +415,21 @@ __device__ __forceinline__ void decode_tile(int tile, const TcParams& p, int& bz
 }
 
 // Work item -> batch entry, row tile, first column and width.  The last
-// num_work - full_work items are two pieces of each of the last tiles: when the
-// tile count leaves the final wave less than half full, cutting those tiles in two
-// shortens the tail from one tile time to about half a tile time.  Two cuts exist:
-//   tail_mode 1  two column halves (256 x 128): independent items, but each needs 3/4 of a
-//                tile's operand bytes for 1/2 of its MMA cycles, and the TMA round trip then
-//                shows through the six-stage ring (measured: 0.6 of the MMA rate);
-//   tail_mode 2  two K ranges of the whole tile: the same bytes per MMA cycle as any other
-//                tile.  Item 1 (the helper) leaves its fp32 partial tile in workspace and sets a
-//                flag per epilogue warp; item 0 (the owner), which runs in the same wave on the
-//                neighbouring cluster, adds that partial to its own accumulator (always
-//                own + helper: a fixed order, so results are reproducible run to run) and
-//                finishes the tile.  Needs caller workspace.
+// num_work - full_work items are the two column halves of the last tiles: when the
+// tile count leaves the final wave less than half full, splitting those tiles
+// shortens the tail from one tile time to half a tile time.
 __device__ __forceinline__ void decode_work(int w, const TcParams& p, int bn, int& bz, int& tm, int& n0, int& width) {
     int tile = w, sel = 0;
     width = bn;
     if (w >= p.full_work) {
         const int h = w - p.full_work;
         tile = p.full_work + (h >> 1);
-        if (p.tail_mode == 1) {
-            sel = h & 1;
-            width = bn >> 1;
-        }
+        sel = h & 1;
+        width = bn >> 1;
     }
     int tn;
     decode_tile(tile, p, bz, tm, tn);
     n0 = tn * bn + sel * width;
-}
-
-// k-blocks [kb_begin, kb_end) that work item w multiplies: all of them, except for the K-range tail items
-__device__ __forceinline__ void work_k_range(int w, const TcParams& p, int& kb_begin, int& kb_end) {
-    kb_begin = 0;
-    kb_end = p.k_blocks;
-    if (p.tail_mode == 2 && w >= p.full_work) {
-        if (((w - p.full_work) & 1) == 0) kb_end = p.tail_kb_split;
-        else kb_begin = p.tail_kb_split;
-    }
 }
 
 // ---------------------------------------------------------------------------
@@ -842,100 +816,6 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const DestMaps*
     }
 }
 
-// Epilogue of ONE K-range tail item (tail_mode 2), for one epilogue warp.  Kept out of line: it runs at most once
-// per CTA and must not cost the straight-line epilogue any registers.
-//   helper (odd item):  accumulator -> workspace (fp32, one 16-byte piece per lane and step, coalesced), then a
-//                       release store of the launch's epoch into this warp's flag;
-//   owner (even item):  waits (bounded) for that flag, adds the helper's partial to its own accumulator and
-//                       finishes the tile: alpha / scales, bias, activation, cast, direct 16-byte stores.
-// Returns false when a wait ran out.
-template <int BN, int CG, int EW>
-static __device__ __noinline__ bool splitk_tail_epilogue(const TcParams& p, const WaitCtx& wctx, uint32_t tmem_base, uint32_t acc_full_bar,
-                                                         uint32_t acc_empty_addr, int warp, int lane, uint32_t cta_rank, int item,
-                                                         uint32_t buf, uint32_t acc_phase) {
-    constexpr int NSPLIT = EW / 4;
-    constexpr int CHUNKS = BN / (32 * NSPLIT);
-    const int lane_group = warp & 3;
-    const int part = (warp - 2) >> 2;
-    const int h = (item - p.full_work) >> 1;                       // which tail tile
-    const bool helper = ((item - p.full_work) & 1) != 0;
-    int bz, tm, n0, width;
-    decode_work(item, p, BN, bz, tm, n0, width);
-    const int row = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32 + lane;
-    const int colbase = n0 + part * (BN / NSPLIT);
-    // this warp's slice of the partial tile: CHUNKS x 8 steps of (32 lanes x 16 bytes)
-    const size_t warp_slot = (static_cast<size_t>(h) * CG + cta_rank) * EW + static_cast<size_t>(warp - 2);
-    float4* ws = reinterpret_cast<float4*>(p.tail_ws) + warp_slot * (CHUNKS * 8 * 32) + lane;
-    unsigned long long* flag = p.tail_flags + warp_slot;
-    bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
-    ok = __all_sync(0xFFFFFFFFu, ok);
-    if (!ok) return false;
-    tcgen05_fence_after();
-    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + buf * BN + part * (BN / NSPLIT);
-    if (!helper) {
-        // the helper's partial must be complete before it is read
-        bool seen = true;
-        if (lane == 0) {
-            const unsigned long long t0 = global_timer_ns();
-            uint32_t spins = 0;
-            for (;;) {
-                unsigned long long v;
-                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
-                if (v == p.tail_epoch) break;
-                if ((++spins & 63u) == 0u) {
-                    if (*wctx.abort_flag != 0u) { seen = false; break; }
-                    if (global_timer_ns() - t0 > wctx.limit_ns) { raise_abort(wctx, 0x32000000u); seen = false; break; }
-                }
-            }
-        }
-        seen = __all_sync(0xFFFFFFFFu, seen);
-        if (!seen) return false;
-    }
-    float alpha = p.alpha;
-    if (p.scale_a_dev != nullptr) alpha /= __ldg(p.scale_a_dev);
-    if (p.scale_b_dev != nullptr) alpha /= __ldg(p.scale_b_dev);
-#pragma unroll 1
-    for (int c = 0; c < CHUNKS; ++c) {
-        uint32_t acc[32];
-        __syncwarp();
-        tmem_ld_32x32_sync(t_row + c * 32, acc);
-        if (c == CHUNKS - 1) {                                     // the accumulator is in registers: hand the TMEM buffer back
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty_addr + 8 * buf);
-        }
-        if (helper) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-                ws[(c * 8 + k) * 32] = make_float4(__uint_as_float(acc[4 * k]), __uint_as_float(acc[4 * k + 1]),
-                                                   __uint_as_float(acc[4 * k + 2]), __uint_as_float(acc[4 * k + 3]));
-        } else {
-            const int col0 = colbase + c * 32;
-            float v[32];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float4 w = __ldcg(ws + (c * 8 + k) * 32);    // written by another SM: read through L2
-                v[4 * k + 0] = alpha * (__uint_as_float(acc[4 * k + 0]) + w.x);      // own K range first, then the helper's
-                v[4 * k + 1] = alpha * (__uint_as_float(acc[4 * k + 1]) + w.y);
-                v[4 * k + 2] = alpha * (__uint_as_float(acc[4 * k + 2]) + w.z);
-                v[4 * k + 3] = alpha * (__uint_as_float(acc[4 * k + 3]) + w.w);
-            }
-            if (col0 < p.N) {                                       // N is a multiple of 32 on this path: whole chunks only
-                if (p.bias != nullptr) bias_add_scalar32(p, col0, 32, v);
-                act_apply32<ACTC_DYNAMIC>(v, p.activation);
-                if (row < p.M)
-                    store_row32_direct(p, static_cast<long long>(bz) * p.stride_c + static_cast<long long>(row) * p.ldc + col0, 32, v);
-            }
-        }
-    }
-    if (helper) {
-        __threadfence();                                            // every lane's partial is visible device-wide ...
-        __syncwarp();
-        if (lane == 0) asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(flag), "l"(p.tail_epoch) : "memory");   // ... before the flag
-    }
-    return true;
-}
-
 // The common case, as straight-line code: the result goes out through TMA stores
 // (beta == 0, C aligned), N is a multiple of 32 (a 32-column chunk is inside the
 // matrix or outside it, never across its edge) and the bias, if any, can be read
@@ -974,16 +854,11 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
     const uint32_t swz = static_cast<uint32_t>(ROWB == 128 ? (lane & 7) : ((lane >> 1) & 3)) << 4;
     uint32_t stores = 0;                                // TMA stores committed by this warp: picks the staging buffer
     int local = 0;
-    // K-range tail items (at most one per CTA, always its last item) are finished after this loop, out of line:
-    // a call inside the loop would make the compiler spill the loop's registers around it
-    const int hot_limit = p.tail_mode == 2 ? p.full_work : p.num_work;
-    int tile = first_tile;
-    bool aborted = false;
-    for (; tile < hot_limit; tile += tile_step, ++local) {
-        const uint32_t buf = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
+    for (int tile = first_tile; tile < p.num_work; tile += tile_step, ++local) {
         int bz, tm, n0, width;
         decode_work(tile, p, BN, bz, tm, n0, width);
+        const uint32_t buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
         const int row0 = (tm * CG + static_cast<int>(cta_rank)) * BM + lane_group * 32;   // first row of this warp
         const int cols_per_warp = width / NSPLIT;
         const int colbase = n0 + half * cols_per_warp;
@@ -993,7 +868,7 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
 
         bool ok = mbar_wait(acc_full_bar + 8 * buf, acc_phase, wctx, 0x31000000u);
         ok = __all_sync(0xFFFFFFFFu, ok);
-        if (!ok) { aborted = true; break; }
+        if (!ok) break;
         tcgen05_fence_after();
         if (p.trace != nullptr && warp == 2 && lane == 0 && local < TRACE_TILES)
             p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 2] = clock64();
@@ -1087,9 +962,6 @@ __device__ __forceinline__ void epilogue_fast(const TcParams& p, const DestMaps*
         if (p.trace != nullptr && warp == 2 && lane == 0 && local < TRACE_TILES)
             p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local + 3] = clock64();
     }
-    if (!aborted && tile < p.num_work)
-        splitk_tail_epilogue<BN, CG, EW>(p, wctx, tmem_base, acc_full_bar, acc_empty_addr, warp, lane, cta_rank, tile,
-                                         static_cast<uint32_t>(local & 1), static_cast<uint32_t>((local >> 1) & 1));
     if (lane == 0) {
         bulk_wait_group_read<0>();     // shared memory must outlive the stores that read it
         if (p.num_dests > 1) {
@@ -1151,7 +1023,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fence_proxy_async_smem();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
-        if (p.tail_mode == 1) prefetch_tmap(&tmap_b_half);
+        if (p.num_work > p.full_work) prefetch_tmap(&tmap_b_half);
         prefetch_tmap(&dests.m[0]);
     }
     if (warp == 1) {
@@ -1199,11 +1071,9 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // MMAs read (a box of half the height, or fewer boxes), which is what keeps the short last
             // wave from being bound by the bytes it pulls out of L2
             const int n0 = nt + static_cast<int>(cta_rank) * (width / CG);
-            const bool half_item = p.tail_mode == 1 && tile >= p.full_work;
+            const bool half_item = tile >= p.full_work;
             const uint32_t stage_tx = half_item ? (A_BYTES + p.b_bytes_half) : STAGE_BYTES;
-            int kb_begin, kb_end;
-            work_k_range(tile, p, kb_begin, kb_end);
-            for (int kb = kb_begin; kb < kb_end; ++kb) {
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
                 if (first && kb == p.stall_kblock) { ok = false; break; }
                 bool w = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, wctx, 0x11000000u);
                 w = __all_sync(0xFFFFFFFFu, w);
@@ -1266,17 +1136,15 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             int local = 0;
             uint32_t acc_iter = 0;                          // accumulation runs issued so far: picks the TMEM buffer and the phase
             for (int tile = first_tile; ok && tile < p.num_work; tile += tile_step, ++local) {
-                const uint32_t idesc = (p.tail_mode == 1 && tile >= p.full_work) ? p.idesc_half : p.idesc;
+                const uint32_t idesc = tile < p.full_work ? p.idesc : p.idesc_half;
                 uint32_t buf = acc_iter & 1u;
                 uint32_t d_tmem = tmem_base + buf * BN;
                 int run_left = 0;                           // k-blocks left in the current accumulation run
-                int kb_begin, kb_end;
-                work_k_range(tile, p, kb_begin, kb_end);
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
                     bool w;
                     if (run_left == 0) {
                         // a new run (the only one of the tile, except on the fp32 path): its TMEM buffer must be free
-                        if (kb != kb_begin) {
+                        if (kb != 0) {
                             if (elect_one_sync()) {         // the previous run is complete, in both CTAs of a pair
                                 umma_commit<CG>(acc_full_bar + 8 * buf);
                                 if constexpr (CG == 2) umma_commit<CG>(map_to_cta(acc_full_bar + 8 * buf, 1u));
@@ -1298,7 +1166,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     w = __all_sync(0xFFFFFFFFu, w);
                     if (!w) { ok = false; break; }
                     tcgen05_fence_after();
-                    if (p.trace != nullptr && kb == kb_begin && lane == 0 && local < TRACE_TILES)
+                    if (p.trace != nullptr && kb == 0 && lane == 0 && local < TRACE_TILES)
                         p.trace[static_cast<size_t>(blockIdx.x) * TRACE_WORDS + 8 + 4 * local] = clock64();
                     const uint32_t soff = stage * (STAGE_BYTES >> 4);
                     if (elect_one_sync()) {
@@ -1381,8 +1249,6 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 // Host helpers defined in gemm_tcgen05.cu, shared with the attention kernel: a cached 3-D tensor map with the
 // 128-byte swizzle (extents, pitch and batch stride in elements), and the device's status words.
-// A 64-bit value that no earlier launch of this process used (and that stale workspace contents will not hold).
-unsigned long long tc_next_epoch();
 bool tc_encode_3d(CUtensorMap* map, const void* ptr, int dtype, int64_t inner, int64_t outer, int64_t nbatch, int64_t pitch,
                   int64_t bstride, uint32_t box_inner, uint32_t box_outer);
 unsigned int* tc_status_address(int device);
@@ -1394,8 +1260,7 @@ unsigned int* tc_status_address(int device);
 // ---------------------------------------------------------------------------
 template <int KIND, int BN, int STAGES, int CG, int EW = 8>
 cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb_half, const DestMaps& tc,
-                           const TcParams& tp, int sm_count, int device, cudaStream_t stream, bool split_tail,
-                           void* split_k_ws, uint64_t split_k_ws_bytes) {
+                           const TcParams& tp, int sm_count, int device, cudaStream_t stream, bool split_tail) {
     using Cfg = TileCfg<KIND, BN, STAGES, CG, EW>;
     static std::atomic<uint64_t> attr_done{0};     // one bit per device
     static std::atomic<int> max_clusters[64];      // CG == 2: co-resident clusters per device (0 = not asked yet)
@@ -1433,25 +1298,13 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const C
         }
         const int want = tp.num_tiles < clusters ? tp.num_tiles : clusters;
         cfg.gridDim = dim3(static_cast<unsigned>(2 * want), 1, 1);
-        // A final wave that is less than half full is cut into two items per tile: two K ranges when the caller
-        // gave workspace for the partial tiles (and the straight-line epilogue applies), else two column halves.
+        // A final wave that is less than half full is run as half-width tiles.
         TcParams t = tp;
         const int rest = tp.num_tiles % clusters;
         // (not with 16 epilogue warps: a warp's quarter of a half-width tile is narrower than its 64-column store)
         if (EW == 8 && tp.num_tiles > clusters && rest > 0 && 2 * rest <= clusters && split_tail) {
             t.full_work = tp.num_tiles - rest;
             t.num_work = t.full_work + 2 * rest;
-            t.tail_mode = 1;
-            const size_t flag_bytes = (static_cast<size_t>(rest) * CG * EW * sizeof(unsigned long long) + 255) & ~size_t(255);
-            const size_t need = flag_bytes + static_cast<size_t>(rest) * (CG * BM) * BN * sizeof(float);
-            if (split_k_ws != nullptr && split_k_ws_bytes >= need && tp.fast_epi && tp.num_dests == 1 && KIND != KIND_TF32 &&
-                tp.k_blocks >= 16) {
-                t.tail_mode = 2;
-                t.tail_kb_split = (tp.k_blocks * 9 + 15) / 16;      // the owner takes 9/16 of K: the helper's partial is there when it looks
-                t.tail_flags = static_cast<unsigned long long*>(split_k_ws);
-                t.tail_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(split_k_ws) + flag_bytes);
-                t.tail_epoch = tc_next_epoch();
-            }
         }
         return cudaLaunchKernelEx(&cfg, kern, ta, tb, tb_half, tc, t);
     } else {

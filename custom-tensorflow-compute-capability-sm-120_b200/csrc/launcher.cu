@@ -101,7 +101,7 @@ cudaError_t resolve(const SM120GemmDesc* d, GemmProblem* out) {
             return cudaErrorInvalidValue;
     }
     if (d->scale_a < 0.0f || d->scale_b < 0.0f) return cudaErrorInvalidValue;
-    if ((d->tuning & ~0x00FFFF7F) != 0) return cudaErrorInvalidValue;
+    if ((d->tuning & ~0x00FFFF3F) != 0) return cudaErrorInvalidValue;
     if ((d->tuning & SM120_TUNE_CTA_GROUP_1) && (d->tuning & SM120_TUNE_CTA_GROUP_2)) return cudaErrorInvalidValue;
     if ((d->tuning & SM120_TUNE_EPI_WARPS_8) && (d->tuning & SM120_TUNE_EPI_WARPS_16)) return cudaErrorInvalidValue;
     if (d->tuning & SM120_TUNE_TRACE) {
@@ -145,11 +145,6 @@ cudaError_t resolve(const SM120GemmDesc* d, GemmProblem* out) {
     p.optimization_level = d->optimization_level;
     p.tuning = d->tuning;
     p.trace = (d->tuning & SM120_TUNE_TRACE) ? d->workspace : nullptr;
-    // 16-bit and FP8 products may use the workspace for the K-range cut of a short last wave
-    if (p.trace == nullptr && d->in_dtype != SM120_DTYPE_FLOAT32) {
-        p.workspace = d->workspace;
-        p.workspace_bytes = d->workspace != nullptr ? d->workspace_bytes : 0;
-    }
     p.stream = d->stream;
     *out = p;
     return cudaSuccess;
@@ -303,12 +298,8 @@ cudaError_t sm120_ipc_close(void* base) {
 size_t sm120_matmul_workspace_bytes(const SM120GemmDesc* desc) {
     GemmProblem p;
     if (resolve(desc, &p) != cudaSuccess) return 0;
-    if (p.M == 0 || p.N == 0 || p.K == 0) return 0;
-    if (p.in_dtype == SM120_DTYPE_FLOAT32) return tf32x3_workspace_bytes(p);
-    // 16-bit and FP8: room for the K-range cut of a short last wave of 256 x 256 pair tiles: at most half of the
-    // co-resident clusters (74 on a 148-SM part, taken as 80) have a helper, each with one fp32 partial tile and flags
-    if (p.M <= 128 || p.N <= 128 || p.K < 1024) return 0;
-    return static_cast<size_t>(40) * 256 * 256 * sizeof(float) + 8192;
+    if (p.in_dtype != SM120_DTYPE_FLOAT32 || p.M == 0 || p.N == 0 || p.K == 0) return 0;
+    return tf32x3_workspace_bytes(p);
 }
 
 cudaError_t sm120_launch_matmul(const void* A, const void* B, void* C, int M, int N, int K, float alpha, float beta,

@@ -158,9 +158,7 @@ typedef struct SM120GemmDesc {
  * override that the chosen kernel has no variant for is ignored.
  *   CTA_GROUP_1 / _2     single-CTA tiles (128 x BN) / CTA-pair tiles (256 x 256)
  *   EPI_WARPS_8 / _16    epilogue warps per CTA (16 exists for pair tiles only)
- *   NO_SPLIT_TAIL        a short last wave is not cut into two items per tile
- *   NO_SPLIT_K           a short last wave is cut by columns even when workspace would allow the cut along K
- *                        (every output element is then one sequential sum over K, whatever the schedule)
+ *   NO_SPLIT_TAIL        a short last wave is not cut into half-width tiles
  *   GROUP_M(g)           raster group of g row tiles, 1 <= g <= 255 (0 = heuristic)
  *   STALL_KBLOCK(kb)     self-test of the bounded waits: every TMA producer stops
  *                        before k-block kb (0 <= kb <= 254) of its first tile, so a
@@ -185,7 +183,6 @@ typedef struct SM120GemmDesc {
 #define SM120_TUNE_EPI_WARPS_16    0x8
 #define SM120_TUNE_NO_SPLIT_TAIL   0x10
 #define SM120_TUNE_TRACE           0x20
-#define SM120_TUNE_NO_SPLIT_K      0x40
 #define SM120_TUNE_GROUP_M(g)      (((g) & 0xFF) << 8)
 #define SM120_TUNE_STALL_KBLOCK(kb) ((((kb) + 1) & 0xFF) << 16)
 #define SM120_TRACE_WORDS_PER_CTA  40
@@ -250,17 +247,8 @@ cudaError_t sm120_ipc_close(void* base);
  * sums are added in registers with round-to-nearest.  The relative Frobenius
  * error against float64 stays below 1e-5 (the op's fp32 gate) for K up to 8192,
  * same-sign data included; the FFMA kernel's stays below 1e-6.
- * FLOAT16 / BFLOAT16 / FP8 inputs: the returned size (about 10 MB for large
- * products, else 0) lets the tensor-core kernel cut the tiles of a short last
- * wave along K between two neighbouring CTA pairs instead of by columns (one
- * writes its fp32 partial tile to the workspace, the other adds it in a fixed
- * order): about 5 % faster on shapes such as 4096^3, still reproducible run to
- * run; without workspace, or with SM120_TUNE_NO_SPLIT_K, every output element
- * stays one sequential sum over K.  The workspace contents need not be
- * initialised.
- * Returns 0 when the descriptor needs no workspace.  The workspace can be reused
- * by later calls on the same stream (not by calls that may overlap on the GPU).
- * No counterpart in the reference.
+ * Returns 0 when the descriptor's types need no workspace.  The workspace can
+ * be reused by later calls on the same stream.  No counterpart in the reference.
  */
 size_t sm120_matmul_workspace_bytes(const SM120GemmDesc* desc);
 

@@ -115,3 +115,13 @@ def test_dense_layer_weights_on_cpu(pkg):
     off.build((2, 8), device="cpu")
     with pytest.raises(pkg.sm120_ops.UnimplementedError):
         off.call(torch.zeros(2, 8))
+
+
+def test_host_pipeline_chunk_schedule(ops):
+    H = ops._HostPipeline
+    for m in (512, 513, 700, 1024, 2048, 4096, 8192, 5000, 100003):
+        rows = H.chunk_rows(m)
+        assert sum(rows) == m and all(r > 0 for r in rows)
+        assert all(r % H.MIN_ROWS == 0 for r in rows[:-1])
+        assert rows[:-1] == sorted(rows[:-1], reverse=True)        # the big chunks first, a short tail
+    assert H.chunk_rows(4096) == [1536, 1024, 768, 512, 256]
