@@ -9,25 +9,27 @@
 // src/cuda_kernels/sm120_c_interface.cu:232-268).
 //
 // One CTA owns 128 query rows of one batch entry and walks over the keys in tiles
-// of 128.  64 + 128 SPLIT threads (SPLIT = threads per query row):
+// of 128.  320 threads:
 //   warp 0     TMA producer: Q once, then K tiles (three-stage ring) and V tiles (two-stage ring)
 //   warp 1     tcgen05.mma issuer and TMEM owner:
-//                S_j  = Q K_j^T   (128 x 128, both operands K-major in shared memory) -> TMEM, two buffers
-//                PV_j = P_j V_j   (128 x D; P_j is read FROM TENSOR MEMORY, where the softmax threads wrote it
-//                                  over the first 64 columns of S_j; V as stored: D contiguous) -> TMEM, two buffers
-//              issue order  ... PV_j, S_{j+2}, PV_{j+1}, S_{j+3} ...: S_{j+2} overwrites the buffer that held S_j and
-//              P_j, and the tensor pipe runs one thread's MMAs in the order they were issued, so it needs no wait.
-//   the rest   softmax: query row r (TMEM lane r) belongs to SPLIT threads, one in each of the warps
-//              w, w + 4, ... (all may read TMEM lanes 32 (w % 4) ..).  Each takes 128 / SPLIT of a tile's keys
-//              and D / SPLIT of the output row.  Per key tile: the scores are read from TMEM in one go,
-//              the partial row maxima are exchanged through shared memory (a bounded wait on the
-//              partners' sequence words), p = exp2(s - m) goes as packed bf16/fp16 pairs back into TMEM as the A
-//              operand of P_j V_j, and O = O * alpha + PV_{j-1} is accumulated in registers (the running output
-//              row lives in registers, so nothing in TMEM is ever rescaled).  At the end O / l is written.
-// While the softmax threads work on tile j the tensor pipe runs P_{j-1} V_{j-1} and Q K_{j+1}^T, and neither P nor
-// the PV accumulator is shared between consecutive tiles, so the two sides only meet through the
-// "P_j is written" and "S_j / PV_j is complete" barriers; the exponentials (one MUFU op per score) are what bounds
-// the kernel.
+//                S_j  = Q K_j^T    (128 x 128, both operands K-major in shared memory) -> TMEM buffer j % 2
+//                O_g += P_j V_j    (128 x D, g = j % 2; P_j is read FROM TENSOR MEMORY, where the softmax threads wrote it
+//                                   over the last 64 columns of S_j;  V as stored: D contiguous) -> TMEM accumulator g
+//              issue order  ... P_j V_j, S_{j+2}, P_{j+1} V_{j+1}, S_{j+3} ...: S_{j+2} overwrites the buffer that held
+//              S_j and P_j, and the tensor pipe runs one thread's MMAs in the order they were issued, so it needs no wait.
+//   warps 2-9  softmax, in two GROUPS of four warps: group g owns the key tiles j with j % 2 = g, and with them S
+//              buffer g and accumulator O_g.  Thread r of a group owns query row r (TMEM lane r) completely, so a tile
+//              needs no exchange between threads: the 128 scores are read from TMEM, p = exp2(s - m) goes back
+//              into TMEM as packed bf16/fp16 pairs (the A operand of P_j V_j), and the row sum is kept in a register.
+//              m is the group's REFERENCE maximum of the row: it only moves when a tile's maximum exceeds it by more
+//              than 8 (a factor 256 in p, harmless in 16 bits and in the fp32 sum); then the thread rescales its row
+//              of O_g in TMEM, which is safe because "S_j is complete" implies that P_{j-2} V_{j-2}, the previous
+//              product into O_g, is complete.  So O never passes through registers inside the loop.  The two groups
+//              run half a period apart: one is in its exponentials (the MUFU unit) while the other loads and reduces.
+//              At the end the groups exchange (m, l) per row through shared memory (a bounded wait on the partner's
+//              sequence word), and each writes half of the columns of  (w_0 O_0 + w_1 O_1) / (w_0 l_0 + w_1 l_1).
+// While a group works on tile j the tensor pipe runs the other group's products, and the two sides only meet through
+// the "S_j is complete" and "P_j is written" barriers; the exponentials (one MUFU op per score) bound the kernel.
 //
 // Every mbarrier wait is bounded like in the GEMM kernel (gemm_tcgen05_kernel.cuh): a wait
 // that runs out records a status code, raises the CTA's abort flag, every role leaves its
@@ -48,9 +50,8 @@ constexpr int ATT_BM = 128;          // query rows per CTA
 constexpr int ATT_BN = 128;          // keys per tile
 constexpr int ATT_K_STAGES = 3;
 constexpr int ATT_V_STAGES = 2;
-#ifndef ATT_SPLIT_128
-#define ATT_SPLIT_128 2                 // threads per query row at head dimension 128
-#endif
+constexpr int ATT_THREADS = 320;
+constexpr float ATT_RESCALE_STEP = 8.0f;   // the reference maximum follows a tile's maximum only beyond this (log2 units)
 
 // 2^x by the hardware unit (MUFU.EX2); -inf gives 0
 __device__ __forceinline__ float att_exp2(float x) {
@@ -59,11 +60,35 @@ __device__ __forceinline__ float att_exp2(float x) {
     return y;
 }
 
-// The SPLIT threads that share a query row hand each other one float per step (the partial row maximum of a key
-// tile; at the end the partial row sum).  Thread `part` publishes value and step number; it then waits, bounded like
-// every other wait of the kernel, until each partner has published the same step, and returns the maximum (MAX) or
-// the sum in part order (so every partner gets the same bits).  Values alternate between two slots, so a thread
-// that is one step ahead never overwrites what a partner still has to read.
+// The two threads that share a query row (one per group) hand each other one float per step.  Thread (g, row)
+// publishes value and step number; it then waits, bounded like every other wait of the kernel, until its partner has
+// published the same step.  Values alternate between two slots, so a thread that is one step ahead never overwrites
+// what its partner still has to read.
+__device__ __forceinline__ bool pair_exchange(volatile float* vals, volatile int* seq, int g, int row, int step, float v,
+                                              float& from_partner, const WaitCtx& w) {
+    volatile float* slot = vals + (step & 1) * (2 * ATT_BM);
+    const int mine = g * ATT_BM + row, other = (g ^ 1) * ATT_BM + row;
+    slot[mine] = v;
+    __threadfence_block();
+    seq[mine] = step;
+    if (seq[other] < step) {
+        const unsigned long long t0 = global_timer_ns();
+        uint32_t spins = 0;
+        while (seq[other] < step) {
+            if ((++spins & 63u) == 0u) {
+                if (*w.abort_flag != 0u) return false;
+                if (global_timer_ns() - t0 > w.limit_ns) {
+                    raise_abort(w, 0x65000000u);
+                    return false;
+                }
+            }
+        }
+    }
+    __threadfence_block();
+    from_partner = slot[other];
+    return true;
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 lanes x 16 K elements, two 16-bit elements per 32-bit cell)
 // comes from tensor memory
 __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -72,14 +97,17 @@ __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, ui
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-// 32 registers per thread -> 32 TMEM lanes x 32 consecutive 32-bit columns (thread i of the warp owns lane i);
-// returns when the store has completed
-__device__ __forceinline__ void tmem_st_32x32_sync(uint32_t taddr, const uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// 32 (16) registers per thread -> 32 TMEM lanes x 32 (16) consecutive 32-bit columns (thread i of the warp owns
+// lane i); complete after tmem_st_wait()
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n\t"
-        "tcgen05.wait::st.sync.aligned;"
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
         :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
            "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
            "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
@@ -87,49 +115,13 @@ __device__ __forceinline__ void tmem_st_32x32_sync(uint32_t taddr, const uint32_
         : "memory");
 }
 
-__device__ __forceinline__ void tmem_st_32x32_sync(uint32_t taddr, const uint32_t (&v)[16]) {
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n\t"
-        "tcgen05.wait::st.sync.aligned;"
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
         :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
            "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
-}
-
-template <int SPLIT, bool MAX>
-__device__ __forceinline__ bool group_exchange(volatile float* vals, volatile int* seq, int part, int row, int step, float v,
-                                               float& combined, const WaitCtx& w) {
-    volatile float* slot = vals + (step & 1) * (SPLIT * ATT_BM);
-    slot[part * ATT_BM + row] = v;
-    __threadfence_block();
-    seq[part * ATT_BM + row] = step;
-    float acc = MAX ? v : 0.0f;
-#pragma unroll
-    for (int o = 0; o < SPLIT; ++o) {
-        if (o == part) {
-            if (!MAX) acc += v;
-            continue;
-        }
-        if (seq[o * ATT_BM + row] < step) {
-            const unsigned long long t0 = global_timer_ns();
-            uint32_t spins = 0;
-            while (seq[o * ATT_BM + row] < step) {
-                if ((++spins & 63u) == 0u) {
-                    if (*w.abort_flag != 0u) return false;
-                    if (global_timer_ns() - t0 > w.limit_ns) {
-                        raise_abort(w, 0x65000000u);
-                        return false;
-                    }
-                }
-            }
-        }
-        __threadfence_block();
-        const float x = slot[o * ATT_BM + row];
-        acc = MAX ? fmaxf(acc, x) : acc + x;
-    }
-    combined = acc;
-    return true;
 }
 
 // p = exp2(s * scale_log2 - m) for this thread's KEYS keys, packed as KEYS / 2 pairs of 16-bit values (the even key in the
@@ -172,34 +164,31 @@ struct AttParams {
     unsigned int* status;
 };
 
-// SPLIT = threads per query row: each takes ATT_BN / SPLIT keys of a tile and D / SPLIT columns of the output row
-template <int D, int SPLIT>
+template <int D>
 struct AttCfg {
     static_assert(D == 64 || D == 128, "head dimension");
-    static_assert((SPLIT == 2 || SPLIT == 4) && D / SPLIT >= 32, "threads per query row");
-    static constexpr int THREADS = 64 + 128 * SPLIT;                  // TMA warp, MMA warp, 4 SPLIT softmax warps
     static constexpr uint32_t Q_BYTES = ATT_BM * D * 2;              // D/64 blocks of [128 rows x 128 B]
     static constexpr uint32_t K_BYTES = ATT_BN * D * 2;              // the same layout, ATT_BN rows
     static constexpr uint32_t V_BYTES = ATT_BN * D * 2;              // [ATT_BN/64 key blocks][D/64 boxes][64 keys x 128 B]
     static constexpr uint32_t TILE_BYTES = Q_BYTES + ATT_K_STAGES * K_BYTES + ATT_V_STAGES * V_BYTES;
-    // barriers + the row exchange: values [parity][part][row] and sequence words [part][row]
-    static constexpr uint32_t BAR_BYTES = 256 + 2 * SPLIT * ATT_BM * 4 + SPLIT * ATT_BM * 4;
+    // barriers + the row exchange: values [parity][group][row] and sequence words [group][row]
+    static constexpr uint32_t BAR_BYTES = 256 + 2 * 2 * ATT_BM * 4 + 2 * ATT_BM * 4;
     static constexpr size_t SMEM_USED = TILE_BYTES + BAR_BYTES + 1024;
     // every CTA allocates all 512 TMEM columns, so two CTAs must never share an SM: request more than half of its shared memory
     static constexpr size_t SMEM = SMEM_USED > 118784 ? SMEM_USED : 118784;
-    // S_0 at column 0, S_1 at 128 (P_j: the first 64 columns of S_j), PV_0 at 256, PV_1 at 256 + D
+    // S_0 at column 0, S_1 at 128 (P_j: the last 64 columns of S_j), O_0 at 256, O_1 at 256 + D
     static constexpr uint32_t TMEM_COLS = 512;
-    static constexpr uint32_t TMEM_PV = 2 * ATT_BN;
+    static constexpr uint32_t TMEM_O = 2 * ATT_BN;
     static_assert(SMEM <= 232448, "shared memory budget exceeded");
 };
 
-template <int D, int SPLIT>
-__global__ void __launch_bounds__(AttCfg<D, SPLIT>::THREADS, 1)
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
 sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                const __grid_constant__ CUtensorMap tmap_k,
                                const __grid_constant__ CUtensorMap tmap_v,
                                const AttParams p) {
-    using Cfg = AttCfg<D, SPLIT>;
+    using Cfg = AttCfg<D>;
     constexpr int DB = D / 64;                       // 64-element (128-byte) blocks along the head dimension
     constexpr int KB = ATT_BN / 64;                  // 64-key blocks per key tile
     extern __shared__ uint8_t smem_raw[];
@@ -214,16 +203,15 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t k_empty = smem_u32(bars + 4);     // [3]
     const uint32_t v_full = smem_u32(bars + 7);      // [2]
     const uint32_t v_empty = smem_u32(bars + 9);     // [2]
-    const uint32_t s_full = smem_u32(bars + 11);     // [2]  S_j is complete in TMEM
-    const uint32_t p_full = smem_u32(bars + 13);     // [2]  S_j has been read and P_j is in TMEM
-    const uint32_t pv_full = smem_u32(bars + 15);    // [2]  P_j V_j is complete in TMEM
-    const uint32_t pv_empty = smem_u32(bars + 17);   // [2]  P_j V_j has been read
-    const uint32_t drain_bar = smem_u32(bars + 19);
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 20);
+    const uint32_t s_full = smem_u32(bars + 11);     // [2]  S_j is complete in TMEM (and with it every product issued before)
+    const uint32_t p_full = smem_u32(bars + 13);     // [2]  S_j has been read, P_j (and a rescaled O_g) is in TMEM
+    const uint32_t o_done = smem_u32(bars + 15);     // [2]  the group's last product is complete
+    const uint32_t drain_bar = smem_u32(bars + 17);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
     volatile uint32_t* abort_flag = tmem_holder + 1;
-    volatile float* xchg = reinterpret_cast<volatile float*>(reinterpret_cast<uint8_t*>(bars) + 256);      // [2][SPLIT][ATT_BM]
-    volatile int* xseq = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 256 + 2 * SPLIT * ATT_BM * 4);   // [SPLIT][ATT_BM]
-    if (threadIdx.x < SPLIT * ATT_BM) xseq[threadIdx.x] = 0;
+    volatile float* xchg = reinterpret_cast<volatile float*>(reinterpret_cast<uint8_t*>(bars) + 256);      // [2][2][ATT_BM]
+    volatile int* xseq = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 256 + 2 * 2 * ATT_BM * 4);   // [2][ATT_BM]
+    if (threadIdx.x < 2 * ATT_BM) xseq[threadIdx.x] = 0;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -250,9 +238,8 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full + 8 * b, 1);
-            mbar_init(p_full + 8 * b, 4 * SPLIT);    // one arrival per softmax warp
-            mbar_init(pv_full + 8 * b, 1);
-            mbar_init(pv_empty + 8 * b, 4 * SPLIT);
+            mbar_init(p_full + 8 * b, 4);            // one arrival per warp of the group
+            mbar_init(o_done + 8 * b, 1);
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0u;
@@ -326,7 +313,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         const uint32_t fmt = p.out_bf16 ? 1u : 0u;
-        // M = 128; S: N = ATT_BN, both operands K-major; PV: N = D, A from TMEM, B (= V as stored) is N-major (bit 16)
+        // M = 128; S: N = ATT_BN, both operands K-major; P V: N = D, A from TMEM, B (= V as stored) is N-major (bit 16)
         const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(ATT_BN >> 3) << 17) | (static_cast<uint32_t>(ATT_BM >> 4) << 24);
         const uint32_t idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17) | (static_cast<uint32_t>(ATT_BM >> 4) << 24);
         const uint64_t desc_hi = (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -375,21 +362,18 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             w = mbar_wait(p_full + 8 * b, bph, wctx, 0x55000000u);               // P_j is in TMEM
             w = __all_sync(0xFFFFFFFFu, w);
             if (!w) { ok = false; break; }
-            w = mbar_wait(pv_empty + 8 * b, bph ^ 1u, wctx, 0x56000000u);        // P_{j-2} V_{j-2} has been read
-            w = __all_sync(0xFFFFFFFFu, w);
-            if (!w) { ok = false; break; }
             tcgen05_fence_after();
             if (elect_one_sync()) {
-                const uint32_t d_tmem = tmem_base + Cfg::TMEM_PV + b * D;
-                const uint32_t a_tmem = tmem_base + b * ATT_BN;
+                const uint32_t d_tmem = tmem_base + Cfg::TMEM_O + b * D;
+                const uint32_t a_tmem = tmem_base + b * ATT_BN + ATT_BN / 2;      // P_j: the upper 64 cells of S buffer b
 #pragma unroll
                 for (int t = 0; t < ATT_BN / 16; ++t) {
                     const uint32_t b_off = (t >> 2) * (DB * 8192) + (t & 3) * 2048;   // 16 key rows of 128 bytes per K step
                     const uint64_t b_desc = desc_hi | ((((v_smem + st * Cfg::V_BYTES + b_off) >> 4) & 0x3FFFu) | lbo_v);
-                    umma_ts_f16(d_tmem, a_tmem + t * 8, b_desc, idesc_pv, t != 0 ? 1u : 0u);   // 16 keys = 8 cells of P
+                    umma_ts_f16(d_tmem, a_tmem + t * 8, b_desc, idesc_pv, (t != 0 || j >= 2) ? 1u : 0u);   // 16 keys = 8 cells of P
                 }
-                umma_commit<1>(pv_full + 8 * b);
                 umma_commit<1>(v_empty + 8 * st);
+                if (j + 2 >= n_kv) umma_commit<1>(o_done + 8 * b);
             }
             __syncwarp();
             if (j + 2 < n_kv) ok = issue_qk(j + 2);
@@ -401,130 +385,180 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     } else {
         // ------------------------------ softmax and output ------------------------------
-        constexpr int HD = D / SPLIT;                          // output columns per thread
-        constexpr int KEYS = ATT_BN / SPLIT;                   // keys of a tile per thread
         const int lane_group = warp & 3;                       // TMEM lanes [32 * lane_group, +32)
-        const int part = (warp - 2) >> 2;                      // which keys of a tile, which columns of the output row
+        const int g = (warp - 2) >> 2;                         // group: key tiles j % 2 == g, S buffer g, accumulator O_g
         const int row = lane_group * 32 + lane;                // this thread's query row inside the tile
         const int q = q0 + row;
         const int key_limit = p.causal ? min(p.seq_k, q + p.seq_k - p.seq_q + 1) : p.seq_k;   // keys [0, key_limit) count
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.0f;
-        float m_run = -CUDART_INF_F, l_run = 0.0f, alpha_prev = 1.0f;
+        const uint32_t t_s = t_lane + g * ATT_BN;              // S_j, and P_j in its last 64 cells
+        const uint32_t t_o = t_lane + Cfg::TMEM_O + g * D;
+        const bool bf16 = p.out_bf16 != 0;
+        const float scale_log2 = p.scale_log2;
+        float m_ref = -CUDART_INF_F, l_run = 0.0f;             // reference maximum (log2 units) and row sum relative to it
         bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            const uint32_t b = j & 1, bph = (j >> 1) & 1;
-            const int key0 = j * ATT_BN + part * KEYS;
-            ok = mbar_wait(s_full + 8 * b, bph, wctx, 0x61000000u);
+        for (int j = g; j < n_kv; j += 2) {
+            const int key0 = j * ATT_BN;
+            ok = mbar_wait(s_full + 8 * g, (j >> 1) & 1, wctx, 0x61000000u);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            const uint32_t t_s = t_lane + b * ATT_BN + part * KEYS;
-            uint32_t s[KEYS];
-            __syncwarp();
-#pragma unroll
-            for (int c = 0; c < KEYS / 32; ++c) tmem_ld_32x32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-#pragma unroll
-            for (int c = 0; c < KEYS / 32; ++c) tmem_ld_wait_regs(*reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-            const bool edge = key0 + KEYS > key_limit;          // some of this thread's keys do not count for this row
+            // pass 1 over the scores, 32 at a time with the next load in flight: the tile's largest scaled score.
+            // Chunks 2 and 3 stay in registers for pass 2.
+            uint32_t ra[32], rb[32];
+            const bool edge = key0 + ATT_BN > key_limit;        // some of the tile's keys do not count for this row
             // (the per-key tests exist only in the branch for tiles that straddle this row's key limit)
-            float m_part = -CUDART_INF_F;
-            if (!edge) {
-                float ma = -CUDART_INF_F, mb = -CUDART_INF_F;       // two chains: the maxima do not depend on one another
+            auto chunk_max = [&](const uint32_t(&r)[32], int k0) -> float {
+                if (!edge) {
+                    // four chains; with a negative scale the largest scaled score belongs to the smallest raw score
+                    float e0 = __uint_as_float(r[0]), e1 = __uint_as_float(r[1]), e2 = __uint_as_float(r[2]), e3 = __uint_as_float(r[3]);
+                    if (scale_log2 >= 0.0f) {
 #pragma unroll
-                for (int i = 0; i < KEYS; i += 2) {
-                    ma = fmaxf(ma, __uint_as_float(s[i]));
-                    mb = fmaxf(mb, __uint_as_float(s[i + 1]));
+                        for (int i = 4; i < 32; i += 4) {
+                            e0 = fmaxf(e0, __uint_as_float(r[i]));
+                            e1 = fmaxf(e1, __uint_as_float(r[i + 1]));
+                            e2 = fmaxf(e2, __uint_as_float(r[i + 2]));
+                            e3 = fmaxf(e3, __uint_as_float(r[i + 3]));
+                        }
+                        return fmaxf(fmaxf(e0, e1), fmaxf(e2, e3)) * scale_log2;
+                    }
+#pragma unroll
+                    for (int i = 4; i < 32; i += 4) {
+                        e0 = fminf(e0, __uint_as_float(r[i]));
+                        e1 = fminf(e1, __uint_as_float(r[i + 1]));
+                        e2 = fminf(e2, __uint_as_float(r[i + 2]));
+                        e3 = fminf(e3, __uint_as_float(r[i + 3]));
+                    }
+                    return fminf(fminf(e0, e1), fminf(e2, e3)) * scale_log2;
                 }
-                m_part = fmaxf(ma, mb);
-            } else {
+                float m = -CUDART_INF_F;
 #pragma unroll
-                for (int i = 0; i < KEYS; ++i)
-                    if (key0 + i < key_limit) m_part = fmaxf(m_part, __uint_as_float(s[i]));
-            }
-            // the row maximum of the tile: over this thread's keys and its partners'
-            float m_tile = -CUDART_INF_F;
-            ok = group_exchange<SPLIT, true>(xchg, xseq, part, row, j + 1, m_part, m_tile, wctx);
-            ok = __all_sync(0xFFFFFFFFu, ok);
-            if (!ok) break;
-            const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
-            const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;      // a row without any key so far
-            const float alpha = att_exp2(m_run - m_use);                     // 0 for the first tile (m_run = -inf)
-            // p = exp2(s * scale_log2 - m), partial row sum, P (16-bit pairs) -> TMEM cells [part * KEYS / 2, +KEYS / 2) of
-            // the S buffer.  Those cells held scores of a partner's keys; the partner read them before it published
-            // its maximum, and the exchange above has seen that.
-            uint32_t packed[KEYS / 2];
-            const float l_tile = edge ? att_exp_pack<KEYS, true>(s, packed, p.scale_log2, m_use, key0, key_limit, p.out_bf16 != 0)
-                                      : att_exp_pack<KEYS, false>(s, packed, p.scale_log2, m_use, key0, key_limit, p.out_bf16 != 0);
-            l_run = fmaf(l_run, alpha, l_tile);
-            m_run = m_new;
+                for (int i = 0; i < 32; ++i)
+                    if (k0 + i < key_limit) m = fmaxf(m, __uint_as_float(r[i]) * scale_log2);
+                return m;
+            };
             __syncwarp();
-            tmem_st_32x32_sync(t_lane + b * ATT_BN + part * (KEYS / 2), packed);
+            tmem_ld_32x32(t_s, ra);
+            tmem_ld_wait_regs(ra);
+            tmem_ld_32x32(t_s + 32, rb);
+            float m_tile = chunk_max(ra, key0);
+            tmem_ld_wait_regs(rb);
+            tmem_ld_32x32(t_s + 64, ra);
+            m_tile = fmaxf(m_tile, chunk_max(rb, key0 + 32));
+            tmem_ld_wait_regs(ra);
+            tmem_ld_32x32(t_s + 96, rb);
+            m_tile = fmaxf(m_tile, chunk_max(ra, key0 + 64));
+            tmem_ld_wait_regs(rb);
+            m_tile = fmaxf(m_tile, chunk_max(rb, key0 + 96));
+            if (j < 2) {
+                m_ref = m_tile;                                 // the group's first tile: O_g does not exist yet
+            } else {
+                // move the reference only when the tile exceeds it by more than ATT_RESCALE_STEP.  O_g may be rewritten
+                // here: its last product (tile j - 2) was issued before S_j, which is complete.
+                const bool moves = m_tile > m_ref + ATT_RESCALE_STEP;
+                if (__any_sync(0xFFFFFFFFu, moves)) {
+                    const float alpha = moves ? att_exp2(m_ref - m_tile) : 1.0f;     // 0 when the row had no key so far
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t oc[32];
+                        tmem_ld_32x32_sync(t_o + c * 32, oc);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) oc[i] = __float_as_uint(__uint_as_float(oc[i]) * alpha);
+                        tmem_st_32x32(t_o + c * 32, oc);
+                    }
+                    l_run *= alpha;
+                    if (moves) m_ref = m_tile;
+                }
+            }
+            const float m_use = m_ref == -CUDART_INF_F ? 0.0f : m_ref;      // a row without any key so far
+            // pass 2: p = exp2(s * scale_log2 - m), row sum, P (16-bit pairs) -> cells [64, 128) of the S buffer, from the
+            // last chunk down: the cells a chunk's P lands in belong to scores that are in registers or already used,
+            // and chunks 1 and 0 are read again from cells that P never touches
+            float l_tile = 0.0f;
+            auto chunk_exp = [&](const uint32_t(&r)[32], int c) {
+                uint32_t packed[16];
+                l_tile += edge ? att_exp_pack<32, true>(r, packed, scale_log2, m_use, key0 + c * 32, key_limit, bf16)
+                               : att_exp_pack<32, false>(r, packed, scale_log2, m_use, key0 + c * 32, key_limit, bf16);
+                tmem_st_32x32(t_s + ATT_BN / 2 + c * 16, packed);
+            };
+            chunk_exp(rb, 3);
+            tmem_ld_32x32(t_s + 32, rb);
+            chunk_exp(ra, 2);
+            tmem_ld_wait_regs(rb);
+            tmem_ld_32x32(t_s, ra);
+            chunk_exp(rb, 1);
+            tmem_ld_wait_regs(ra);
+            chunk_exp(ra, 0);
+            l_run += l_tile;
+            tmem_st_wait();
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * b);
-            // O_{j-1} = O_{j-2} * alpha_{j-1} + P_{j-1} V_{j-1}: that product finished long ago
-            if (j > 0) {
-                const uint32_t pb = (j - 1) & 1;
-                ok = mbar_wait(pv_full + 8 * pb, ((j - 1) >> 1) & 1, wctx, 0x63000000u);
-                ok = __all_sync(0xFFFFFFFFu, ok);
-                if (!ok) break;
-                tcgen05_fence_after();
-#pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t pv[32];
-                    __syncwarp();
-                    tmem_ld_32x32_sync(t_lane + Cfg::TMEM_PV + pb * D + part * HD + c * 32, pv);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(pv[i]));
-                }
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(pv_empty + 8 * pb);
-            }
-            alpha_prev = alpha;
+            if (lane == 0) mbar_arrive(p_full + 8 * g);
         }
-        if (ok && n_kv > 0) {
-            const uint32_t pb = (n_kv - 1) & 1;
-            ok = mbar_wait(pv_full + 8 * pb, ((n_kv - 1) >> 1) & 1, wctx, 0x64000000u);
+        // both accumulators complete (a group without tiles has none: its weight below is 0 and its O is not read)
+        const bool has0 = n_kv > 0, has1 = n_kv > 1;
+        if (ok && has0) {
+            ok = mbar_wait(o_done, 0u, wctx, 0x64000000u);
             ok = __all_sync(0xFFFFFFFFu, ok);
-            if (ok) {
-                tcgen05_fence_after();
-#pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t pv[32];
-                    __syncwarp();
-                    tmem_ld_32x32_sync(t_lane + Cfg::TMEM_PV + pb * D + part * HD + c * 32, pv);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(pv[i]));
-                }
-                tcgen05_fence_before();
-            }
         }
-        // the row sum is the sum of the partners' partial sums (all used the same maxima)
-        float l_row = 0.0f;
-        if (ok) ok = group_exchange<SPLIT, false>(xchg, xseq, part, row, n_kv + 1, l_run, l_row, wctx);
-        if (ok && q < p.seq_q) {
+        if (ok && has1) {
+            ok = mbar_wait(o_done + 8, 0u, wctx, 0x64000000u);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+        }
+        // the row's true reference is the larger of the groups'; weights w_g = 2^(m_g - m), sum = w_0 l_0 + w_1 l_1
+        float m_other = -CUDART_INF_F, lw_other = 0.0f;
+        if (ok) ok = pair_exchange(xchg, xseq, g, row, 1, m_ref, m_other, wctx);
+        const float m_all = fmaxf(m_ref, m_other);
+        const float m_fin = m_all == -CUDART_INF_F ? 0.0f : m_all;
+        const float w_mine = att_exp2(m_ref - m_fin), w_other = att_exp2(m_other - m_fin);      // 0 for a group without keys
+        const float lw_mine = l_run * w_mine;
+        if (ok) ok = pair_exchange(xchg, xseq, g, row, 2, lw_mine, lw_other, wctx);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (ok && n_kv > 0) {
+            tcgen05_fence_after();
+            const float l_row = g == 0 ? lw_mine + lw_other : lw_other + lw_mine;     // the same bits in both threads
             const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * p.seq_q + q) * D + part * HD);
+            const float w0 = (g == 0 ? w_mine : w_other) * inv, w1 = (g == 0 ? w_other : w_mine) * inv;
+            constexpr int HD = D / 2;                           // this thread writes columns [g * HD, +HD) of its row
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * p.seq_q + q) * D + g * HD);
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
-                uint32_t w[4];
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t o0[32], o1[32];
+                __syncwarp();
+                tmem_ld_32x32_sync(t_lane + Cfg::TMEM_O + g * HD + c * 32, o0);
+                if (has1) tmem_ld_32x32_sync(t_lane + Cfg::TMEM_O + D + g * HD + c * 32, o1);
+                float r[32];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float a = o[c * 8 + 2 * k] * inv, b = o[c * 8 + 2 * k + 1] * inv;
-                    if (p.out_bf16) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                        w[k] = *reinterpret_cast<const uint32_t*>(&h);
-                    } else {
-                        const __half2 h = __floats2half2_rn(a, b);
-                        w[k] = *reinterpret_cast<const uint32_t*>(&h);
+                for (int i = 0; i < 32; ++i) {
+                    r[i] = __uint_as_float(o0[i]) * w0;
+                    if (has1) r[i] = fmaf(__uint_as_float(o1[i]), w1, r[i]);
+                }
+                if (q < p.seq_q) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float a = r[v * 8 + 2 * k], b = r[v * 8 + 2 * k + 1];
+                            if (bf16) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                                w[k] = *reinterpret_cast<const uint32_t*>(&h);
+                            } else {
+                                const __half2 h = __floats2half2_rn(a, b);
+                                w[k] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                        }
+                        dst[c * 4 + v] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
-                dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
             }
+            tcgen05_fence_before();
+        } else if (ok && q < p.seq_q) {
+            // no key tile at all: the output row is 0
+            constexpr int HD = D / 2;
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + (static_cast<size_t>(bh) * p.seq_q + q) * D + g * HD);
+#pragma unroll
+            for (int c = 0; c < HD / 8; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
         }
     }
 
@@ -538,12 +572,12 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
 }
 
-template <int D, int SPLIT>
+template <int D>
 static cudaError_t attention_launch_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttParams& p,
                                       int device, cudaStream_t stream) {
-    using Cfg = AttCfg<D, SPLIT>;
+    using Cfg = AttCfg<D>;
     static std::atomic<uint64_t> attr_done{0};
-    auto kern = sm120_attention_tcgen05_kernel<D, SPLIT>;
+    auto kern = sm120_attention_tcgen05_kernel<D>;
     const uint64_t bit = 1ull << (device & 63);
     if ((attr_done.load(std::memory_order_acquire) & bit) == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::SMEM));
@@ -551,7 +585,7 @@ static cudaError_t attention_launch_d(const CUtensorMap& tq, const CUtensorMap& 
         attr_done.fetch_or(bit, std::memory_order_release);
     }
     const dim3 grid(static_cast<unsigned>((p.seq_q + ATT_BM - 1) / ATT_BM), static_cast<unsigned>(p.batch), 1);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tq, tk, tv, p);
+    kern<<<grid, ATT_THREADS, Cfg::SMEM, stream>>>(tq, tk, tv, p);
     return cudaGetLastError();
 }
 
@@ -582,8 +616,7 @@ cudaError_t attention_fused_launch(const void* q, const void* k, const void* v, 
     p.wait_limit_ns = wait_limit_ns;
     p.status = tc_status_address(device);
     if (p.status == nullptr) return cudaErrorInvalidSymbol;
-    return head_dim == 128 ? attention_launch_d<128, ATT_SPLIT_128>(tq, tk, tv, p, device, stream)
-                           : attention_launch_d<64, 2>(tq, tk, tv, p, device, stream);
+    return head_dim == 128 ? attention_launch_d<128>(tq, tk, tv, p, device, stream) : attention_launch_d<64>(tq, tk, tv, p, device, stream);
 }
 
 }  // namespace sm120
