@@ -50,7 +50,13 @@ constexpr int ATT_BM = 128;          // query rows per CTA
 constexpr int ATT_BN = 128;          // keys per tile
 constexpr int ATT_K_STAGES = 3;
 constexpr int ATT_V_STAGES = 2;
-constexpr int ATT_THREADS = 320;
+constexpr int ATT_THREADS = 384;           // warp group 0: TMA, MMA and two idle warps; warp groups 1 and 2: softmax
+constexpr int ATT_REGS_LOW = 40;            // registers per thread of warp group 0 after the hand-over
+constexpr int ATT_REGS_HIGH = 232;          // ... of the softmax warp groups
+constexpr int ATT_REGS_LAUNCH = 168;        // what the kernel must be compiled to (65536 / 384, rounded down to 8)
+// setmaxnreg.inc waits, without a limit, for registers that warps of the SAME CTA have released: the eight softmax warps
+// may only ask for what the four warps of group 0 give back
+static_assert(8 * (ATT_REGS_HIGH - ATT_REGS_LAUNCH) <= 4 * (ATT_REGS_LAUNCH - ATT_REGS_LOW), "register hand-over does not balance");
 constexpr float ATT_RESCALE_STEP = 8.0f;   // the reference maximum follows a tile's maximum only beyond this (log2 units)
 
 // 2^x by the hardware unit (MUFU.EX2); -inf gives 0
@@ -89,12 +95,42 @@ __device__ __forceinline__ bool pair_exchange(volatile float* vals, volatile int
     return true;
 }
 
+// The bounded mbarrier wait of the GEMM kernel, fully inlined: a warp whose register count was changed by
+// setmaxnreg must not call a function that was compiled for the kernel's launch-time count.
+__device__ __forceinline__ bool att_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t code, bool watch_abort = true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0u) {
+            if (watch_abort && *w.abort_flag != 0u) return false;
+            if (global_timer_ns() - t0 > w.limit_ns) {
+                raise_abort(w, code);
+                return false;
+            }
+        }
+    }
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 lanes x 16 K elements, two 16-bit elements per 32-bit cell)
 // comes from tensor memory
 __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// 32 TMEM lanes x 16 consecutive 32-bit columns -> 16 registers per thread; the registers are valid when it returns
+__device__ __forceinline__ void tmem_ld_32x16_sync(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
 }
 
 __device__ __forceinline__ void tmem_st_wait() {
@@ -124,25 +160,46 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v
         : "memory");
 }
 
-// p = exp2(s * scale_log2 - m) for this thread's KEYS keys, packed as KEYS / 2 pairs of 16-bit values (the even key in the
-// low half: the K-major A operand of P V); returns the row-sum contribution.  EDGE: keys at or beyond key_limit count
-// as 0 (only tiles that straddle the row's limit pay for the per-key tests).  The sum adds the unrounded
-// exponentials: rounding each to 16 bits first costs two conversions per pair and changes the sum by a relative
-// 2^-9 / sqrt(keys), far inside the output's own rounding.
+// Two fp32 values in one 64-bit register pair, and the packed fp32 arithmetic of sm_100 on them: one issue slot for
+// two results
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f32x2_split(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// p = exp2(s * scale_log2 - m) for KEYS of this thread's keys, packed as KEYS / 2 pairs of 16-bit values (the even key
+// in the low half: the K-major A operand of P V); adds the exponentials to the pair of partial row sums l2.  EDGE: keys
+// at or beyond key_limit count as 0 (only tiles that straddle the row's limit pay for the per-key tests).  The sum
+// adds the unrounded exponentials: rounding each to 16 bits first costs two conversions per pair and changes the sum
+// by a relative 2^-9 / sqrt(keys), far inside the output's own rounding.
 template <int KEYS, bool EDGE>
-__device__ __forceinline__ float att_exp_pack(const uint32_t (&s)[KEYS], uint32_t (&packed)[KEYS / 2], float scale_log2, float m_use,
-                                              int key0, int key_limit, bool bf16) {
-    float l_a = 0.0f, l_b = 0.0f;
+__device__ __forceinline__ void att_exp_pack(const uint32_t (&s)[KEYS], uint32_t (&packed)[KEYS / 2], uint64_t scale2, uint64_t neg_m2,
+                                             uint64_t& l2, int key0, int key_limit, bool bf16) {
 #pragma unroll
     for (int i = 0; i < KEYS; i += 2) {
-        float p0 = att_exp2(fmaf(__uint_as_float(s[i]), scale_log2, -m_use));
-        float p1 = att_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -m_use));
+        const uint64_t x2 = fma2(f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), scale2, neg_m2);
+        float x0, x1;
+        f32x2_split(x2, x0, x1);
+        float p0 = att_exp2(x0), p1 = att_exp2(x1);
         if constexpr (EDGE) {
             if (key0 + i >= key_limit) p0 = 0.0f;
             if (key0 + i + 1 >= key_limit) p1 = 0.0f;
         }
-        l_a += p0;
-        l_b += p1;
+        l2 = add2(l2, f32x2(p0, p1));
         if (bf16) {
             const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
             packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
@@ -151,7 +208,6 @@ __device__ __forceinline__ float att_exp_pack(const uint32_t (&s)[KEYS], uint32_
             packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
         }
     }
-    return l_a + l_b;
 }
 
 struct AttParams {
@@ -204,10 +260,11 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t v_full = smem_u32(bars + 7);      // [2]
     const uint32_t v_empty = smem_u32(bars + 9);     // [2]
     const uint32_t s_full = smem_u32(bars + 11);     // [2]  S_j is complete in TMEM (and with it every product issued before)
-    const uint32_t p_full = smem_u32(bars + 13);     // [2]  S_j has been read, P_j (and a rescaled O_g) is in TMEM
+    const uint32_t p_lo = smem_u32(bars + 13);       // [2]  S_j has been read, keys 0-63 of P_j (and a rescaled O_g) are in TMEM
+    const uint32_t p_hi = smem_u32(bars + 19);       // [2]  keys 64-127 of P_j are in TMEM
     const uint32_t o_done = smem_u32(bars + 15);     // [2]  the group's last product is complete
     const uint32_t drain_bar = smem_u32(bars + 17);
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22);
     volatile uint32_t* abort_flag = tmem_holder + 1;
     volatile float* xchg = reinterpret_cast<volatile float*>(reinterpret_cast<uint8_t*>(bars) + 256);      // [2][2][ATT_BM]
     volatile int* xseq = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars) + 256 + 2 * 2 * ATT_BM * 4);   // [2][ATT_BM]
@@ -238,7 +295,8 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full + 8 * b, 1);
-            mbar_init(p_full + 8 * b, 4);            // one arrival per warp of the group
+            mbar_init(p_lo + 8 * b, 4);              // one arrival per warp of the group
+            mbar_init(p_hi + 8 * b, 4);
             mbar_init(o_done + 8 * b, 1);
         }
         mbar_init(drain_bar, 1);
@@ -258,6 +316,8 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
+    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ATT_REGS_LOW));
+
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         bool ok = n_kv > 0;
@@ -270,7 +330,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         __syncwarp();
         auto load_k = [&](int j) -> bool {
             const uint32_t st = j % ATT_K_STAGES, ph = (j / ATT_K_STAGES) & 1;
-            bool w = mbar_wait(k_empty + 8 * st, ph ^ 1u, wctx, 0x41000000u);
+            bool w = att_wait(k_empty + 8 * st, ph ^ 1u, wctx, 0x41000000u);
             w = __all_sync(0xFFFFFFFFu, w);
             if (!w) return false;
             if (elect_one_sync()) {
@@ -288,7 +348,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (ok && n_kv > 1) ok = load_k(1);
         for (int j = 0; ok && j < n_kv; ++j) {
             const uint32_t st = j % ATT_V_STAGES, ph = (j / ATT_V_STAGES) & 1;
-            bool w = mbar_wait(v_empty + 8 * st, ph ^ 1u, wctx, 0x42000000u);
+            bool w = att_wait(v_empty + 8 * st, ph ^ 1u, wctx, 0x42000000u);
             w = __all_sync(0xFFFFFFFFu, w);
             if (!w) { ok = false; break; }
             if (elect_one_sync()) {
@@ -305,11 +365,11 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (j + 2 < n_kv) ok = load_k(j + 2);
         }
         // before leaving: every copy issued must have landed (immediate unless the CTA is aborting)
-        if (n_kv > 0) mbar_wait(q_full, 0u, wctx, 0x43000000u, false);
+        if (n_kv > 0) att_wait(q_full, 0u, wctx, 0x43000000u, false);
         for (int i = max(0, issued_k - ATT_K_STAGES); i < issued_k; ++i)
-            mbar_wait(k_full + 8 * (i % ATT_K_STAGES), (i / ATT_K_STAGES) & 1, wctx, 0x43000000u, false);
+            att_wait(k_full + 8 * (i % ATT_K_STAGES), (i / ATT_K_STAGES) & 1, wctx, 0x43000000u, false);
         for (int i = max(0, issued_v - ATT_V_STAGES); i < issued_v; ++i)
-            mbar_wait(v_full + 8 * (i % ATT_V_STAGES), (i / ATT_V_STAGES) & 1, wctx, 0x43000000u, false);
+            att_wait(v_full + 8 * (i % ATT_V_STAGES), (i / ATT_V_STAGES) & 1, wctx, 0x43000000u, false);
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         const uint32_t fmt = p.out_bf16 ? 1u : 0u;
@@ -322,29 +382,29 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         bool ok = n_kv > 0;
         bool issued_any = false;
         if (ok) {
-            bool w = mbar_wait(q_full, 0u, wctx, 0x51000000u);
-            w = __all_sync(0xFFFFFFFFu, w);
-            ok = w;
+            bool w = att_wait(q_full, 0u, wctx, 0x51000000u);
+            ok = __all_sync(0xFFFFFFFFu, w);
         }
-        // S_j = Q K_j^T into S buffer j % 2.  The buffer is free: its last reader was P_{j-2} V_{j-2} (P_{j-2} lies
-        // in it), issued by this thread before this product, and the softmax threads had read S_{j-2} before they
-        // wrote P_{j-2}.
+        // S_j = Q K_j^T into S buffer j % 2.  The buffer is free: its last reader was P_{j-2} V_{j-2} (P_{j-2} lies in it),
+        // issued by this thread before this product, and the softmax threads had read S_{j-2} before they wrote
+        // P_{j-2}.
         auto issue_qk = [&](int j) -> bool {
             const uint32_t st = j % ATT_K_STAGES, ph = (j / ATT_K_STAGES) & 1;
-            bool w = mbar_wait(k_full + 8 * st, ph, wctx, 0x52000000u);
+            bool w = att_wait(k_full + 8 * st, ph, wctx, 0x52000000u);
             w = __all_sync(0xFFFFFFFFu, w);
             if (!w) return false;
             tcgen05_fence_after();
             if (elect_one_sync()) {
-                const uint32_t d_tmem = tmem_base + (j & 1) * ATT_BN;
+                const uint32_t g = j & 1;
+                const uint32_t s_tmem = tmem_base + g * ATT_BN;
 #pragma unroll
                 for (int t = 0; t < D / 16; ++t) {
                     const uint32_t off = (t >> 2) * (128 * 128) + (t & 3) * 32;       // 64-element block, then 32 bytes per K step
                     const uint64_t a_desc = desc_hi | ((((q_smem + off) >> 4) & 0x3FFFu) | lbo_k);
                     const uint64_t b_desc = desc_hi | ((((k_smem + st * Cfg::K_BYTES + off) >> 4) & 0x3FFFu) | lbo_k);
-                    umma_ss<KIND_F16, 1>(d_tmem, a_desc, b_desc, idesc_s, t != 0 ? 1u : 0u);
+                    umma_ss<KIND_F16, 1>(s_tmem, a_desc, b_desc, idesc_s, t != 0 ? 1u : 0u);
                 }
-                umma_commit<1>(s_full + 8 * (j & 1));
+                umma_commit<1>(s_full + 8 * g);
                 umma_commit<1>(k_empty + 8 * st);
             }
             __syncwarp();
@@ -354,39 +414,46 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (ok) ok = issue_qk(0);
         if (ok && n_kv > 1) ok = issue_qk(1);
         for (int j = 0; ok && j < n_kv; ++j) {
-            const uint32_t b = j & 1, bph = (j >> 1) & 1;
+            const uint32_t g = j & 1, bph = (j >> 1) & 1;
+            const uint32_t p_tmem = tmem_base + g * ATT_BN + ATT_BN / 2;      // P_j: the upper 64 cells of S buffer g
+            const uint32_t o_tmem = tmem_base + Cfg::TMEM_O + g * D;
             const uint32_t st = j % ATT_V_STAGES, ph = (j / ATT_V_STAGES) & 1;
-            bool w = mbar_wait(v_full + 8 * st, ph, wctx, 0x54000000u);
+            bool w = att_wait(v_full + 8 * st, ph, wctx, 0x54000000u);
             w = __all_sync(0xFFFFFFFFu, w);
             if (!w) { ok = false; break; }
-            w = mbar_wait(p_full + 8 * b, bph, wctx, 0x55000000u);               // P_j is in TMEM
-            w = __all_sync(0xFFFFFFFFu, w);
-            if (!w) { ok = false; break; }
-            tcgen05_fence_after();
-            if (elect_one_sync()) {
-                const uint32_t d_tmem = tmem_base + Cfg::TMEM_O + b * D;
-                const uint32_t a_tmem = tmem_base + b * ATT_BN + ATT_BN / 2;      // P_j: the upper 64 cells of S buffer b
 #pragma unroll
-                for (int t = 0; t < ATT_BN / 16; ++t) {
-                    const uint32_t b_off = (t >> 2) * (DB * 8192) + (t & 3) * 2048;   // 16 key rows of 128 bytes per K step
-                    const uint64_t b_desc = desc_hi | ((((v_smem + st * Cfg::V_BYTES + b_off) >> 4) & 0x3FFFu) | lbo_v);
-                    umma_ts_f16(d_tmem, a_tmem + t * 8, b_desc, idesc_pv, (t != 0 || j >= 2) ? 1u : 0u);   // 16 keys = 8 cells of P
+            for (int h = 0; h < 2; ++h) {
+                w = att_wait((h == 0 ? p_lo : p_hi) + 8 * g, bph, wctx, 0x55000000u);    // this half of P_j is in TMEM
+                w = __all_sync(0xFFFFFFFFu, w);
+                if (!w) break;
+                tcgen05_fence_after();
+                if (elect_one_sync()) {
+#pragma unroll
+                    for (int t = 4 * h; t < 4 * h + 4; ++t) {
+                        const uint32_t b_off = (t >> 2) * (DB * 8192) + (t & 3) * 2048;   // 16 key rows of 128 bytes per K step
+                        const uint64_t b_desc = desc_hi | ((((v_smem + st * Cfg::V_BYTES + b_off) >> 4) & 0x3FFFu) | lbo_v);
+                        umma_ts_f16(o_tmem, p_tmem + t * 8, b_desc, idesc_pv, (t != 0 || j >= 2) ? 1u : 0u);   // 16 keys = 8 cells of P
+                    }
+                    if (h == 1) {
+                        umma_commit<1>(v_empty + 8 * st);
+                        if (j + 2 >= n_kv) umma_commit<1>(o_done + 8 * g);
+                    }
                 }
-                umma_commit<1>(v_empty + 8 * st);
-                if (j + 2 >= n_kv) umma_commit<1>(o_done + 8 * b);
+                __syncwarp();
             }
-            __syncwarp();
+            if (!w) { ok = false; break; }
             if (j + 2 < n_kv) ok = issue_qk(j + 2);
         }
         if (*abort_flag != 0u && issued_any) {
             if (elect_one_sync()) umma_commit<1>(drain_bar);
             __syncwarp();
-            mbar_wait(drain_bar, 0u, wctx, 0x57000000u, false);
+            att_wait(drain_bar, 0u, wctx, 0x57000000u, false);
         }
-    } else {
+    } else if (warp >= 4) {
         // ------------------------------ softmax and output ------------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(ATT_REGS_HIGH));
         const int lane_group = warp & 3;                       // TMEM lanes [32 * lane_group, +32)
-        const int g = (warp - 2) >> 2;                         // group: key tiles j % 2 == g, S buffer g, accumulator O_g
+        const int g = (warp - 4) >> 2;                         // group: key tiles j % 2 == g, S buffer g, accumulator O_g
         const int row = lane_group * 32 + lane;                // this thread's query row inside the tile
         const int q = q0 + row;
         const int key_limit = p.causal ? min(p.seq_k, q + p.seq_k - p.seq_q + 1) : p.seq_k;   // keys [0, key_limit) count
@@ -399,57 +466,48 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         bool ok = true;
         for (int j = g; j < n_kv; j += 2) {
             const int key0 = j * ATT_BN;
-            ok = mbar_wait(s_full + 8 * g, (j >> 1) & 1, wctx, 0x61000000u);
+            ok = att_wait(s_full + 8 * g, (j >> 1) & 1, wctx, 0x61000000u);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            // pass 1 over the scores, 32 at a time with the next load in flight: the tile's largest scaled score.
-            // Chunks 2 and 3 stay in registers for pass 2.
-            uint32_t ra[32], rb[32];
+            // the row's 128 scores -> registers; the tile's largest scaled score
+            uint32_t s[ATT_BN];
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < ATT_BN / 32; ++c) tmem_ld_32x32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+#pragma unroll
+            for (int c = 0; c < ATT_BN / 32; ++c) tmem_ld_wait_regs(*reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
             const bool edge = key0 + ATT_BN > key_limit;        // some of the tile's keys do not count for this row
             // (the per-key tests exist only in the branch for tiles that straddle this row's key limit)
-            auto chunk_max = [&](const uint32_t(&r)[32], int k0) -> float {
-                if (!edge) {
-                    // four chains; with a negative scale the largest scaled score belongs to the smallest raw score
-                    float e0 = __uint_as_float(r[0]), e1 = __uint_as_float(r[1]), e2 = __uint_as_float(r[2]), e3 = __uint_as_float(r[3]);
-                    if (scale_log2 >= 0.0f) {
+            float m_tile;
+            if (!edge) {
+                // four chains; with a negative scale the largest scaled score belongs to the smallest raw score
+                float e0 = __uint_as_float(s[0]), e1 = __uint_as_float(s[1]), e2 = __uint_as_float(s[2]), e3 = __uint_as_float(s[3]);
+                if (scale_log2 >= 0.0f) {
 #pragma unroll
-                        for (int i = 4; i < 32; i += 4) {
-                            e0 = fmaxf(e0, __uint_as_float(r[i]));
-                            e1 = fmaxf(e1, __uint_as_float(r[i + 1]));
-                            e2 = fmaxf(e2, __uint_as_float(r[i + 2]));
-                            e3 = fmaxf(e3, __uint_as_float(r[i + 3]));
-                        }
-                        return fmaxf(fmaxf(e0, e1), fmaxf(e2, e3)) * scale_log2;
+                    for (int i = 4; i < ATT_BN; i += 4) {
+                        e0 = fmaxf(e0, __uint_as_float(s[i]));
+                        e1 = fmaxf(e1, __uint_as_float(s[i + 1]));
+                        e2 = fmaxf(e2, __uint_as_float(s[i + 2]));
+                        e3 = fmaxf(e3, __uint_as_float(s[i + 3]));
                     }
+                    m_tile = fmaxf(fmaxf(e0, e1), fmaxf(e2, e3)) * scale_log2;
+                } else {
 #pragma unroll
-                    for (int i = 4; i < 32; i += 4) {
-                        e0 = fminf(e0, __uint_as_float(r[i]));
-                        e1 = fminf(e1, __uint_as_float(r[i + 1]));
-                        e2 = fminf(e2, __uint_as_float(r[i + 2]));
-                        e3 = fminf(e3, __uint_as_float(r[i + 3]));
+                    for (int i = 4; i < ATT_BN; i += 4) {
+                        e0 = fminf(e0, __uint_as_float(s[i]));
+                        e1 = fminf(e1, __uint_as_float(s[i + 1]));
+                        e2 = fminf(e2, __uint_as_float(s[i + 2]));
+                        e3 = fminf(e3, __uint_as_float(s[i + 3]));
                     }
-                    return fminf(fminf(e0, e1), fminf(e2, e3)) * scale_log2;
+                    m_tile = fminf(fminf(e0, e1), fminf(e2, e3)) * scale_log2;
                 }
-                float m = -CUDART_INF_F;
+            } else {
+                m_tile = -CUDART_INF_F;
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (k0 + i < key_limit) m = fmaxf(m, __uint_as_float(r[i]) * scale_log2);
-                return m;
-            };
-            __syncwarp();
-            tmem_ld_32x32(t_s, ra);
-            tmem_ld_wait_regs(ra);
-            tmem_ld_32x32(t_s + 32, rb);
-            float m_tile = chunk_max(ra, key0);
-            tmem_ld_wait_regs(rb);
-            tmem_ld_32x32(t_s + 64, ra);
-            m_tile = fmaxf(m_tile, chunk_max(rb, key0 + 32));
-            tmem_ld_wait_regs(ra);
-            tmem_ld_32x32(t_s + 96, rb);
-            m_tile = fmaxf(m_tile, chunk_max(ra, key0 + 64));
-            tmem_ld_wait_regs(rb);
-            m_tile = fmaxf(m_tile, chunk_max(rb, key0 + 96));
+                for (int i = 0; i < ATT_BN; ++i)
+                    if (key0 + i < key_limit) m_tile = fmaxf(m_tile, __uint_as_float(s[i]) * scale_log2);
+            }
             if (j < 2) {
                 m_ref = m_tile;                                 // the group's first tile: O_g does not exist yet
             } else {
@@ -459,50 +517,48 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (__any_sync(0xFFFFFFFFu, moves)) {
                     const float alpha = moves ? att_exp2(m_ref - m_tile) : 1.0f;     // 0 when the row had no key so far
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t oc[32];
-                        tmem_ld_32x32_sync(t_o + c * 32, oc);
+                    for (int c = 0; c < D / 16; ++c) {
+                        uint32_t oc[16];
+                        tmem_ld_32x16_sync(t_o + c * 16, oc);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) oc[i] = __float_as_uint(__uint_as_float(oc[i]) * alpha);
-                        tmem_st_32x32(t_o + c * 32, oc);
+                        for (int i = 0; i < 16; ++i) oc[i] = __float_as_uint(__uint_as_float(oc[i]) * alpha);
+                        tmem_st_32x32(t_o + c * 16, oc);
                     }
                     l_run *= alpha;
                     if (moves) m_ref = m_tile;
                 }
             }
             const float m_use = m_ref == -CUDART_INF_F ? 0.0f : m_ref;      // a row without any key so far
-            // pass 2: p = exp2(s * scale_log2 - m), row sum, P (16-bit pairs) -> cells [64, 128) of the S buffer, from the
-            // last chunk down: the cells a chunk's P lands in belong to scores that are in registers or already used,
-            // and chunks 1 and 0 are read again from cells that P never touches
-            float l_tile = 0.0f;
-            auto chunk_exp = [&](const uint32_t(&r)[32], int c) {
-                uint32_t packed[16];
-                l_tile += edge ? att_exp_pack<32, true>(r, packed, scale_log2, m_use, key0 + c * 32, key_limit, bf16)
-                               : att_exp_pack<32, false>(r, packed, scale_log2, m_use, key0 + c * 32, key_limit, bf16);
-                tmem_st_32x32(t_s + ATT_BN / 2 + c * 16, packed);
-            };
-            chunk_exp(rb, 3);
-            tmem_ld_32x32(t_s + 32, rb);
-            chunk_exp(ra, 2);
-            tmem_ld_wait_regs(rb);
-            tmem_ld_32x32(t_s, ra);
-            chunk_exp(rb, 1);
-            tmem_ld_wait_regs(ra);
-            chunk_exp(ra, 0);
-            l_run += l_tile;
-            tmem_st_wait();
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * g);
+            // p = exp2(s * scale_log2 - m), row sum, P (16-bit pairs) -> cells [64, 128) of the S buffer, whose scores are
+            // in registers by now
+            const uint64_t scale2 = f32x2(scale_log2, scale_log2), neg_m2 = f32x2(-m_use, -m_use);
+            uint64_t l2 = f32x2(0.0f, 0.0f);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                // 64 keys at a time: one long run of independent exponentials, then one store; when half of P_j is
+                // written its four MMAs may start
+                uint32_t packed[32];
+                const uint32_t(&sc)[64] = *reinterpret_cast<const uint32_t(*)[64]>(&s[c * 64]);
+                if (edge) att_exp_pack<64, true>(sc, packed, scale2, neg_m2, l2, key0 + c * 64, key_limit, bf16);
+                else att_exp_pack<64, false>(sc, packed, scale2, neg_m2, l2, key0 + c * 64, key_limit, bf16);
+                tmem_st_32x32(t_s + ATT_BN / 2 + c * 32, packed);
+                tmem_st_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive((c == 0 ? p_lo : p_hi) + 8 * g);
+            }
+            float l_a, l_b;
+            f32x2_split(l2, l_a, l_b);
+            l_run += l_a + l_b;
         }
         // both accumulators complete (a group without tiles has none: its weight below is 0 and its O is not read)
         const bool has0 = n_kv > 0, has1 = n_kv > 1;
         if (ok && has0) {
-            ok = mbar_wait(o_done, 0u, wctx, 0x64000000u);
+            ok = att_wait(o_done, 0u, wctx, 0x64000000u);
             ok = __all_sync(0xFFFFFFFFu, ok);
         }
         if (ok && has1) {
-            ok = mbar_wait(o_done + 8, 0u, wctx, 0x64000000u);
+            ok = att_wait(o_done + 8, 0u, wctx, 0x64000000u);
             ok = __all_sync(0xFFFFFFFFu, ok);
         }
         // the row's true reference is the larger of the groups'; weights w_g = 2^(m_g - m), sum = w_0 l_0 + w_1 l_1
@@ -580,7 +636,12 @@ static cudaError_t attention_launch_d(const CUtensorMap& tq, const CUtensorMap& 
     auto kern = sm120_attention_tcgen05_kernel<D>;
     const uint64_t bit = 1ull << (device & 63);
     if ((attr_done.load(std::memory_order_acquire) & bit) == 0) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::SMEM));
+        // the register hand-over inside the kernel balances only if the kernel starts with ATT_REGS_LAUNCH registers
+        cudaFuncAttributes fa{};
+        cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+        if (e != cudaSuccess) return e;
+        if (fa.numRegs != ATT_REGS_LAUNCH) return cudaErrorLaunchOutOfResources;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::SMEM));
         if (e != cudaSuccess) return e;
         attr_done.fetch_or(bit, std::memory_order_release);
     }
