@@ -9,7 +9,7 @@
 // src/cuda_kernels/sm120_c_interface.cu:232-268).
 //
 // One CTA owns 128 query rows of one batch entry and walks over the keys in tiles
-// of 128.  320 threads:
+// of 128.  384 threads in three warp groups:
 //   warp 0     TMA producer: Q once, then K tiles (three-stage ring) and V tiles (two-stage ring)
 //   warp 1     tcgen05.mma issuer and TMEM owner:
 //                S_j  = Q K_j^T    (128 x 128, both operands K-major in shared memory) -> TMEM buffer j % 2
@@ -17,19 +17,27 @@
 //                                   over the last 64 columns of S_j;  V as stored: D contiguous) -> TMEM accumulator g
 //              issue order  ... P_j V_j, S_{j+2}, P_{j+1} V_{j+1}, S_{j+3} ...: S_{j+2} overwrites the buffer that held
 //              S_j and P_j, and the tensor pipe runs one thread's MMAs in the order they were issued, so it needs no wait.
-//   warps 2-9  softmax, in two GROUPS of four warps: group g owns the key tiles j with j % 2 = g, and with them S
+//              P_j arrives in two halves of 64 keys with a barrier each, so the first four MMAs of P_j V_j start
+//              while the second half is still being computed.
+//   warps 2-3  idle (they complete warp group 0, which hands most of its registers to the other two groups)
+//   warps 4-11 softmax, two GROUPS of four warps: group g owns the key tiles j with j % 2 = g, and with them S
 //              buffer g and accumulator O_g.  Thread r of a group owns query row r (TMEM lane r) completely, so a tile
-//              needs no exchange between threads: the 128 scores are read from TMEM, p = exp2(s - m) goes back
-//              into TMEM as packed bf16/fp16 pairs (the A operand of P_j V_j), and the row sum is kept in a register.
+//              needs no exchange between threads: the 128 scores are read from TMEM into registers (232 per thread
+//              after setmaxnreg), p = exp2(s - m) goes back into TMEM as packed bf16/fp16 pairs (the A operand of
+//              P_j V_j), and the row sum is kept in a register.  The exponentials run in two straight runs of 64:
+//              every asm volatile in between (a TMEM store, a fence) is a point the compiler cannot schedule across,
+//              and each costs a drain of the MUFU pipeline.
 //              m is the group's REFERENCE maximum of the row: it only moves when a tile's maximum exceeds it by more
 //              than 8 (a factor 256 in p, harmless in 16 bits and in the fp32 sum); then the thread rescales its row
 //              of O_g in TMEM, which is safe because "S_j is complete" implies that P_{j-2} V_{j-2}, the previous
 //              product into O_g, is complete.  So O never passes through registers inside the loop.  The two groups
-//              run half a period apart: one is in its exponentials (the MUFU unit) while the other loads and reduces.
-//              At the end the groups exchange (m, l) per row through shared memory (a bounded wait on the partner's
-//              sequence word), and each writes half of the columns of  (w_0 O_0 + w_1 O_1) / (w_0 l_0 + w_1 l_1).
-// While a group works on tile j the tensor pipe runs the other group's products, and the two sides only meet through
-// the "S_j is complete" and "P_j is written" barriers; the exponentials (one MUFU op per score) bound the kernel.
+//              run half a period apart: one is in its exponentials (the MUFU unit) while the tensor pipe serves the
+//              other.  At the end the groups exchange (m, l) per row through shared memory (a bounded wait on the
+//              partner's sequence word), and each writes half of the columns of
+//              (w_0 O_0 + w_1 O_1) / (w_0 l_0 + w_1 l_1).
+// A group's period is its softmax time plus P_j V_j plus Q K_{j+2}^T (the next scores need the buffer that P_j lies
+// in); TMEM (two score buffers + two accumulators = 512 columns at D = 128) has no room for a third score buffer
+// that would take the products off that path.
 //
 // Every mbarrier wait is bounded like in the GEMM kernel (gemm_tcgen05_kernel.cuh): a wait
 // that runs out records a status code, raises the CTA's abort flag, every role leaves its
