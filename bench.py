@@ -70,10 +70,12 @@ OUT_BYTES = {"f32": 4, "f16": 2, "bf16": 2, "f8e4m3": 2}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from the ncu
 # captures summarised under profiles/ (the file named beside each figure); None = not captured.
 NCU_TRAFFIC_BYTES = {
-    "f16_4096_tn": 93319680,        # profiles/gemm_tcgen05_cfg2_fp16_4096.txt: 74.60 MB read + 18.72 MB written
-    "bf16_4096_tn": 93319680,       # same kernel, shape and byte counts
-    "bf16_dense_gelu": 529810176,   # profiles/gemm_tcgen05_cfg3_bf16_dense_gelu.txt: 366.6 MB read + 163.2 MB written
-    "bf16_batched_qk": 546989312,   # profiles/gemm_tcgen05_cfg4_bf16_batched.txt: 67.2 MB read + 479.8 MB written
+    "f16_4096_tn": 91455744,        # profiles/gemm_tcgen05_f16_4096x4096x4096.txt: 74.30 MB read + 17.16 MB written
+    "bf16_4096_tn": 91455744,       # same kernel, shape and byte counts
+    "bf16_dense_gelu": 517800000,   # profiles/gemm_tcgen05_bf16_dense_gelu_8192x11008x4096.txt: 351.7 MB read + 166.1 MB written
+    "bf16_batched_qk": 547412224,   # profiles/gemm_tcgen05_bf16_batched_qk_96x1024x1024x128.txt: 67.2 MB read + 480.2 MB written
+    "fp8_8192": 402100000,          # profiles/gemm_tcgen05_fp8_8192x8192x8192.txt: 284.4 MB read + 117.7 MB written
+    "attention_64x2048x128": 115696896,   # profiles/attention_tcgen05_64x2048x128_bf16.txt: 100.8 MB read + 14.9 MB written
 }
 
 
@@ -646,7 +648,7 @@ def run_attention(args, torch, pkg, device, peaks, peak_kind):
             "data": "synthetic",
             "config": {"workload": args.workload, "batch_x_heads": bh, "seq": s, "head_dim": d,
                        "what": "softmax(Q K^T / sqrt(d)) V in one kernel", "l2": "three sets of Q, K, V rotate"},
-            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "kernel": kernel, "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": 4 * bh * s * d * 2,
                          "peak_source": f"{peak_kind}: bf16_tflops (cuBLAS bf16 8192^3 burst)"},
             "pct_of_nominal_dense_peak": 100.0 * tf / NOMINAL_PEAK["bf16"],
