@@ -53,7 +53,7 @@ ACT_CODES = {
 }
 E4M3_MAX = 448.0
 
-# BASELINE tolerances (relative Frobenius error against this oracle)
+# parity tolerances per input type (relative Frobenius error against this oracle)
 TOLERANCE = {"float32": 1e-5, "float16": 1e-2, "bfloat16": 1e-2, "fp8_e4m3": 5e-2}
 
 
@@ -68,7 +68,7 @@ def quantize(x: np.ndarray, dtype: str) -> np.ndarray:
 
 
 def fp8_scale(x: np.ndarray) -> float:
-    """Per-tensor scale that maps amax(x) to 448 (BASELINE config 5)."""
+    """Per-tensor scale that maps amax(x) to 448 (the FP8 workload)."""
     amax = float(np.max(np.abs(x)))
     return E4M3_MAX / amax if amax > 0 else 1.0
 
@@ -168,7 +168,7 @@ def attention_oracle(q, k, v, scale=None, mask=None, causal=False, return_weight
 
 
 def rel_frobenius(x, ref) -> float:
-    """||x - ref||_F / ||ref||_F in float64 (BASELINE's parity metric)."""
+    """||x - ref||_F / ||ref||_F in float64 (the parity metric)."""
     x = np.asarray(x).astype(np.float64)
     ref = np.asarray(ref).astype(np.float64)
     den = float(np.linalg.norm(ref.ravel()))
@@ -187,7 +187,7 @@ def max_abs_tolerance_ok(x, ref, rtol=1e-3, atol=1e-3) -> bool:
 
 
 # ---------------------------------------------------------------------------
-# Seeded inputs for the five BASELINE configurations.  `shrink` divides the
+# Seeded inputs for the five benchmark configurations.  `shrink` divides the
 # large extents so the same distributions can be checked at oracle-friendly size.
 # ---------------------------------------------------------------------------
 CONFIG_NAMES = {
@@ -223,7 +223,7 @@ def config_flops(idx: int, shrink: int = 1) -> float:
 
 def make_config(idx: int, shrink: int = 1) -> dict:
     """Inputs (already quantised to the config's input dtype), descriptor fields
-    and oracle keyword arguments for BASELINE config `idx` (1..5), drawn from
+    and oracle keyword arguments for benchmark configuration `idx` (1..5), drawn from
     numpy.random.default_rng(idx - 1)."""
     sh = config_shapes(idx, shrink)
     M, N, K, batch = sh["M"], sh["N"], sh["K"], sh["batch"]

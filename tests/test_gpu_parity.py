@@ -250,7 +250,7 @@ def test_fp8_scaled(ops, binding):
     assert binding.last_kernel_name().startswith("tc_e4m3")
     assert got.dtype == ref.NP_DTYPES["bfloat16"]
     assert ref.rel_frobenius(got, want_deq) <= 1e-2          # kernel error alone
-    assert ref.rel_frobenius(got, want_true) <= TOL["fp8_e4m3"]   # BASELINE gate: vs the unquantised product
+    assert ref.rel_frobenius(got, want_true) <= TOL["fp8_e4m3"]   # the FP8 gate: against the unquantised product
     # scales supplied as device scalars give the same bits
     r2 = ops.fused_matmul(U.to_cuda(a), U.to_cuda(b), transpose_b=True,
                           scale_a=torch.tensor([sa], device="cuda"), scale_b=torch.tensor([sb], device="cuda"))
@@ -405,7 +405,7 @@ def test_baseline_config5_slab(ops, binding):
     rows = torch.randint(0, 8192, (32,), device="cuda")
     inv = 1.0 / (float(sa) * float(sb))
     assert _sampled_rows_check(ops, qa, qb, c, rows, tb=True, inv_scale=inv, tol=1e-2)
-    # BASELINE gate against the unquantised product on the sampled rows
+    # the FP8 gate against the unquantised product on the sampled rows
     exact = a32[rows].double() @ b32.double().T
     assert ref.rel_frobenius(U.to_numpy(c[rows]), exact.cpu().numpy()) <= TOL["fp8_e4m3"]
 

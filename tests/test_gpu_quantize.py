@@ -34,7 +34,7 @@ def test_quantizer_matches_oracle(ops, dtype, n):
         assert np.array_equal(got_q.view(np.uint8), want_q.view(np.uint8))
     else:
         assert np.mean(got_q.view(np.uint8) == want_q.view(np.uint8)) > 0.999
-    assert float(np.max(np.abs(got_q.astype(np.float32)))) == 448.0      # amax maps to 448 (BASELINE config 5)
+    assert float(np.max(np.abs(got_q.astype(np.float32)))) == 448.0      # amax maps to 448 (the FP8 workload)
 
 
 def test_quantizer_edge_cases(ops, binding):
@@ -76,7 +76,7 @@ def test_quantizer_edge_cases(ops, binding):
 
 
 def test_quantizer_full_size_slab(ops):
-    # one rank's A slab of BASELINE config 5: 8192 x 8192 fp32 -> e4m3; idempotence and round trip as size-independent checks
+    # one rank's A slab of the M-sharded FP8 workload: 8192 x 8192 fp32 -> e4m3; idempotence and round trip as size-independent checks
     torch.manual_seed(0)
     x = torch.randn(8192, 8192, device="cuda")
     q, s = ops.quantize_fp8(x)

@@ -113,7 +113,7 @@ def test_baseline_config_generators():
         assert c.shape == lead + (cfg["M"], cfg["N"])
         assert c.dtype == ref.NP_DTYPES[cfg["out_dtype"]]
         assert np.isfinite(c.astype(np.float32)).all()
-    # full-size shapes and FLOP counts of the five BASELINE configurations
+    # full-size shapes and FLOP counts of the five benchmark configurations
     assert ref.config_flops(2) == 2 * 4096 ** 3
     assert ref.config_shapes(3) == dict(M=8192, N=11008, K=4096, batch=1)
     assert ref.config_shapes(4) == dict(M=2048, N=2048, K=128, batch=64)
