@@ -105,6 +105,35 @@ def test_fused_attention_matches_oracle(ops, binding, dtype, d):
     assert binding.load_library().sm120_get_kernel_status(0, ctypes.byref(st), 0) == 0 and st.value == 0
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("d", [64, 128])
+def test_fused_attention_growing_scores_and_scale_signs(ops, binding, dtype, d):
+    """Keys whose scores grow from tile to tile move the kernel's reference maximum again and again (it rescales
+    its accumulator in tensor memory, one group of key tiles independently of the other, and merges the two at the
+    end); a negative scale turns the maximum search into a minimum search; scale 0 is the plain mean of V."""
+    rng = np.random.default_rng(40 + d)
+    lead, sq, sk = (2,), 200, 1100                      # nine key tiles, the last one ragged
+    q, k, v = _qkv(rng, lead, sq, sk, d, dtype)
+    grow = (1.0 + 0.75 * (np.arange(sk) // 128)).astype(np.float32)[:, None]     # tile t: scores x (1 + 0.75 t)
+    k = ref.quantize(k.astype(np.float32) * grow, dtype)
+    for scale, causal in ((1.0, False), (1.0, True), (-1.0, False), (-0.7, True), (0.0, False)):
+        cq = q if not causal else ref.quantize(np.concatenate([q] * 6, axis=-2)[..., :sk, :], dtype)
+        got = ops.scaled_dot_product_attention(U.to_cuda(cq), U.to_cuda(k), U.to_cuda(v), scale=scale, causal_mask=causal)
+        torch.cuda.synchronize()
+        assert binding.last_kernel_name() == f"attention_tcgen05_d{d}"
+        want = ref.attention_oracle(cq, k, v, scale=scale, causal=causal)
+        g = U.to_numpy(got)
+        assert np.isfinite(g.astype(np.float32)).all()
+        err = ref.rel_frobenius(g, want)
+        assert err <= ref.TOLERANCE[dtype], (scale, causal, err)
+    # scores that SHRINK from tile to tile: the reference maximum of the first tiles stays, nothing is rescaled
+    k2 = ref.quantize(k.astype(np.float32)[..., ::-1, :].copy(), dtype)
+    got = ops.scaled_dot_product_attention(U.to_cuda(q), U.to_cuda(k2), U.to_cuda(v), scale=1.0)
+    assert ref.rel_frobenius(U.to_numpy(got), ref.attention_oracle(q, k2, v, scale=1.0)) <= ref.TOLERANCE[dtype]
+    st = ctypes.c_uint(1)
+    assert binding.load_library().sm120_get_kernel_status(0, ctypes.byref(st), 0) == 0 and st.value == 0
+
+
 def test_attention_reference_signature_and_weights(binding):
     # sm120_launch_attention(queries, keys, values, output, attention_weights, batch, seq_len, head_dim, scale, dtype, stream)
     lib = binding.load_library()
