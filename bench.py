@@ -564,7 +564,7 @@ def run_aux(args, torch, pkg, device, peaks, peak_kind):
     if args.workload == "quant_fp8_64m":
         xs = [torch.randn(n, device=device).bfloat16() for _ in range(3)]
         nbytes = n * (2 + 2 + 1)          # x read twice (amax, cast), q written once
-        what = "amax + scale + cast of 64 Mi bf16 elements to e4m3 (three launches)"
+        what = "amax + scale + cast of 64 Mi bf16 elements to e4m3 (two launches)"
 
         def step(i):
             ops.quantize_fp8(xs[i % 3])

@@ -375,7 +375,7 @@ cudaError_t sm120_launch_quantize_fp8(const void* x, SM120DataType x_dtype, int6
     if (e != cudaSuccess) return e;
     e = quant_launch(x, x_dtype, q, scale_out, n, static_cast<float*>(scratch), stream);
     if (e == cudaSuccess) {
-        g_launch_count.fetch_add(3, std::memory_order_relaxed);
+        g_launch_count.fetch_add(2, std::memory_order_relaxed);
         t_last_kernel = "quant_e4m3_amax_scale_cast";
     }
     return e;
@@ -400,7 +400,7 @@ cudaError_t sm120_launch_quantize_fp8_static(const void* x, SM120DataType x_dtyp
     if (e != cudaSuccess) return e;
     e = quant_launch_static(x, x_dtype, q, scale_out, n, device, stream);
     if (e == cudaSuccess) {
-        g_launch_count.fetch_add(3, std::memory_order_relaxed);
+        g_launch_count.fetch_add(2, std::memory_order_relaxed);
         t_last_kernel = "quant_e4m3_amax_scale_cast_static";
     }
     return e;

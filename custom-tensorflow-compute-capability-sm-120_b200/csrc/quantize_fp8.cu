@@ -11,11 +11,12 @@
 // operands; the matmul consumes `scale` through SM120GemmDesc::scale_a_dev /
 // scale_b_dev, so no host round trip is needed between the two.
 //
-// Three launches on the caller's stream, all HBM-bound (x is read twice, q
+// Two launches on the caller's stream, both HBM-bound (x is read twice, q
 // written once):
 //   1. amax_partial : one block per span of 65536 elements -> partial[b] = max|x| of the span
-//   2. amax_final   : one block reduces the partials -> *scale_out
-//   3. scale_cast   : q = sat(x * *scale_out), 16-byte loads where alignment allows
+//   2. scale_cast   : every block reduces the partials to the same maximum (block 0 writes *scale_out),
+//                     then q = sat(x * scale), 16-byte loads where alignment allows, the spans in
+//                     reverse order so that what the first pass read last is still in the L2
 // `partial` is scratch memory: one float per span.  Every slot that a call reads
 // is written by that call's first launch, so nothing has to be zero beforehand.
 
@@ -66,7 +67,19 @@ sm120_quant_amax_partial_kernel(const T* __restrict__ x, long long n, float* __r
     if (vec_ok) {
         const long long nvec = (end - begin) / VEC;
         const uint4* xv = reinterpret_cast<const uint4*>(x + begin);
-        for (long long i = threadIdx.x; i < nvec; i += QUANT_THREADS) {
+        long long i = threadIdx.x;
+        for (; i + 3 * QUANT_THREADS < nvec; i += 4 * QUANT_THREADS) {          // four loads in flight per thread
+            uint4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = __ldg(xv + i + u * QUANT_THREADS);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const T* e = reinterpret_cast<const T*>(&w[u]);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) m = fmaxf(m, fabsf(q_to_float<T>(e[k])));
+            }
+        }
+        for (; i < nvec; i += QUANT_THREADS) {
             const uint4 w = __ldg(xv + i);
             const T* e = reinterpret_cast<const T*>(&w);
 #pragma unroll
@@ -80,32 +93,37 @@ sm120_quant_amax_partial_kernel(const T* __restrict__ x, long long n, float* __r
     if (threadIdx.x == 0) partial[blockIdx.x] = m;
 }
 
-__global__ void __launch_bounds__(1024)
-sm120_quant_amax_final_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ scale_out) {
-    __shared__ float red[32];
-    float m = 0.0f;
-    for (int i = threadIdx.x; i < nparts; i += blockDim.x) m = fmaxf(m, partial[i]);
-    m = block_max(m, red);
-    if (threadIdx.x == 0) *scale_out = m > 0.0f ? 448.0f / fminf(m, 3.402823466e38f) : 1.0f;
-}
-
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
     return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
-template <typename T>
+// q = sat_e4m3(x * scale).  FROM_PARTIALS: the scale is not given but derived here, by every CTA alike, from the
+// partial maxima of the first kernel (the same reduction in the same order in every CTA, so all use the same bits;
+// CTA 0 also writes it to `scale`); that saves a one-CTA kernel between the two passes over x.  The spans are walked
+// from the last to the first: the first pass read x front to back, so its tail is what the L2 still holds.
+template <typename T, bool FROM_PARTIALS>
 __global__ void __launch_bounds__(QUANT_THREADS)
-sm120_quant_scale_cast_kernel(const T* __restrict__ x, long long n, const float* __restrict__ scale, uint8_t* __restrict__ q) {
+sm120_quant_scale_cast_kernel(const T* __restrict__ x, long long n, float* __restrict__ scale, uint8_t* __restrict__ q,
+                              const float* __restrict__ partial, int nparts) {
     constexpr int VEC = 16 / sizeof(T);          // elements per 16-byte load
-    const float s = __ldg(scale);
-    const long long begin = static_cast<long long>(blockIdx.x) * QUANT_SPAN;
+    float s;
+    if constexpr (FROM_PARTIALS) {
+        __shared__ float red[32];
+        float m = 0.0f;
+        for (int i = threadIdx.x; i < nparts; i += QUANT_THREADS) m = fmaxf(m, partial[i]);
+        m = block_max(m, red);
+        s = m > 0.0f ? 448.0f / fminf(m, 3.402823466e38f) : 1.0f;
+        if (blockIdx.x == 0 && threadIdx.x == 0) *scale = s;
+    } else {
+        s = __ldg(scale);
+    }
+    const long long begin = static_cast<long long>(gridDim.x - 1 - blockIdx.x) * QUANT_SPAN;
     const long long end = min(n, begin + QUANT_SPAN);
     const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q) & 15u) == 0;
     if (vec_ok) {
         const long long nvec = (end - begin) / VEC;
         const uint4* xv = reinterpret_cast<const uint4*>(x + begin);
-        for (long long i = threadIdx.x; i < nvec; i += QUANT_THREADS) {
-            const uint4 w = __ldg(xv + i);
+        const auto cast_store = [&](const uint4& w, long long i) {
             const T* e = reinterpret_cast<const T*>(&w);
             uint8_t out[VEC];
 #pragma unroll
@@ -113,7 +131,16 @@ sm120_quant_scale_cast_kernel(const T* __restrict__ x, long long n, const float*
             uint8_t* dst = q + begin + i * VEC;
             if constexpr (VEC == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(out);
             else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(out);
+        };
+        long long i = threadIdx.x;
+        for (; i + 3 * QUANT_THREADS < nvec; i += 4 * QUANT_THREADS) {          // four loads in flight per thread
+            uint4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = __ldcs(xv + i + u * QUANT_THREADS);          // last use of x
+#pragma unroll
+            for (int u = 0; u < 4; ++u) cast_store(w[u], i + u * QUANT_THREADS);
         }
+        for (; i < nvec; i += QUANT_THREADS) cast_store(__ldcs(xv + i), i);
         for (long long i = begin + nvec * VEC + threadIdx.x; i < end; i += QUANT_THREADS) q[i] = to_e4m3(q_to_float<T>(x[i]) * s);
     } else {
         for (long long i = begin + threadIdx.x; i < end; i += QUANT_THREADS) q[i] = to_e4m3(q_to_float<T>(x[i]) * s);
@@ -127,12 +154,12 @@ static cudaError_t quant_typed(const void* x, long long n, uint8_t* q, float* sc
     const long long spans = quant_spans(n);
     const T* xt = static_cast<const T*>(x);
     sm120_quant_amax_partial_kernel<T><<<static_cast<unsigned>(spans), QUANT_THREADS, 0, stream>>>(xt, n, partial);
-    sm120_quant_amax_final_kernel<<<1, 1024, 0, stream>>>(partial, static_cast<int>(spans), scale_out);
-    sm120_quant_scale_cast_kernel<T><<<static_cast<unsigned>(spans), QUANT_THREADS, 0, stream>>>(xt, n, scale_out, q);
+    sm120_quant_scale_cast_kernel<T, true><<<static_cast<unsigned>(spans), QUANT_THREADS, 0, stream>>>(xt, n, scale_out, q, partial,
+                                                                                                       static_cast<int>(spans));
     return cudaGetLastError();
 }
 
-// Enqueue the three kernels.  `partial` must hold quant_spans(n) floats.
+// Enqueue the two kernels (partial maxima; final maximum + scale + cast).  `partial` must hold quant_spans(n) floats.
 cudaError_t quant_launch(const void* x, int x_dtype, void* q, float* scale_out, long long n, float* partial, cudaStream_t stream) {
     if (quant_spans(n) > 0x7FFFFFFFll) return cudaErrorInvalidValue;
     switch (x_dtype) {
@@ -152,13 +179,13 @@ cudaError_t quant_cast_launch(const void* x, int x_dtype, void* q, const float* 
     const unsigned grid = static_cast<unsigned>(spans);
     switch (x_dtype) {
         case SM120_DTYPE_FLOAT32:
-            sm120_quant_scale_cast_kernel<float><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float*>(x), n, scale, qq);
+            sm120_quant_scale_cast_kernel<float, false><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float*>(x), n, const_cast<float*>(scale), qq, nullptr, 0);
             break;
         case SM120_DTYPE_FLOAT16:
-            sm120_quant_scale_cast_kernel<__half><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __half*>(x), n, scale, qq);
+            sm120_quant_scale_cast_kernel<__half, false><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __half*>(x), n, const_cast<float*>(scale), qq, nullptr, 0);
             break;
         case SM120_DTYPE_BFLOAT16:
-            sm120_quant_scale_cast_kernel<__nv_bfloat16><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), n, scale, qq);
+            sm120_quant_scale_cast_kernel<__nv_bfloat16, false><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), n, const_cast<float*>(scale), qq, nullptr, 0);
             break;
         default: return cudaErrorInvalidValue;
     }
