@@ -46,6 +46,43 @@ template <> __device__ __forceinline__ __nv_bfloat16 ew_from_float<__nv_bfloat16
 // instruction rate instead of HBM.  fp32 tensors keep the accurate functions.
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
+// Two fp32 values in one 64-bit register pair and sm_100's packed fp32 arithmetic on them (one issue slot for two
+// results): the sigmoid-based 16-bit activations are bound by the instruction rate, not by HBM, without it.
+__device__ __forceinline__ uint64_t ew_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void ew_split2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ew_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t ew_mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t ew_add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// 1 / (1 + 2^z) for a pair: sigmoid(t) with z = -t log2(e).  2^z = inf gives 0, 2^z = 0 gives 1.
+__device__ __forceinline__ uint64_t ew_sigmoid_exp2_2(uint64_t z2) {
+    float z0, z1, e0, e1, r0, r1, d0, d1;
+    ew_split2(z2, z0, z1);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(z0));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(z1));
+    ew_split2(ew_add2(ew_pack2(e0, e1), ew_pack2(1.0f, 1.0f)), d0, d1);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(d0));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(d1));
+    return ew_pack2(r0, r1);
+}
+
 template <int VEC, bool FAST16>
 __device__ __forceinline__ void activate_vec(float (&x)[VEC], int act) {
     if constexpr (!FAST16) {
@@ -76,17 +113,39 @@ __device__ __forceinline__ void activate_vec(float (&x)[VEC], int act) {
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) x[k] = x[k] > 0.0f ? 1.0507f * x[k] : 1.0507f * 1.67326f * (__expf(x[k]) - 1.0f);
                 break;
-            case SM120_ACTIVATION_GELU:        // 0.5 x (1 + tanh(u)) = x sigmoid(2u)
+            case SM120_ACTIVATION_GELU: {      // 0.5 x (1 + tanh(u)) = x sigmoid(2u), u = 0.79788 (x + 0.044715 x^3)
+                if constexpr (VEC % 2 == 0) {
+                    const uint64_t c3 = ew_pack2(0.044715f, 0.044715f), one = ew_pack2(1.0f, 1.0f);
+                    const uint64_t cz = ew_pack2(-2.0f * 0.7978845608f * 1.4426950409f, -2.0f * 0.7978845608f * 1.4426950409f);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) {
-                    const float u = 0.7978845608f * (x[k] + 0.044715f * x[k] * x[k] * x[k]);
-                    x[k] = x[k] * fast_sigmoid(2.0f * u);
+                    for (int k = 0; k < VEC; k += 2) {
+                        const uint64_t x2 = ew_pack2(x[k], x[k + 1]);
+                        const uint64_t t = ew_mul2(ew_fma2(ew_mul2(x2, x2), c3, one), x2);         // x + 0.044715 x^3
+                        ew_split2(ew_mul2(x2, ew_sigmoid_exp2_2(ew_mul2(t, cz))), x[k], x[k + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) {
+                        const float u = 0.7978845608f * (x[k] + 0.044715f * x[k] * x[k] * x[k]);
+                        x[k] = x[k] * fast_sigmoid(2.0f * u);
+                    }
                 }
                 break;
-            case SM120_ACTIVATION_SWISH:
+            }
+            case SM120_ACTIVATION_SWISH: {
+                if constexpr (VEC % 2 == 0) {
+                    const uint64_t cz = ew_pack2(-1.4426950409f, -1.4426950409f);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) x[k] = x[k] * fast_sigmoid(x[k]);
+                    for (int k = 0; k < VEC; k += 2) {
+                        const uint64_t x2 = ew_pack2(x[k], x[k + 1]);
+                        ew_split2(ew_mul2(x2, ew_sigmoid_exp2_2(ew_mul2(x2, cz))), x[k], x[k + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) x[k] = x[k] * fast_sigmoid(x[k]);
+                }
                 break;
+            }
             case SM120_ACTIVATION_MISH:        // tanh(log(1 + e^x)) = n / (n + 2) with n = e^x (e^x + 2)
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
