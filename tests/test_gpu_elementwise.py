@@ -107,7 +107,8 @@ def test_dense_unfused_equals_fused(ops):
 @pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
 def test_bias_grad(ops, binding, dtype):
     rng = np.random.default_rng(8)
-    for (M, N) in ((1, 1), (5, 7), (300, 264), (4096, 1000), (1000, 64), (8192, 1032)):
+    # the last two shapes have enough columns for the 256- and the 512-byte strip rows (ragged last strip)
+    for (M, N) in ((1, 1), (5, 7), (300, 264), (4096, 1000), (1000, 64), (8192, 1032), (1024, 4100), (2048, 8200)):
         g = ref.quantize(rng.standard_normal((M, N), dtype=np.float32), dtype)
         tg = U.to_cuda(g)
         got32 = ops.bias_grad(tg, out_dtype=torch.float32)
