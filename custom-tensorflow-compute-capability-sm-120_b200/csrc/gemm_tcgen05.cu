@@ -26,7 +26,7 @@ __device__ unsigned long long g_sm120_probe[2];
                                                                      const TcParams&, int, int, cudaStream_t, bool);
 SM120_TC_EXTERN(KIND_F16, 256, 6, 2) SM120_TC_EXTERN(KIND_F16, 256, 4, 1) SM120_TC_EXTERN(KIND_F16, 128, 6, 1) SM120_TC_EXTERN(KIND_F16, 64, 8, 1)
 SM120_TC_EXTERN(KIND_F8, 256, 6, 2) SM120_TC_EXTERN(KIND_F8, 256, 4, 1) SM120_TC_EXTERN(KIND_F8, 128, 6, 1) SM120_TC_EXTERN(KIND_F8, 64, 8, 1)
-SM120_TC_EXTERN(KIND_TF32, 128, 8, 2) SM120_TC_EXTERN(KIND_TF32, 128, 6, 1) SM120_TC_EXTERN(KIND_TF32, 64, 8, 1)
+SM120_TC_EXTERN(KIND_TF32, 128, 4, 2) SM120_TC_EXTERN(KIND_TF32, 128, 3, 1) SM120_TC_EXTERN(KIND_TF32, 64, 4, 1)
 #undef SM120_TC_EXTERN
 // the pair tile with 16 epilogue warps, for short-K (store-bound) problems
 extern template cudaError_t launch_variant<KIND_F16, 256, 5, 2, 16>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
@@ -218,10 +218,12 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.batch = static_cast<int>(p.batch);
     tp.tiles_m = static_cast<int>((p.M + BM * cg - 1) / (BM * cg));
     tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
-    tp.k_blocks = static_cast<int>((p.K + bk - 1) / bk);
-    // fp32 path: the tensor cores' fp32 accumulation truncates, so a sum is carried in TMEM for 8 k-blocks
-    // (256 tf32 products) only and the runs are added in registers with round-to-nearest (see epilogue_role)
-    tp.kb_per_run = fp32 ? 8 : tp.k_blocks;
+    // fp32 path: the operands' rows are [hi | lo] (K = 2 x the padded K of the product) and a k-block of 32 feeds
+    // three products.  The tensor cores' fp32 accumulation truncates, so a sum is carried in TMEM for 3 k-blocks
+    // (36 MMAs of 8 tf32 products) only and the runs are added in registers with round-to-nearest (see epilogue_role)
+    tp.k_lo = fp32 ? static_cast<int>(p.K / 2) : 0;
+    tp.k_blocks = static_cast<int>(((fp32 ? p.K / 2 : p.K) + bk - 1) / bk);
+    tp.kb_per_run = fp32 ? 3 : tp.k_blocks;
     // Epilogue warps: with at most 8 k-blocks per tile the MMAs of a tile take less time than
     // its epilogue, and 16 epilogue warps (pair tiles only) hide the epilogue's latencies.
     // The same variant also serves the transcendental activations at any K: with GELU fused, 16 warps of 96
@@ -353,9 +355,9 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
 
     if (p.in_dtype == SM120_DTYPE_FLOAT32) {
         // operands already split into tf32 pieces (see split_tf32.cu)
-        if (cg == 2) SM120_TC_CASE(KIND_TF32, 128, 8, 2, "tc_tf32x3_2cta_256x128x32_s8");
-        if (bn == 128) SM120_TC_CASE(KIND_TF32, 128, 6, 1, "tc_tf32x3_128x128x32_s6");
-        SM120_TC_CASE(KIND_TF32, 64, 8, 1, "tc_tf32x3_128x64x32_s8");
+        if (cg == 2) SM120_TC_CASE(KIND_TF32, 128, 4, 2, "tc_tf32x3_2cta_256x128x32_s4");
+        if (bn == 128) SM120_TC_CASE(KIND_TF32, 128, 3, 1, "tc_tf32x3_128x128x32_s3");
+        SM120_TC_CASE(KIND_TF32, 64, 4, 1, "tc_tf32x3_128x64x32_s4");
     } else if (!fp8) {
         const bool bf = p.in_dtype == SM120_DTYPE_BFLOAT16;
         if (cg == 2 && ew == 16) {

@@ -3,6 +3,6 @@
 #include "gemm_tcgen05_kernel.cuh"
 
 namespace sm120 {
-template cudaError_t launch_variant<KIND_TF32, 128, 8, 2>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+template cudaError_t launch_variant<KIND_TF32, 128, 4, 2>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
                                                         const TcParams&, int, int, cudaStream_t, bool);
 }  // namespace sm120

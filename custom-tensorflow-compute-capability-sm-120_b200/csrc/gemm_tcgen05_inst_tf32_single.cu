@@ -3,8 +3,8 @@
 #include "gemm_tcgen05_kernel.cuh"
 
 namespace sm120 {
-template cudaError_t launch_variant<KIND_TF32, 128, 6, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+template cudaError_t launch_variant<KIND_TF32, 128, 3, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
                                                         const TcParams&, int, int, cudaStream_t, bool);
-template cudaError_t launch_variant<KIND_TF32, 64, 8, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
+template cudaError_t launch_variant<KIND_TF32, 64, 4, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DestMaps&,
                                                         const TcParams&, int, int, cudaStream_t, bool);
 }  // namespace sm120

@@ -182,7 +182,7 @@ cudaError_t launch_resolved(GemmProblem& p, int path, void* workspace = nullptr,
             return e;
         }
         if (e == cudaSuccess) {
-            g_launch_count.fetch_add(3, std::memory_order_relaxed);
+            g_launch_count.fetch_add(2, std::memory_order_relaxed);
             t_last_kernel = name;
         }
         return e;

@@ -5,16 +5,20 @@
 // and  lo = (x - hi) with its low 13 bits cleared  (x - hi is exact), both
 // exactly representable in tf32.  Then
 //     A.B  ~=  A_hi.B_hi + A_hi.B_lo + A_lo.B_hi          (lo.lo dropped: 2^-22 relative)
-// is ONE tf32 GEMM over a K dimension three times as long:
-//     A3[m, :] = [ A_hi[m, :] | A_hi[m, :] | A_lo[m, :] ]     (K-major, pitch 3*Kp)
-//     B3[n, :] = [ B_hi[:, n] | B_lo[:, n] | B_hi[:, n] ]     (K-major, pitch 3*Kp)
-// with Kp = K rounded up to 32 and zero padding, accumulated in fp32 in TMEM by
-// the same kernel as the 16-bit types.  The split kernels below write A3 and B3
-// into caller-provided workspace, handling the caller's transposes and pitches,
-// so the GEMM always sees two K-major operands.  The tensor cores truncate when
-// they add into the fp32 accumulator, so the relative Frobenius error against
-// float64 grows with K, about K * 2^-27: 1.16e-5 measured at K = 1024, outside
-// the op's 1e-5 gate, which is why this path is opt-in.
+// is ONE tf32 GEMM whose k-blocks each issue three products.  The split kernel below writes
+//     A2[m, :] = [ A_hi[m, :] | A_lo[m, :] ]     (K-major, pitch 2*Kp)
+//     B2[n, :] = [ B_hi[:, n] | B_lo[:, n] ]     (K-major, pitch 2*Kp)
+// with Kp = K rounded up to 32 and zero padding into caller-provided workspace, handling the
+// caller's transposes and pitches, so the GEMM always sees two K-major operands; the GEMM kernel
+// (the same as for the 16-bit types) loads the hi and lo tiles of both operands into one pipeline
+// stage and accumulates the three products in fp32 in TMEM.  (A K dimension three times as long,
+// [hi | hi | lo] . [hi | lo | hi], gives the same sums but fills shared memory 1.5x as often, and that
+// fill, 96 bytes per clock and SM, was what bounded the first version.)  The tensor cores truncate when
+// they add into the fp32 accumulator, so a sum left in TMEM over the whole of K
+// drifts by about K * 2^-27 relative (1.16e-5 measured at K = 1024, outside the
+// op's 1e-5 gate); the GEMM therefore runs K in runs of eight k-blocks, each into a
+// zeroed accumulator, and the epilogue warps add the runs in registers with
+// round-to-nearest (gemm_tcgen05_kernel.cuh), which keeps K = 8192 below 6e-6.
 //
 // This is the tensor-core answer to the reference's fp32 kernels
 // (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:46-101,
@@ -28,17 +32,31 @@
 
 namespace sm120 {
 
-// One 32 x 32 tile of op(X) per block, 32 x 8 threads.  `rows` is M (for A) or N
-// (for B); element (r, k) of op(X) is X[r*ld + k] when k is contiguous in memory
-// and X[k*ld + r] otherwise.  seg_lo selects which of the three K segments holds
-// the lo piece: 2 for A ([hi | hi | lo]), 1 for B ([hi | lo | hi]).
+// One operand's split: `rows` is M (for A) or N (for B); element (r, k) of op(X) is X[r*ld + k] when k is
+// contiguous in memory and X[k*ld + r] otherwise.
+struct SplitJob {
+    const float* X;
+    float* X2;
+    long long rows, ld, stride_x;
+    int k_contiguous;
+    unsigned row_tiles, batches;
+};
+
+// One 32 x 32 tile of op(X) per block, 32 x 8 threads; both operands in ONE launch (grid z: A's batch entries, then
+// B's), because at the sizes where fp32 products are small the launches cost as much as the work.
 __global__ void __launch_bounds__(256)
-sm120_split_tf32_kernel(const float* __restrict__ X, float* __restrict__ X3, long long rows, long long K, long long Kp,
-                        long long ld, long long stride_x, int k_contiguous, int seg_lo) {
+sm120_split_tf32_kernel(const SplitJob ja, const SplitJob jb, long long K, long long Kp) {
+    // the GEMM that consumes the split operands may start its set-up now; it waits for this grid before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float tile[32][33];
-    const long long bz = blockIdx.z;
-    const float* x = X + bz * stride_x;
-    float* x3 = X3 + bz * rows * 3 * Kp;
+    const bool is_a = blockIdx.z < ja.batches;
+    const SplitJob& job = is_a ? ja : jb;
+    if (blockIdx.y >= job.row_tiles) return;
+    const long long bz = is_a ? blockIdx.z : blockIdx.z - ja.batches;
+    const long long rows = job.rows, ld = job.ld;
+    const int k_contiguous = job.k_contiguous;
+    const float* x = job.X + bz * job.stride_x;
+    float* x2 = job.X2 + bz * rows * 2 * Kp;
     const long long r0 = static_cast<long long>(blockIdx.y) * 32;
     const long long k0 = static_cast<long long>(blockIdx.x) * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -66,10 +84,9 @@ sm120_split_tf32_kernel(const float* __restrict__ X, float* __restrict__ X3, lon
         const float v = tile[j][tx];
         const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
         const float lo = __uint_as_float(__float_as_uint(v - hi) & 0xFFFFE000u);
-        float* row = x3 + r * 3 * Kp;
+        float* row = x2 + r * 2 * Kp;
         row[k] = hi;
-        row[Kp + k] = (seg_lo == 1) ? lo : hi;
-        row[2 * Kp + k] = (seg_lo == 2) ? lo : hi;
+        row[Kp + k] = lo;
     }
 }
 
@@ -79,35 +96,35 @@ size_t tf32x3_workspace_bytes(const GemmProblem& p) {
     const long long kp = padded_k(p.K);
     const long long nb_b = (p.batch > 1 && p.stride_b == 0) ? 1 : p.batch;     // a broadcast B is split once
     const long long nb_a = (p.batch > 1 && p.stride_a == 0) ? 1 : p.batch;
-    return static_cast<size_t>((p.M * nb_a + p.N * nb_b) * 3 * kp) * sizeof(float);
+    return static_cast<size_t>((p.M * nb_a + p.N * nb_b) * 2 * kp) * sizeof(float);
 }
 
 cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_limit_ns, const char** kernel_name) {
     const long long kp = padded_k(p.K);
     const long long nb_a = (p.batch > 1 && p.stride_a == 0) ? 1 : p.batch;
     const long long nb_b = (p.batch > 1 && p.stride_b == 0) ? 1 : p.batch;
-    if (nb_a > 65535 || nb_b > 65535 || (p.M + 31) / 32 > 65535 || (p.N + 31) / 32 > 65535) return cudaErrorInvalidValue;
-    float* a3 = static_cast<float*>(workspace);
-    float* b3 = a3 + p.M * nb_a * 3 * kp;
+    if (nb_a + nb_b > 65535 || (p.M + 31) / 32 > 65535 || (p.N + 31) / 32 > 65535) return cudaErrorInvalidValue;
+    float* a2 = static_cast<float*>(workspace);
+    float* b2 = a2 + p.M * nb_a * 2 * kp;
     // the GEMM over the split operands; checked before anything is enqueued, so a rejected call launches nothing
     GemmProblem g = p;
-    g.A = a3; g.B = b3;
-    g.K = 3 * kp;
-    g.lda = 3 * kp; g.ldb = 3 * kp;
+    g.A = a2; g.B = b2;
+    g.K = 2 * kp;                       // [hi | lo]: the GEMM walks kp and reads both halves of a row per k-block
+    g.lda = 2 * kp; g.ldb = 2 * kp;
     g.transpose_a = 0; g.transpose_b = 1;
-    g.stride_a = (nb_a > 1) ? p.M * 3 * kp : 0;
-    g.stride_b = (nb_b > 1) ? p.N * 3 * kp : 0;
+    g.stride_a = (nb_a > 1) ? p.M * 2 * kp : 0;
+    g.stride_b = (nb_b > 1) ? p.N * 2 * kp : 0;
     g.tf32_operands = 1;
     const char* why = nullptr;
     if (!tc_supported(g, &why)) return cudaErrorInvalidValue;
-    const dim3 block(256);
-    const dim3 grid_a(static_cast<unsigned>(kp / 32), static_cast<unsigned>((p.M + 31) / 32), static_cast<unsigned>(nb_a));
-    const dim3 grid_b(static_cast<unsigned>(kp / 32), static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(nb_b));
     // A: op(A)[m,k]; k is contiguous unless A is stored transposed.  B: op(B)^T[n,k]; k is contiguous when B is stored [N,K].
-    sm120_split_tf32_kernel<<<grid_a, block, 0, p.stream>>>(static_cast<const float*>(p.A), a3, p.M, p.K, kp, p.lda,
-                                                           p.stride_a, p.transpose_a ? 0 : 1, 2);
-    sm120_split_tf32_kernel<<<grid_b, block, 0, p.stream>>>(static_cast<const float*>(p.B), b3, p.N, p.K, kp, p.ldb,
-                                                           p.stride_b, p.transpose_b ? 1 : 0, 1);
+    const SplitJob ja{static_cast<const float*>(p.A), a2, p.M, p.lda, p.stride_a, p.transpose_a ? 0 : 1,
+                      static_cast<unsigned>((p.M + 31) / 32), static_cast<unsigned>(nb_a)};
+    const SplitJob jb{static_cast<const float*>(p.B), b2, p.N, p.ldb, p.stride_b, p.transpose_b ? 1 : 0,
+                      static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(nb_b)};
+    const dim3 grid(static_cast<unsigned>(kp / 32), ja.row_tiles > jb.row_tiles ? ja.row_tiles : jb.row_tiles,
+                    static_cast<unsigned>(nb_a + nb_b));
+    sm120_split_tf32_kernel<<<grid, 256, 0, p.stream>>>(ja, jb, p.K, kp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
 

@@ -596,7 +596,7 @@ def test_fp32_tensor_core_path(ops, binding):
     d.A = d.B = d.C = x.data_ptr()
     d.M = d.N = d.K = 256
     d.path = binding.PATH_TENSOR_CORE
-    assert lib.sm120_matmul_workspace_bytes(ctypes.byref(d)) == 2 * 256 * 3 * 256 * 4
+    assert lib.sm120_matmul_workspace_bytes(ctypes.byref(d)) == 2 * 256 * 2 * 256 * 4      # both operands as [hi | lo] rows
     assert lib.sm120_launch_matmul_ex(ctypes.byref(d)) == 1
     # AUTO without workspace: the FFMA kernel (the reference-signature entry point carries none)
     d.path = binding.PATH_AUTO
