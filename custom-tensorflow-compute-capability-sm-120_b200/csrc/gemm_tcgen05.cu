@@ -219,11 +219,13 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.tiles_m = static_cast<int>((p.M + BM * cg - 1) / (BM * cg));
     tp.tiles_n = static_cast<int>((p.N + bn - 1) / bn);
     // fp32 path: the operands' rows are [hi | lo] (K = 2 x the padded K of the product) and a k-block of 32 feeds
-    // three products.  The tensor cores' fp32 accumulation truncates, so a sum is carried in TMEM for 3 k-blocks
-    // (36 MMAs of 8 tf32 products) only and the runs are added in registers with round-to-nearest (see epilogue_role)
+    // three products.  The tensor cores' fp32 accumulation truncates, so a sum is carried in TMEM for 6 k-blocks
+    // (192 elements of K) only and the runs are added in registers with round-to-nearest (see epilogue_role).
+    // Measured relative Frobenius error against float64, K = 1024 and 8192 alike: 1.9e-6 on N(0,1) operands and
+    // 4.3e-6 on same-sign U[0,1) operands with runs of 6; 1.2e-6 / 2.2e-6 with runs of 3 at 10 % less speed.
     tp.k_lo = fp32 ? static_cast<int>(p.K / 2) : 0;
     tp.k_blocks = static_cast<int>(((fp32 ? p.K / 2 : p.K) + bk - 1) / bk);
-    tp.kb_per_run = fp32 ? 3 : tp.k_blocks;
+    tp.kb_per_run = fp32 ? 6 : tp.k_blocks;
     // Epilogue warps: with at most 8 k-blocks per tile the MMAs of a tile take less time than
     // its epilogue, and 16 epilogue warps (pair tiles only) hide the epilogue's latencies.
     // The same variant also serves the transcendental activations at any K: with GELU fused, 16 warps of 96

