@@ -29,7 +29,7 @@ QUANTIZE_FP8_STATIC_MAX_ELEMENTS = 268435456      # SM120_QUANTIZE_FP8_STATIC_MA
 
 # SM120_TUNE_* bits of SM120GemmDesc.tuning (per-call overrides for tests and tuning runs)
 TUNE_CTA_GROUP_1, TUNE_CTA_GROUP_2, TUNE_EPI_WARPS_8, TUNE_EPI_WARPS_16 = 0x1, 0x2, 0x4, 0x8
-TUNE_NO_SPLIT_TAIL, TUNE_TRACE = 0x10, 0x20
+TUNE_NO_SPLIT_TAIL, TUNE_TRACE, TUNE_NO_SPLIT_K = 0x10, 0x20, 0x40
 TRACE_WORDS_PER_CTA, TRACE_MAX_CTAS = 40, 160
 TRACE_BYTES = TRACE_MAX_CTAS * TRACE_WORDS_PER_CTA * 8
 
@@ -107,6 +107,7 @@ EXPORTS = {
     "sm120_set_wait_limit_ms": (None, [c_uint]),
     "sm120_get_launch_count": (c_uint64, []),
     "sm120_get_last_kernel_name": (c_char_p, []),
+    "sm120_get_last_split_k": (c_int, []),
 }
 
 _lib = None
@@ -159,6 +160,11 @@ def error_string(code: int) -> str:
 def last_kernel_name() -> str:
     s = load_library().sm120_get_last_kernel_name()
     return s.decode() if s else ""
+
+
+def last_split_k() -> int:
+    """K ranges of this thread's last matmul launch (1 = not split)."""
+    return int(load_library().sm120_get_last_split_k())
 
 
 def launch_count() -> int:

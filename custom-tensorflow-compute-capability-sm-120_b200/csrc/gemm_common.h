@@ -40,6 +40,8 @@ struct GemmProblem {
     void* extra_dests[7];
     int num_extra_dests;
     int tuning;                      // SM120GemmDesc::tuning (SM120_TUNE_* bits)
+    int64_t split_k;                 // 0, or: the `batch` entries are consecutive K ranges of this length of ONE product
+                                     // (A and B are not batched; entry z writes its partial sums to C + z * stride_c)
     void* trace;                     // null, or the caller's buffer for SM120_TUNE_TRACE
 };
 
@@ -64,6 +66,14 @@ cudaError_t simt_launch(const GemmProblem& p, const char** kernel_name);
 // (split kernels + tcgen05 kind::tf32 GEMM over the three partial products).
 size_t tf32x3_workspace_bytes(const GemmProblem& p);
 cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_limit_ns, const char** kernel_name);
+
+// Split-K for products with too few output tiles to fill the GPU: the K range is cut into `splitk_factor` parts
+// that run as the batch entries of one tcgen05 launch into fp32 workspace, and a second kernel adds the parts
+// in a fixed order and applies alpha, beta, bias, activation and the output type.  splitk_factor returns 1 when
+// the product should not be split (enough tiles, short K, batched, fp32, extra destinations, or switched off).
+int splitk_factor(const GemmProblem& p);
+size_t splitk_workspace_bytes(const GemmProblem& p);
+cudaError_t splitk_launch(const GemmProblem& p, void* workspace, uint64_t wait_limit_ns, const char** kernel_name);
 
 // Per-device status word of the tcgen05 kernel (0 = no wait ran out).
 cudaError_t tc_read_status(unsigned int* status, int clear);

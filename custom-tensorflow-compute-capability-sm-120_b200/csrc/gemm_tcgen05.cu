@@ -224,7 +224,8 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     // Measured relative Frobenius error against float64, K = 1024 and 8192 alike: 1.9e-6 on N(0,1) operands and
     // 4.3e-6 on same-sign U[0,1) operands with runs of 6; 1.2e-6 / 2.2e-6 with runs of 3 at 10 % less speed.
     tp.k_lo = fp32 ? static_cast<int>(p.K / 2) : 0;
-    tp.k_blocks = static_cast<int>(((fp32 ? p.K / 2 : p.K) + bk - 1) / bk);
+    tp.k_blocks = static_cast<int>(((fp32 ? p.K / 2 : (p.split_k > 0 ? p.split_k : p.K)) + bk - 1) / bk);
+    tp.k_split = static_cast<int>(p.split_k);
     tp.kb_per_run = fp32 ? 6 : tp.k_blocks;
     // Epilogue warps: with at most 8 k-blocks per tile the MMAs of a tile take less time than
     // its epilogue, and 16 epilogue warps (pair tiles only) hide the epilogue's latencies.
@@ -257,8 +258,8 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
     tp.full_work = tp.num_tiles;
     tp.a_mn_major = a_mn ? 1 : 0;
     tp.b_mn_major = b_mn ? 1 : 0;
-    tp.a_batched = (p.batch > 1 && p.stride_a != 0) ? 1 : 0;
-    tp.b_batched = (p.batch > 1 && p.stride_b != 0) ? 1 : 0;
+    tp.a_batched = (p.batch > 1 && p.stride_a != 0 && p.split_k == 0) ? 1 : 0;
+    tp.b_batched = (p.batch > 1 && p.stride_b != 0 && p.split_k == 0) ? 1 : 0;
     tp.C = p.C; tp.ldc = p.ldc; tp.stride_c = p.stride_c; tp.out_dtype = p.out_dtype;
     const int out_es = dtype_size(p.out_dtype);
     tp.c_vec_ok = (aligned16(p.C) && (p.ldc * out_es) % 16 == 0 && (p.stride_c * out_es) % 16 == 0) ? 1 : 0;

@@ -106,6 +106,7 @@ struct TcParams {
     int tiles_m, tiles_n, k_blocks, num_tiles;   // tiles are (CG*128) x BN
     int kb_per_run;                 // k-blocks summed in TMEM before the epilogue takes the partial sum (k_blocks: one run per tile)
     int k_lo;                       // fp32 path: K coordinate at which the operands' low pieces start (their rows are [hi | lo])
+    int k_split;                    // split-K: batch entry z covers K coordinates [z * k_split, (z + 1) * k_split) of unbatched operands; else 0
     int group_m;                    // row tiles per raster group (tiles of a group share their B columns in L2)
     FastDiv div_per_batch;          // tiles_m * tiles_n
     FastDiv div_group_span;         // group_m * tiles_n
@@ -1089,7 +1090,7 @@ sm120_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const uint32_t fb = full_for_tma + 8 * stage;
                     const uint32_t a_dst = smem_u32(smem) + stage * STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_BYTES;
-                    const int k0 = kb * BK;
+                    const int k0 = bz * p.k_split + kb * BK;
                     if (!p.a_mn_major) {
                         tma_load_3d<CG>(a_dst, &tmap_a, fb, k0, m0, za);
                     } else {

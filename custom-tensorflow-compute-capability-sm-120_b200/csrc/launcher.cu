@@ -48,6 +48,7 @@ DeviceInfo g_devices[MAX_DEVICES];
 std::atomic<uint64_t> g_launch_count{0};
 std::atomic<uint64_t> g_wait_limit_ns{0};   // 0 = not initialised yet
 thread_local const char* t_last_kernel = "";
+thread_local int t_last_split_k = 1;        // K parts of this thread's last matmul launch
 
 uint64_t wait_limit_ns() {
     uint64_t v = g_wait_limit_ns.load(std::memory_order_relaxed);
@@ -101,7 +102,7 @@ cudaError_t resolve(const SM120GemmDesc* d, GemmProblem* out) {
             return cudaErrorInvalidValue;
     }
     if (d->scale_a < 0.0f || d->scale_b < 0.0f) return cudaErrorInvalidValue;
-    if ((d->tuning & ~0x00FFFF3F) != 0) return cudaErrorInvalidValue;
+    if ((d->tuning & ~0x00FFFF7F) != 0) return cudaErrorInvalidValue;
     if ((d->tuning & SM120_TUNE_CTA_GROUP_1) && (d->tuning & SM120_TUNE_CTA_GROUP_2)) return cudaErrorInvalidValue;
     if ((d->tuning & SM120_TUNE_EPI_WARPS_8) && (d->tuning & SM120_TUNE_EPI_WARPS_16)) return cudaErrorInvalidValue;
     if (d->tuning & SM120_TUNE_TRACE) {
@@ -189,6 +190,21 @@ cudaError_t launch_resolved(GemmProblem& p, int path, void* workspace = nullptr,
     }
     const bool tc_ok = tc_supported(p, &why);
     if (path == SM120_PATH_TENSOR_CORE && !tc_ok) return cudaErrorInvalidValue;
+    // few output tiles and a long K: split K over the idle SMs when the caller gave workspace for the partial sums
+    if (path != SM120_PATH_SIMT && tc_ok && workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
+        const size_t need = splitk_workspace_bytes(p);
+        if (need != 0 && workspace_bytes >= need) {
+            e = splitk_launch(p, workspace, wait_limit_ns(), &name);
+            if (e == cudaSuccess) {
+                g_launch_count.fetch_add(2, std::memory_order_relaxed);
+                t_last_kernel = name;
+                t_last_split_k = splitk_factor(p);
+                return e;
+            }
+            if (e != cudaErrorInvalidValue) return e;          // InvalidValue: nothing was enqueued; run unsplit
+        }
+    }
+    t_last_split_k = 1;
     if (path != SM120_PATH_SIMT && tc_ok) {
         e = tc_launch(p, wait_limit_ns(), &name);
     } else {
@@ -298,8 +314,16 @@ cudaError_t sm120_ipc_close(void* base) {
 size_t sm120_matmul_workspace_bytes(const SM120GemmDesc* desc) {
     GemmProblem p;
     if (resolve(desc, &p) != cudaSuccess) return 0;
-    if (p.in_dtype != SM120_DTYPE_FLOAT32 || p.M == 0 || p.N == 0 || p.K == 0) return 0;
-    return tf32x3_workspace_bytes(p);
+    if (p.M == 0 || p.N == 0 || p.K == 0) return 0;
+    if (p.in_dtype == SM120_DTYPE_FLOAT32) return tf32x3_workspace_bytes(p);
+    // 16-bit and FP8 products take workspace only when they would be split along K
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || query_device(device, &sms) != cudaSuccess) return 0;
+    p.device = device;
+    p.sm_count = sms;
+    const char* why = nullptr;
+    if (desc->path == SM120_PATH_SIMT || !tc_supported(p, &why)) return 0;
+    return splitk_workspace_bytes(p);
 }
 
 cudaError_t sm120_launch_matmul(const void* A, const void* B, void* C, int M, int N, int K, float alpha, float beta,
@@ -623,6 +647,8 @@ void sm120_set_wait_limit_ms(unsigned int ms) {
 uint64_t sm120_get_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
 
 const char* sm120_get_last_kernel_name(void) { return t_last_kernel; }
+
+int sm120_get_last_split_k(void) { return t_last_split_k; }
 
 cudaError_t sm120_get_kernel_clock(int device_id, unsigned long long* cycles, unsigned long long* ns) {
     if (cycles == nullptr || ns == nullptr) return cudaErrorInvalidValue;

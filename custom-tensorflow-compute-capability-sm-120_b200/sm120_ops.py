@@ -499,6 +499,13 @@ def fused_matmul(
         d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
         if fp32_tensor_cores:
             d.path = _b.PATH_TENSOR_CORE
+    elif a.dtype != torch.float32 and batch == 1 and trace is None and use_tensor_cores and not peer_outs and K >= 1024:
+        # few output tiles and a long K: the launcher splits K when it is given room for the partial sums
+        need = int(_b.load_library().sm120_matmul_workspace_bytes(ctypes.byref(d)))
+        if need:
+            ws = _workspace(a.device, need)
+            keep.append(ws)
+            d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
 
     if peer_outs:
         if host_kind is not None or beta != 0.0:

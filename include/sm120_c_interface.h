@@ -159,6 +159,7 @@ typedef struct SM120GemmDesc {
  *   CTA_GROUP_1 / _2     single-CTA tiles (128 x BN) / CTA-pair tiles (256 x 256)
  *   EPI_WARPS_8 / _16    epilogue warps per CTA (16 exists for pair tiles only)
  *   NO_SPLIT_TAIL        a short last wave is not cut into half-width tiles
+ *   NO_SPLIT_K           the K range is never cut into parts (see sm120_matmul_workspace_bytes)
  *   GROUP_M(g)           raster group of g row tiles, 1 <= g <= 255 (0 = heuristic)
  *   STALL_KBLOCK(kb)     self-test of the bounded waits: every TMA producer stops
  *                        before k-block kb (0 <= kb <= 254) of its first tile, so a
@@ -183,6 +184,7 @@ typedef struct SM120GemmDesc {
 #define SM120_TUNE_EPI_WARPS_16    0x8
 #define SM120_TUNE_NO_SPLIT_TAIL   0x10
 #define SM120_TUNE_TRACE           0x20
+#define SM120_TUNE_NO_SPLIT_K      0x40
 #define SM120_TUNE_GROUP_M(g)      (((g) & 0xFF) << 8)
 #define SM120_TUNE_STALL_KBLOCK(kb) ((((kb) + 1) & 0xFF) << 16)
 #define SM120_TRACE_WORDS_PER_CTA  40
@@ -248,7 +250,16 @@ cudaError_t sm120_ipc_close(void* base);
  * sums are added in registers with round-to-nearest.  The relative Frobenius
  * error against float64 stays below 1e-5 (the op's fp32 gate) for K up to 8192,
  * same-sign data included; the FFMA kernel's stays below 1e-6.
- * Returns 0 when the descriptor's types need no workspace.  The workspace can
+ * FLOAT16 / BFLOAT16 / FP8 inputs: split-K.  A product whose output tiles would
+ * occupy less than half of the GPU and whose K is long (at least 16 k-blocks of
+ * 128 bytes) is cut into 2..8 consecutive K ranges that run as ONE tensor-core
+ * launch into fp32 partial sums in the workspace; a second kernel adds the parts
+ * in ascending order (reproducible, no atomics) and applies alpha, beta, bias,
+ * activation and the output type.  The returned size is parts * M * N * 4 bytes
+ * for such a product and 0 otherwise; a launch whose workspace is absent or
+ * smaller runs unsplit.  Batched products, launches with peer destinations and
+ * SM120_TUNE_NO_SPLIT_K are never split.
+ * Returns 0 when the descriptor needs no workspace.  The workspace can
  * be reused by later calls on the same stream.  No counterpart in the reference.
  */
 size_t sm120_matmul_workspace_bytes(const SM120GemmDesc* desc);
@@ -515,6 +526,10 @@ uint64_t sm120_get_launch_count(void);
  * "tc_bf16_128x256x64_s4" or "simt_f32_64x64"; "" before any launch.
  * No counterpart in the reference. */
 const char* sm120_get_last_kernel_name(void);
+
+/* Number of K ranges (1 = not split) of the last matmul launch on this host
+ * thread.  No counterpart in the reference. */
+int sm120_get_last_split_k(void);
 
 #ifdef __cplusplus
 }

@@ -78,7 +78,7 @@ def _good_desc(binding):
     lambda d: setattr(d, "scale_a", -1.0),
     lambda d: (setattr(d, "batch", 2), setattr(d, "stride_c", 10)),       # overlapping outputs
     lambda d: (setattr(d, "bias", 0x4000), setattr(d, "bias_dtype", 3)),  # FP8 bias
-    lambda d: setattr(d, "tuning", 0x40),          # an undefined tuning bit
+    lambda d: setattr(d, "tuning", 0x80),          # an undefined tuning bit
     lambda d: setattr(d, "tuning", 0x3),           # both CTA-group overrides at once
     lambda d: setattr(d, "tuning", 0xC),           # both epilogue-warp overrides at once
     lambda d: setattr(d, "tuning", 0x20),          # a trace without a buffer for it

@@ -451,6 +451,71 @@ def test_baseline_config5_full_size_one_gpu(ops, binding):
     assert torch.equal(ops.fused_matmul(qa, qb, transpose_b=True, scale_a=sa, scale_b=sb), c)
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_split_k_matches_oracle(ops, binding, dtype, ta, tb):
+    """Few output tiles and a long K: the launcher cuts K into parts that run as one launch into fp32 workspace and
+    a second kernel adds them in a fixed order (with alpha, beta, bias, activation).  Every operand layout, a ragged
+    M and N, skinny M; the result against the oracle, against the unsplit launch, and run to run."""
+    rng = np.random.default_rng(70 + 2 * ta + tb)
+    for (M, N, K) in ((296, 520, 4096), (128, 1024, 2048), (1000, 264, 8192)):
+        a = ref.quantize(rng.standard_normal((K, M) if ta else (M, K), dtype=np.float32), dtype)
+        b = ref.quantize(0.05 * rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32), dtype)
+        bias = rng.standard_normal(N).astype(np.float32)
+        c_in = ref.quantize(rng.standard_normal((M, N), dtype=np.float32), dtype)
+        kw = dict(ta=ta, tb=tb, bias=bias, act=0, alpha=0.5, beta=0.25)          # 0 = relu
+        got = run(ops, a, b, c_in=c_in.copy(), **kw)
+        assert binding.last_split_k() >= 2, (M, N, K, binding.last_kernel_name())
+        want = ref.matmul_oracle(a, b, transpose_a=ta, transpose_b=tb, alpha=0.5, beta=0.25, c_in=c_in, bias=bias, act=kw["act"],
+                                 out_dtype=dtype)
+        check(got, want, dtype, f"split-K {M}x{N}x{K}")
+        again = run(ops, a, b, c_in=c_in.copy(), **kw)
+        assert np.array_equal(got.view(np.uint16), again.view(np.uint16))
+        # the unsplit launch of the same product (switched off per call) agrees within the output rounding
+        r = ops.fused_matmul(U.to_cuda(a), U.to_cuda(b), transpose_a=ta, transpose_b=tb, bias=U.to_cuda(bias), activation=kw["act"],
+                             alpha=0.5, beta=0.25, out=U.to_cuda(c_in.copy()), tuning=binding.TUNE_NO_SPLIT_K)
+        torch.cuda.synchronize()
+        assert binding.last_split_k() == 1
+        assert ref.rel_frobenius(U.to_numpy(r), got) <= TOL[dtype]
+
+
+def test_split_k_fp8_and_when_it_is_not_used(ops, binding):
+    rng = np.random.default_rng(80)
+    M, N, K = 256, 512, 8192
+    a32 = rng.standard_normal((M, K), dtype=np.float32)
+    b32 = rng.standard_normal((N, K), dtype=np.float32)
+    sa, sb = float(np.float32(ref.fp8_scale(a32))), float(np.float32(ref.fp8_scale(b32)))
+    a, b = ref.quantize(a32 * np.float32(sa), "fp8_e4m3"), ref.quantize(b32 * np.float32(sb), "fp8_e4m3")
+    want = ref.matmul_oracle(a, b, transpose_b=True, scale_a=sa, scale_b=sb, out_dtype="bfloat16")
+    got = run(ops, a, b, tb=True, sa=sa, sb=sb)
+    assert binding.last_split_k() >= 2 and binding.last_kernel_name().startswith("tc_e4m3")
+    assert ref.rel_frobenius(got, want) <= 1e-2
+    r2 = ops.fused_matmul(U.to_cuda(a), U.to_cuda(b), transpose_b=True,
+                          scale_a=torch.tensor([sa], device="cuda"), scale_b=torch.tensor([sb], device="cuda"))
+    torch.cuda.synchronize()
+    assert binding.last_split_k() >= 2 and ref.rel_frobenius(U.to_numpy(r2), want) <= 1e-2
+    # enough tiles, a short K, or a batch: one launch as before
+    for shape in ((4096, 4096, 4096), (256, 512, 512)):
+        x = torch.randn(shape[0], shape[2], device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(shape[2], shape[1], device="cuda", dtype=torch.bfloat16)
+        ops.fused_matmul(x, w)
+        assert binding.last_split_k() == 1, shape
+    xb = torch.randn(2, 256, 4096, device="cuda", dtype=torch.bfloat16)
+    wb = torch.randn(2, 4096, 256, device="cuda", dtype=torch.bfloat16)
+    ops.fused_matmul(xb, wb)
+    assert binding.last_split_k() == 1
+    # through the C ABI without workspace (the reference-signature entry point carries none): unsplit
+    lib = binding.load_library()
+    x = torch.randn(256, 8192, device="cuda", dtype=torch.float16)
+    w = torch.randn(8192, 512, device="cuda", dtype=torch.float16)
+    c = torch.empty(256, 512, device="cuda", dtype=torch.float16)
+    assert lib.sm120_launch_matmul(x.data_ptr(), w.data_ptr(), c.data_ptr(), 256, 512, 8192, 1.0, 0.0, 1,
+                                   torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert binding.last_split_k() == 1
+    assert ref.rel_frobenius(c.float().cpu().numpy(), (x.float() @ w.float()).cpu().numpy()) <= 1e-2
+
+
 def test_determinism_small_and_ragged(ops):
     rng = np.random.default_rng(77)
     for dtype, shape in (("bfloat16", (392, 520, 264)), ("float32", (300, 200, 100))):
