@@ -19,7 +19,9 @@ host-BLAS product of the whole workload timed on this box's cores;
 `fp8_m_sharded` is the FP8 product M = 65536, N = K = 8192 split by rows over
 the N ranks (strong scaling: the whole M on one GPU at N = 1), with the fused
 and the NCCL gather of C beside it at N > 1; `all_configs` (N = 1) lists every
-benchmark workload.  `--impl reference` times only the CPU product.
+benchmark workload and `small_shapes` four products with few output tiles (GPU time
+from CUDA-graph replays, the K parts chosen, cuBLAS beside them).  `--impl reference`
+times only the CPU product.
 
 Other workloads (`--workload`): f32_1024, f16_4096_tn, bf16_4096_tn,
 bf16_dense_gelu, bf16_batched_qk, fp8_65536 (M split over the ranks), fp8_8192,
@@ -492,6 +494,63 @@ def side_table(torch, ops, binding, device):
     return table
 
 
+def small_shapes(torch, ops, binding, device):
+    """Products with few output tiles (projection, decode-time and weight-gradient shapes, bf16, B stored [N, K]):
+    GPU time per call with the host taken out (24 calls captured into a CUDA graph, the graph replayed), the K
+    parts the launcher chose, and cuBLAS through torch.matmul timed the same way."""
+    def graph_time(fn, calls=24):
+        for _ in range(6):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(calls):
+                    fn()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (3 * calls) * 1e-3
+
+    table = {}
+    for (M, N, K) in ((1024, 1024, 8192), (128, 4096, 4096), (64, 8192, 8192), (256, 8192, 8192)):
+        key = f"bf16_{M}x{N}x{K}"
+        try:
+            nsets = min(6, max(2, int(400e6 // ((M * K + N * K + M * N) * 2)) + 1))
+            sets = [(torch.randn(M, K, device=device, dtype=torch.bfloat16), torch.randn(N, K, device=device, dtype=torch.bfloat16),
+                     torch.empty(M, N, device=device, dtype=torch.bfloat16)) for _ in range(nsets)]
+            turn = [0]
+
+            def ours():
+                a, b, c = sets[turn[0] % nsets]
+                turn[0] += 1
+                ops.fused_matmul(a, b, out=c, transpose_b=True)
+
+            def cublas():
+                a, b, c = sets[turn[0] % nsets]
+                turn[0] += 1
+                torch.matmul(a, b.t(), out=c)
+            t_ours = graph_time(ours)
+            kernel, parts = binding.last_kernel_name(), binding.last_split_k()
+            t_cublas = graph_time(cublas)
+            flops = 2.0 * M * N * K
+            table[key] = {"us": round(t_ours * 1e6, 1), "tflops": round(flops / t_ours / 1e12, 1), "kernel": kernel, "k_parts": parts,
+                          "cublas_us": round(t_cublas * 1e6, 1), "cublas_tflops": round(flops / t_cublas / 1e12, 1)}
+            del sets
+            torch.cuda.empty_cache()
+        except Exception as e:  # keep the headline even if a side measurement fails
+            table[key] = {"error": str(e)[:200]}
+    return table
+
+
 def fp8_m_sharded(torch, dist, pkg, device, rank, world, barrier, steps=64, warmup=5):
     """The FP8 product M = 65536, N = K = 8192 split by rows over the ranks (the whole M on one GPU
     at world 1): one scale for all of A from the maximum over every rank's slab, B replicated.
@@ -858,6 +917,7 @@ def run_gpu(args, rank, world, local_rank):
             line["trace"] = trace_summary
         if world == 1 and not args.no_side_table and not args.lean:
             line["all_configs"] = side_table(torch, ops, binding, device)
+            line["small_shapes"] = small_shapes(torch, ops, binding, device)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

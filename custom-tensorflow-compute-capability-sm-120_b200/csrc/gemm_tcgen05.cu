@@ -213,6 +213,10 @@ cudaError_t tc_launch(const GemmProblem& p, uint64_t wait_limit_ns, const char**
         }
     }
 
+    // The K parts of a split product (see splitk.cu) were counted in 128 x 128 tiles when there are at most 128 rows:
+    // narrower tiles would fill the SMs on paper, but a 128 x 64 tile's MMAs are bound by shared-memory bandwidth
+    // (measured on [64, 8192] x [8192, 8192]: 40 us against 31 us)
+    if (p.split_k > 0 && cg == 1 && p.optimization_level != 0 && p.N > 64 && min_bn <= 128) bn = 128;
     TcParams tp{};
     tp.M = static_cast<int>(p.M); tp.N = static_cast<int>(p.N); tp.K = static_cast<int>(p.K);
     tp.batch = static_cast<int>(p.batch);

@@ -89,9 +89,10 @@ int splitk_factor(const GemmProblem& p) {
     if (p.M < 1 || p.N < 1 || p.sm_count < 1) return 1;
     const int64_t bk = 128 / dtype_size(p.in_dtype);             // elements of K per k-block
     if (p.K < 16 * bk) return 1;
-    // output tiles of the shape the kernel would take: 256 x 256 pairs when there are more than 128 rows, else 128 x 256
+    // output tiles of the shape the kernel takes when the tiles do not fill the GPU: 256 x 256 pairs when there are more
+    // than 128 rows, else 128 x 128; the parts are chosen so that parts x tiles stays within one wave
     const bool pair = p.M > 128;
-    const int64_t tiles = ((p.M + (pair ? 255 : 127)) / (pair ? 256 : 128)) * ((p.N + 255) / 256);
+    const int64_t tiles = pair ? ((p.M + 255) / 256) * ((p.N + 255) / 256) : (p.N + 127) / 128;
     const int64_t slots = pair ? p.sm_count / 2 : p.sm_count;
     int64_t s = slots / tiles;
     if (s > SPLITK_MAX) s = SPLITK_MAX;
