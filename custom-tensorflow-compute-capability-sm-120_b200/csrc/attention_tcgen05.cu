@@ -280,8 +280,11 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = static_cast<int>(blockIdx.x) * ATT_BM;
-    const int bh = static_cast<int>(blockIdx.y);
+    // Grid: (query tiles, batch), or with the causal mask (batch, query tiles) walked from the LAST query tile down:
+    // a causal tile's work grows with its index, blocks are handed out in x-then-y order, so the long tiles of every
+    // batch entry start first and the short ones fill the end of the launch
+    const int q0 = (p.causal ? static_cast<int>(gridDim.y - 1 - blockIdx.y) : static_cast<int>(blockIdx.x)) * ATT_BM;
+    const int bh = static_cast<int>(p.causal ? blockIdx.x : blockIdx.y);
     WaitCtx wctx{p.status, abort_flag, 0u, p.wait_limit_ns};
 
     // key tiles this CTA visits: all of them, or up to the diagonal of its last query row
@@ -653,7 +656,8 @@ static cudaError_t attention_launch_d(const CUtensorMap& tq, const CUtensorMap& 
         if (e != cudaSuccess) return e;
         attr_done.fetch_or(bit, std::memory_order_release);
     }
-    const dim3 grid(static_cast<unsigned>((p.seq_q + ATT_BM - 1) / ATT_BM), static_cast<unsigned>(p.batch), 1);
+    const unsigned q_tiles = static_cast<unsigned>((p.seq_q + ATT_BM - 1) / ATT_BM), entries = static_cast<unsigned>(p.batch);
+    const dim3 grid = p.causal ? dim3(entries, q_tiles, 1) : dim3(q_tiles, entries, 1);
     kern<<<grid, ATT_THREADS, Cfg::SMEM, stream>>>(tq, tk, tv, p);
     return cudaGetLastError();
 }
@@ -662,7 +666,8 @@ bool attention_fused_supported(int dtype, long long batch, long long seq_q, long
                                const void* k, const void* v, const void* out) {
     if (dtype != SM120_DTYPE_FLOAT16 && dtype != SM120_DTYPE_BFLOAT16) return false;
     if (head_dim != 64 && head_dim != 128) return false;
-    if (batch < 1 || batch > 65535 || seq_q < 1 || seq_k < 1 || seq_q >= (1ll << 31) || seq_k >= (1ll << 31)) return false;
+    // batch entries and query tiles are grid dimensions, either of which may be the y dimension
+    if (batch < 1 || batch > 65535 || seq_q < 1 || seq_k < 1 || seq_q > 65535ll * ATT_BM || seq_k >= (1ll << 31)) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                            reinterpret_cast<uintptr_t>(out);
     return (bits & 15u) == 0;
