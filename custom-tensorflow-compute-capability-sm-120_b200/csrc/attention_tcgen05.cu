@@ -317,6 +317,22 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         prefetch_tmap(&tmap_q);
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
+        // Q and the first two K tiles are requested here, before the TMEM allocation and the block-wide barrier below:
+        // their trip from HBM is the longest part of a block's start, and nothing they need is still missing
+        if (n_kv > 0) {
+            mbar_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+            for (int d = 0; d < DB; ++d) tma_load_3d<1>(q_smem + d * (ATT_BM * 128), &tmap_q, q_full, d * 64, q0, bh);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (j < n_kv) {
+                    mbar_expect_tx(k_full + 8 * j, Cfg::K_BYTES);
+#pragma unroll
+                    for (int d = 0; d < DB; ++d)
+                        tma_load_3d<1>(k_smem + j * Cfg::K_BYTES + d * (ATT_BN * 128), &tmap_k, k_full + 8 * j, d * 64, j * ATT_BN, bh);
+                }
+            }
+        }
     }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(tmem_holder), Cfg::TMEM_COLS);
@@ -332,13 +348,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         bool ok = n_kv > 0;
-        int issued_k = 0, issued_v = 0;
-        if (ok && elect_one_sync()) {
-            mbar_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-            for (int d = 0; d < DB; ++d) tma_load_3d<1>(q_smem + d * (ATT_BM * 128), &tmap_q, q_full, d * 64, q0, bh);
-        }
-        __syncwarp();
+        int issued_k = min(n_kv, 2), issued_v = 0;             // Q, K_0 and K_1 were requested during set-up
         auto load_k = [&](int j) -> bool {
             const uint32_t st = j % ATT_K_STAGES, ph = (j / ATT_K_STAGES) & 1;
             bool w = att_wait(k_empty + 8 * st, ph ^ 1u, wctx, 0x41000000u);
@@ -354,9 +364,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             ++issued_k;
             return true;
         };
-        // the scores run two tiles ahead of the P V products: K_0 and K_1 first, then V_j and K_{j+2}
-        if (ok) ok = load_k(0);
-        if (ok && n_kv > 1) ok = load_k(1);
+        // the scores run two tiles ahead of the P V products: K_0 and K_1 first (above), then V_j and K_{j+2}
         for (int j = 0; ok && j < n_kv; ++j) {
             const uint32_t st = j % ATT_V_STAGES, ph = (j / ATT_V_STAGES) & 1;
             bool w = att_wait(v_empty + 8 * st, ph ^ 1u, wctx, 0x42000000u);
