@@ -456,6 +456,49 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
     return 0.5f * x * (1.0f + copysignf(erf_abs, z));
 }
 
+// The same for two values at once on sm_100's packed fp32 arithmetic (fma.rn.f32x2 and friends: one issue slot for
+// two results).  In the fused Dense epilogue the activation competes with the tensor pipe's feed for issue slots;
+// the polynomial, the products and the final scaling take half as many this way.  Same formula, same constants.
+__device__ __forceinline__ uint64_t epi_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void epi_split2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t epi_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t epi_mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ void gelu_erf_fast2(float& x0, float& x1) {
+    const uint64_t x2 = epi_pack2(x0, x1);
+    float z0, z1;
+    epi_split2(epi_mul2(x2, epi_pack2(0.70710678118654752440f, 0.70710678118654752440f)), z0, z1);
+    const uint64_t az2 = epi_pack2(fabsf(z0), fabsf(z1));
+    float d0, d1;
+    epi_split2(epi_fma2(az2, epi_pack2(0.3275911f, 0.3275911f), epi_pack2(1.0f, 1.0f)), d0, d1);
+    const uint64_t t2 = epi_pack2(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
+    uint64_t poly = epi_fma2(epi_pack2(1.061405429f, 1.061405429f), t2, epi_pack2(-1.453152027f, -1.453152027f));
+    poly = epi_fma2(poly, t2, epi_pack2(1.421413741f, 1.421413741f));
+    poly = epi_fma2(poly, t2, epi_pack2(-0.284496736f, -0.284496736f));
+    poly = epi_fma2(poly, t2, epi_pack2(0.254829592f, 0.254829592f));
+    poly = epi_mul2(poly, t2);
+    float s0, s1;
+    epi_split2(epi_mul2(az2, az2), s0, s1);
+    const uint64_t e2 = epi_pack2(__expf(-s0), __expf(-s1));
+    float a0, a1;
+    epi_split2(epi_fma2(epi_mul2(poly, e2), epi_pack2(-1.0f, -1.0f), epi_pack2(1.0f, 1.0f)), a0, a1);      // |erf|
+    const uint64_t one_plus = epi_pack2(1.0f + copysignf(a0, z0), 1.0f + copysignf(a1, z1));
+    epi_split2(epi_mul2(epi_mul2(x2, epi_pack2(0.5f, 0.5f)), one_plus), x0, x1);
+}
+
 template <int ACT>
 __device__ __forceinline__ void act_loop(float (&v)[32]) {
 #pragma unroll
@@ -475,7 +518,7 @@ __device__ __forceinline__ void act_apply32(float (&v)[32], int act) {
         for (int j = 0; j < 32; ++j) v[j] = fmaxf(0.0f, v[j]);
     } else if constexpr (ACTC == ACTC_GELU_ERF) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = gelu_erf_fast(v[j]);
+        for (int j = 0; j < 32; j += 2) gelu_erf_fast2(v[j], v[j + 1]);
     } else {
         switch (act) {
             case SM120_ACTIVATION_RELU:       act_apply32<ACTC_RELU>(v, act); break;
