@@ -494,6 +494,13 @@ def test_split_k_fp8_and_when_it_is_not_used(ops, binding):
                           scale_a=torch.tensor([sa], device="cuda"), scale_b=torch.tensor([sb], device="cuda"))
     torch.cuda.synchronize()
     assert binding.last_split_k() >= 2 and ref.rel_frobenius(U.to_numpy(r2), want) <= 1e-2
+    # a width that neither TMA stores nor 16-byte loads can use (N % 4 != 0): the general epilogue writes the partial sums,
+    # the element-wise form of the second kernel adds them; fp32 output
+    a16 = ref.quantize(rng.standard_normal((200, 4096), dtype=np.float32), "float16")
+    b16 = ref.quantize(0.05 * rng.standard_normal((262, 4096), dtype=np.float32), "float16")
+    got32 = run(ops, a16, b16, tb=True, out_dtype="float32")
+    assert binding.last_split_k() >= 2
+    assert ref.rel_frobenius(got32, ref.matmul_oracle(a16, b16, transpose_b=True, round_output=False)) <= 1e-3
     # enough tiles, a short K, or a batch: one launch as before
     for shape in ((4096, 4096, 4096), (256, 512, 512)):
         x = torch.randn(shape[0], shape[2], device="cuda", dtype=torch.bfloat16)
