@@ -191,6 +191,21 @@ def _row_major_2d(t: torch.Tensor) -> bool:
 _WORKSPACES: Dict[Any, torch.Tensor] = {}
 
 
+_SM_COUNTS: Dict[int, int] = {}
+
+
+def _few_tiles(device: torch.device, m: int, n: int) -> bool:
+    """Could the launcher want to split K?  Only when the output tiles (256 x 256 above 128 rows, else 128 x 128)
+    leave at least half of the SMs idle; asking the library for the workspace size is skipped otherwise."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    sms = _SM_COUNTS.get(idx)
+    if sms is None:
+        sms = _SM_COUNTS[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    if m > 128:
+        return 2 * ((m + 255) // 256) * ((n + 255) // 256) <= sms // 2
+    return 2 * ((n + 127) // 128) <= sms
+
+
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """A scratch buffer of at least `nbytes` for the current stream of `device`, reused by
     later calls on that stream (which orders the launches that use it).  Streams do not
@@ -499,7 +514,8 @@ def fused_matmul(
         d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
         if fp32_tensor_cores:
             d.path = _b.PATH_TENSOR_CORE
-    elif a.dtype != torch.float32 and batch == 1 and trace is None and use_tensor_cores and not peer_outs and K >= 1024:
+    elif (a.dtype != torch.float32 and batch == 1 and trace is None and use_tensor_cores and not peer_outs and K >= 1024
+          and _few_tiles(a.device, M, N)):
         # few output tiles and a long K: the launcher splits K when it is given room for the partial sums
         need = int(_b.load_library().sm120_matmul_workspace_bytes(ctypes.byref(d)))
         if need:
