@@ -131,7 +131,7 @@ def make_device_operands(spec, seed, device, ops, reduce_max=None):
         b = torch.rand(K, N, generator=g, device=device) * 2 - 1
         if spec.get("ffma"):
             kw["use_tensor_cores"] = False          # the exact FFMA kernel instead of 3xTF32 on the tensor cores
-    elif spec["name"] in ("f16_4096_tn", "bf16_4096_tn"):
+    elif dt in ("f16", "bf16") and spec["layout"] == "tn":
         tdt = torch.float16 if dt == "f16" else torch.bfloat16
         a = (torch.randn(M, K, generator=g, device=device) / K ** 0.5).to(tdt)
         b = (torch.randn(N, K, generator=g, device=device) / K ** 0.5).to(tdt)      # stored [N, K]
@@ -144,6 +144,8 @@ def make_device_operands(spec, seed, device, ops, reduce_max=None):
     elif spec["name"] == "bf16_batched_qk":
         a = torch.randn(B, M, K, generator=g, device=device).bfloat16()
         b = torch.randn(B, K, N, generator=g, device=device).bfloat16()
+    elif dt != "f8e4m3":
+        raise SystemExit(f"no operand recipe for workload {spec['name']}")
     else:   # FP8: N(0,1) before quantisation, per-tensor scales that map amax to 448
         b32 = torch.randn(N, K, generator=g, device=device)
         b, sb = ops.quantize_fp8(b32)
