@@ -347,7 +347,7 @@ def fused_matmul(
 
     float32 operands of a large product (at least 2^24 multiply-adds) run on the tensor
     cores by the 3xTF32 split, whose partial sums are promoted to round-to-nearest fp32
-    every 256 products so that the result stays inside the op's 1e-5 gate; smaller ones,
+    every 192 products so that the result stays inside the op's 1e-5 gate; smaller ones,
     and everything with ``use_tensor_cores=False`` or ``fp32_tensor_cores=False``, run on
     the exact FFMA kernel.  ``fp32_tensor_cores=True`` forces the tensor cores.
 

@@ -832,3 +832,50 @@ def test_launch_trace(ops, binding):
     assert (lead[:, 8] > lead[:, 3]).all() and (lead[:, 9] > lead[:, 8]).all()            # first k-block, last MMA issued
     assert (t[:ctas, 10] > t[:ctas, 3]).all() and (t[:ctas, 11] > t[:ctas, 10]).all()     # accumulator ready, last store
     assert (t[:ctas, 5] >= t[:ctas, 11]).all()
+
+
+# ----- seeded sweep over random shapes and argument combinations -----
+_SWEEP_DIMS = [1, 2, 7, 8, 16, 24, 33, 64, 72, 100, 128, 136, 200, 256, 264, 384, 520, 640]
+_SWEEP_DIMS_LARGE = [64, 128, 520, 776, 1024, 1160, 2048, 2312]          # pair tiles, ragged edges, few-tile shapes
+_SWEEP_K_LARGE = [264, 1024, 2048, 4096, 8192]                           # long enough for split-K and the fp32 split
+
+
+def _sweep_case(seed, large=False):
+    rng = np.random.default_rng((9500 if large else 9000) + seed)
+    pick = lambda xs: xs[int(rng.integers(len(xs)))]
+    din = pick(["float32", "float16", "bfloat16", "bfloat16", "fp8_e4m3"])
+    dims = _SWEEP_DIMS_LARGE if large else _SWEEP_DIMS
+    M, N, K = pick(dims), pick(dims), pick(_SWEEP_K_LARGE if large else dims)
+    if din == "fp8_e4m3":
+        K = max(16, K - K % 16)                  # FP8 operands: K a multiple of 16 (the ABI's rule)
+    case = dict(din=din, M=M, N=N, K=K, batch=pick([1, 1, 1, 2] if large else [1, 1, 1, 3]), ta=bool(rng.integers(2)), tb=bool(rng.integers(2)),
+                act=int(rng.integers(-1, 10)), alpha=pick([1.0, 1.0, 0.5, -1.25]), beta=pick([0.0, 0.0, 0.75]),
+                bias=pick([None, None, "float32", "float16", "bfloat16"]),
+                dout=pick(["float32", "float16", "bfloat16"]) if din == "fp8_e4m3" or rng.integers(3) == 0 else din,
+                tc=pick([None, None, None, False]))
+    return rng, case
+
+
+@pytest.mark.parametrize("large,seed", [(False, s) for s in range(48)] + [(True, s) for s in range(20)])
+def test_seeded_sweep_matches_oracle(ops, large, seed):
+    """Shapes from 1 to 640 with ragged and unaligned sizes (and, in the large class, up to 2312 x 2312 x 8192), every
+    operand layout, bias, activation, alpha / beta and output type drawn together from one seeded stream, each against
+    the float64 oracle at the looser of the input and output types' gates."""
+    rng, c = _sweep_case(seed, large)
+    a, b, sa, sb = U.random_operands(rng, c["M"], c["N"], c["K"], c["batch"], c["ta"], c["tb"], c["din"], scale=0.3)
+    lead = (c["batch"],) if c["batch"] > 1 else ()
+    bias = None if c["bias"] is None else ref.quantize(rng.standard_normal((c["N"],), dtype=np.float32), c["bias"])
+    c_in = None
+    if c["beta"] != 0.0:
+        c_in = ref.quantize(rng.standard_normal(lead + (c["M"], c["N"]), dtype=np.float32), c["dout"])
+    fp8 = c["din"] == "fp8_e4m3"
+    got = run(ops, a, b, ta=c["ta"], tb=c["tb"], bias=bias, act=c["act"], alpha=c["alpha"], beta=c["beta"], c_in=c_in,
+              out_dtype=c["dout"], sa=sa if fp8 else None, sb=sb if fp8 else None, use_tensor_cores=c["tc"])
+    want = ref.matmul_oracle(a, b, transpose_a=c["ta"], transpose_b=c["tb"], alpha=c["alpha"], beta=c["beta"], c_in=c_in,
+                             bias=bias, act=c["act"], out_dtype=c["dout"], scale_a=sa, scale_b=sb)
+    assert got.shape == want.shape, c
+    gate = "float16" if (c["din"] == "float32") != (c["dout"] == "float32") and not fp8 else c["din"]
+    if np.linalg.norm(np.asarray(want).astype(np.float64)) == 0.0:
+        assert not np.asarray(got).astype(np.float32).any(), c
+    else:
+        check(got, want, gate, str(c))
