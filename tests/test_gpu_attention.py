@@ -240,3 +240,34 @@ def test_attention_full_size_attention_score_shape(ops, binding):
     # the unfused route (GEMM, softmax, GEMM) agrees with the fused kernel
     two = ops.scaled_dot_product_attention(q[:4], k[:4], v[:4], attention_mask=torch.zeros(s, s, device="cuda"))
     assert ref.rel_frobenius(U.to_numpy(two), U.to_numpy(out[:4]).astype(np.float64)) <= ref.TOLERANCE["bfloat16"]
+
+
+_ATT_SWEEP_LENS = [1, 5, 64, 127, 128, 129, 200, 256, 383, 512, 700, 1024, 1300]
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_fused_attention_seeded_sweep(ops, binding, seed):
+    """Batch shape, query and key counts (ragged, shorter and longer than one tile, more queries than keys), head size,
+    type, scale, score spread and the causal switch drawn together from one seeded stream.  Causal attention with
+    more queries than keys is an argument error; the case then runs without the causal switch."""
+    rng = np.random.default_rng(7000 + seed)
+    pick = lambda xs: xs[int(rng.integers(len(xs)))]
+    dtype, d = pick(["bfloat16", "float16"]), pick([64, 128])
+    lead = pick([(1,), (3,), (2, 2), (1, 5)])
+    sq, sk = pick(_ATT_SWEEP_LENS), pick(_ATT_SWEEP_LENS)
+    causal = bool(rng.integers(2))
+    scale = pick([None, None, 0.05, 0.2, -0.1])
+    q, k, v = _qkv(rng, lead, sq, sk, d, dtype, spread=pick([0.5, 1.0, 2.0]))
+    what = (dtype, d, lead, sq, sk, causal, scale)
+    if causal and sq > sk:                     # queries with no key to look at: rejected, not computed
+        with pytest.raises(ops.InvalidArgumentError):
+            ops.scaled_dot_product_attention(U.to_cuda(q), U.to_cuda(k), U.to_cuda(v), scale=scale, causal_mask=True)
+        causal = False
+    got = ops.scaled_dot_product_attention(U.to_cuda(q), U.to_cuda(k), U.to_cuda(v), scale=scale, causal_mask=causal)
+    torch.cuda.synchronize()
+    assert binding.last_kernel_name() == f"attention_tcgen05_d{d}", what
+    want = ref.attention_oracle(q, k, v, scale=scale, causal=causal)
+    g = U.to_numpy(got)
+    assert g.shape == want.shape and np.isfinite(g.astype(np.float32)).all(), what
+    err = ref.rel_frobenius(g, want)
+    assert err <= ref.TOLERANCE[dtype], what + (err,)
