@@ -250,16 +250,9 @@ struct AttCfg {
     static constexpr size_t SMEM_USED = TILE_BYTES + BAR_BYTES + 1024;
     // every CTA allocates all 512 TMEM columns, so two CTAs must never share an SM: request more than half of its shared memory
     static constexpr size_t SMEM = SMEM_USED > 118784 ? SMEM_USED : 118784;
-    // S_0 at column 0, S_1 at 128, O_0 at 256, O_1 at 256 + D.  P_j (64 cells): at D = 128 the last 64 columns of S_j,
-    // because nothing else is free; at D = 64 a place of its own behind the accumulators, and then S_{j+2} may be
-    // computed as soon as the softmax threads have READ S_j, while they are still busy with it (EARLY_QK)
+    // S_0 at column 0, S_1 at 128 (P_j: the last 64 columns of S_j), O_0 at 256, O_1 at 256 + D
     static constexpr uint32_t TMEM_COLS = 512;
     static constexpr uint32_t TMEM_O = 2 * ATT_BN;
-    static constexpr bool EARLY_QK = D == 64;
-    __host__ __device__ static constexpr uint32_t p_col(uint32_t g) {
-        return EARLY_QK ? 2 * ATT_BN + 2 * D + g * (ATT_BN / 2) : g * ATT_BN + ATT_BN / 2;
-    }
-    static_assert(!EARLY_QK || 2 * ATT_BN + 2 * D + ATT_BN <= TMEM_COLS, "no room for P beside S");
     static_assert(SMEM <= 232448, "shared memory budget exceeded");
 };
 
@@ -289,8 +282,6 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t p_hi = smem_u32(bars + 19);       // [2]  keys 64-127 of P_j are in TMEM
     const uint32_t o_done = smem_u32(bars + 15);     // [2]  the group's last product is complete
     const uint32_t drain_bar = smem_u32(bars + 17);
-    const uint32_t s_read = smem_u32(bars + 24);     // [2]  EARLY_QK: the group's four warps hold S_j in registers
-    const uint32_t o_step = smem_u32(bars + 26);     // [2]  EARLY_QK: P_j V_j is complete (every tile but the group's last)
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22);
     volatile uint32_t* abort_flag = tmem_holder + 1;
     volatile float* xchg = reinterpret_cast<volatile float*>(reinterpret_cast<uint8_t*>(bars) + 256);      // [2][2][ATT_BM]
@@ -328,8 +319,6 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             mbar_init(p_lo + 8 * b, 4);              // one arrival per warp of the group
             mbar_init(p_hi + 8 * b, 4);
             mbar_init(o_done + 8 * b, 1);
-            mbar_init(s_read + 8 * b, 4);
-            mbar_init(o_step + 8 * b, 1);
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0u;
@@ -387,10 +376,6 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         };
         // the scores run two tiles ahead of the P V products: K_0 and K_1 first (above), then V_j and K_{j+2}
         for (int j = 0; ok && j < n_kv; ++j) {
-            if constexpr (Cfg::EARLY_QK) {                      // K_{j+2} is wanted before V_j there
-                if (j + 2 < n_kv) ok = load_k(j + 2);
-                if (!ok) break;
-            }
             const uint32_t st = j % ATT_V_STAGES, ph = (j / ATT_V_STAGES) & 1;
             bool w = att_wait(v_empty + 8 * st, ph ^ 1u, wctx, 0x42000000u);
             w = __all_sync(0xFFFFFFFFu, w);
@@ -406,9 +391,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             __syncwarp();
             ++issued_v;
-            if constexpr (!Cfg::EARLY_QK) {
-                if (j + 2 < n_kv) ok = load_k(j + 2);
-            }
+            if (j + 2 < n_kv) ok = load_k(j + 2);
         }
         // before leaving: every copy issued must have landed (immediate unless the CTA is aborting)
         if (n_kv > 0) att_wait(q_full, 0u, wctx, 0x43000000u, false);
@@ -433,7 +416,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         // S_j = Q K_j^T into S buffer j % 2.  The buffer is free: its last reader was P_{j-2} V_{j-2} (P_{j-2} lies in it),
         // issued by this thread before this product, and the softmax threads had read S_{j-2} before they wrote
-        // P_{j-2}.  With EARLY_QK the buffer holds scores only, and the caller has waited for s_read.
+        // P_{j-2}.
         // (One elected thread; the caller has waited for K_j.)
         auto qk_mmas = [&](int j) {
             const uint32_t st = j % ATT_K_STAGES, g = j & 1;
@@ -451,7 +434,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // O_g += P_j[:, 16 t0 .. 16 t1) V_j[16 t0 .. 16 t1, :]   (one elected thread)
         auto pv_mmas = [&](int j, int t0, int t1) {
             const uint32_t g = j & 1, st = j % ATT_V_STAGES;
-            const uint32_t p_tmem = tmem_base + Cfg::p_col(g);
+            const uint32_t p_tmem = tmem_base + g * ATT_BN + ATT_BN / 2;      // P_j: the upper 64 cells of S buffer g
             const uint32_t o_tmem = tmem_base + Cfg::TMEM_O + g * D;
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
@@ -463,7 +446,6 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (t1 == 8) {
                 umma_commit<1>(v_empty + 8 * st);
                 if (j + 2 >= n_kv) umma_commit<1>(o_done + 8 * g);
-                else if constexpr (Cfg::EARLY_QK) umma_commit<1>(o_step + 8 * g);
             }
         };
         auto k_bar = [&](int j) { return k_full + 8 * (j % ATT_K_STAGES); };
@@ -484,43 +466,22 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const uint32_t g = j & 1, bph = (j >> 1) & 1;
             const uint32_t vst = j % ATT_V_STAGES, vph = (j / ATT_V_STAGES) & 1;
             const bool more = j + 2 < n_kv;
-            bool w;
-            if constexpr (Cfg::EARLY_QK) {
-                // the next scores of this group as soon as S_j has left its buffer: they are ready long before the
-                // group has finished tile j, so neither product is on the group's path from tile to tile
-                if (more) {
-                    w = att_wait2(s_read + 8 * g, bph, k_bar(j + 2), k_par(j + 2), wctx, 0x58000000u, 0x52000000u);
-                    ok = __all_sync(0xFFFFFFFFu, w);
-                    if (!ok) break;
-                    tcgen05_fence_after();
-                    if (elect_one_sync()) qk_mmas(j + 2);
-                    __syncwarp();
-                }
-                // P_j complete (its first half with it: the same warps arrive on p_lo first)
-                w = att_wait2(v_full + 8 * vst, vph, p_hi + 8 * g, bph, wctx, 0x54000000u, 0x55000000u);
-                ok = __all_sync(0xFFFFFFFFu, w);
-                if (!ok) break;
-                tcgen05_fence_after();
-                if (elect_one_sync()) pv_mmas(j, 0, 8);
-                __syncwarp();
-            } else {
-                w = att_wait2(v_full + 8 * vst, vph, p_lo + 8 * g, bph, wctx, 0x54000000u, 0x55000000u);   // keys 0-63 of P_j are in TMEM
-                ok = __all_sync(0xFFFFFFFFu, w);
-                if (!ok) break;
-                tcgen05_fence_after();
-                if (elect_one_sync()) pv_mmas(j, 0, 4);
-                __syncwarp();
-                if (more) w = att_wait2(p_hi + 8 * g, bph, k_bar(j + 2), k_par(j + 2), wctx, 0x55000000u, 0x52000000u);
-                else w = att_wait(p_hi + 8 * g, bph, wctx, 0x55000000u);
-                ok = __all_sync(0xFFFFFFFFu, w);
-                if (!ok) break;
-                tcgen05_fence_after();
-                if (elect_one_sync()) {
-                    pv_mmas(j, 4, 8);
-                    if (more) qk_mmas(j + 2);
-                }
-                __syncwarp();
+            bool w = att_wait2(v_full + 8 * vst, vph, p_lo + 8 * g, bph, wctx, 0x54000000u, 0x55000000u);   // keys 0-63 of P_j are in TMEM
+            ok = __all_sync(0xFFFFFFFFu, w);
+            if (!ok) break;
+            tcgen05_fence_after();
+            if (elect_one_sync()) pv_mmas(j, 0, 4);
+            __syncwarp();
+            if (more) w = att_wait2(p_hi + 8 * g, bph, k_bar(j + 2), k_par(j + 2), wctx, 0x55000000u, 0x52000000u);
+            else w = att_wait(p_hi + 8 * g, bph, wctx, 0x55000000u);
+            ok = __all_sync(0xFFFFFFFFu, w);
+            if (!ok) break;
+            tcgen05_fence_after();
+            if (elect_one_sync()) {
+                pv_mmas(j, 4, 8);
+                if (more) qk_mmas(j + 2);
             }
+            __syncwarp();
         }
         if (*abort_flag != 0u && issued_any) {
             if (elect_one_sync()) umma_commit<1>(drain_bar);
@@ -536,8 +497,7 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int q = q0 + row;
         const int key_limit = p.causal ? min(p.seq_k, q + p.seq_k - p.seq_q + 1) : p.seq_k;   // keys [0, key_limit) count
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
-        const uint32_t t_s = t_lane + g * ATT_BN;              // S_j
-        const uint32_t t_p = t_lane + Cfg::p_col(g);           // P_j
+        const uint32_t t_s = t_lane + g * ATT_BN;              // S_j, and P_j in its last 64 cells
         const uint32_t t_o = t_lane + Cfg::TMEM_O + g * D;
         const bool bf16 = p.out_bf16 != 0;
         const float scale_log2 = p.scale_log2;
@@ -556,11 +516,6 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             for (int c = 0; c < ATT_BN / 32; ++c) tmem_ld_32x32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
 #pragma unroll
             for (int c = 0; c < ATT_BN / 32; ++c) tmem_ld_wait_regs(*reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-            if constexpr (Cfg::EARLY_QK) {
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_read + 8 * g);     // the S buffer may take S_{j+2}
-            }
             const bool edge = key0 + ATT_BN > key_limit;        // some of the tile's keys do not count for this row
             // (the per-key tests exist only in the branch for tiles that straddle this row's key limit)
             float m_tile;
@@ -599,13 +554,6 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 // here: its last product (tile j - 2) was issued before S_j, which is complete.
                 const bool moves = m_tile > m_ref + ATT_RESCALE_STEP;
                 if (__any_sync(0xFFFFFFFFu, moves)) {
-                    if constexpr (Cfg::EARLY_QK) {
-                        // S_j was issued BEFORE P_{j-2} V_{j-2} there: wait for that product itself
-                        ok = att_wait(o_step + 8 * g, ((j >> 1) - 1) & 1, wctx, 0x66000000u);
-                        ok = __all_sync(0xFFFFFFFFu, ok);
-                        if (!ok) break;
-                        tcgen05_fence_after();
-                    }
                     const float alpha = moves ? att_exp2(m_ref - m_tile) : 1.0f;     // 0 when the row had no key so far
 #pragma unroll
                     for (int c = 0; c < D / 16; ++c) {
@@ -632,23 +580,12 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const uint32_t(&sc)[64] = *reinterpret_cast<const uint32_t(*)[64]>(&s[c * 64]);
                 if (edge) att_exp_pack<64, true>(sc, packed, scale2, neg_m2, l2, key0 + c * 64, key_limit, bf16);
                 else att_exp_pack<64, false>(sc, packed, scale2, neg_m2, l2, key0 + c * 64, key_limit, bf16);
-                if constexpr (Cfg::EARLY_QK) {
-                    // P_j goes where P_{j-2} was: its product must have finished reading (it was issued a tile ago;
-                    // the same phase as in the rescale branch above, so waiting twice is harmless)
-                    if (c == 0 && j >= 2) {
-                        ok = att_wait(o_step + 8 * g, ((j >> 1) - 1) & 1, wctx, 0x66000000u);
-                        ok = __all_sync(0xFFFFFFFFu, ok);
-                        if (!ok) break;
-                        tcgen05_fence_after();
-                    }
-                }
-                tmem_st_32x32(t_p + c * 32, packed);
+                tmem_st_32x32(t_s + ATT_BN / 2 + c * 32, packed);
                 tmem_st_wait();
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive((c == 0 ? p_lo : p_hi) + 8 * g);
             }
-            if (!ok) break;
             float l_a, l_b;
             f32x2_split(l2, l_a, l_b);
             l_run += l_a + l_b;
