@@ -199,6 +199,18 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     return d;
 }
 
+// the three-input maximum / minimum of sm_100: half the instructions and half the chain length of a row's search
+__device__ __forceinline__ float att_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float att_min3(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // p = exp2(s * scale_log2 - m) for KEYS of this thread's keys, packed as KEYS / 2 pairs of 16-bit values (the even key
 // in the low half: the K-major A operand of P V); adds the exponentials to the pair of partial row sums l2.  EDGE: keys
 // at or beyond key_limit count as 0 (only tiles that straddle the row's limit pay for the per-key tests).  The sum
@@ -520,25 +532,30 @@ sm120_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // (the per-key tests exist only in the branch for tiles that straddle this row's key limit)
             float m_tile;
             if (!edge) {
-                // four chains; with a negative scale the largest scaled score belongs to the smallest raw score
+                // four chains of three-input maxima; with a negative scale the largest scaled score belongs to the
+                // smallest raw score
                 float e0 = __uint_as_float(s[0]), e1 = __uint_as_float(s[1]), e2 = __uint_as_float(s[2]), e3 = __uint_as_float(s[3]);
                 if (scale_log2 >= 0.0f) {
 #pragma unroll
-                    for (int i = 4; i < ATT_BN; i += 4) {
-                        e0 = fmaxf(e0, __uint_as_float(s[i]));
-                        e1 = fmaxf(e1, __uint_as_float(s[i + 1]));
-                        e2 = fmaxf(e2, __uint_as_float(s[i + 2]));
-                        e3 = fmaxf(e3, __uint_as_float(s[i + 3]));
+                    for (int i = 4; i + 8 <= ATT_BN; i += 8) {
+                        e0 = att_max3(e0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                        e1 = att_max3(e1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                        e2 = att_max3(e2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                        e3 = att_max3(e3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
                     }
+                    e0 = att_max3(e0, __uint_as_float(s[ATT_BN - 4]), __uint_as_float(s[ATT_BN - 3]));
+                    e1 = att_max3(e1, __uint_as_float(s[ATT_BN - 2]), __uint_as_float(s[ATT_BN - 1]));
                     m_tile = fmaxf(fmaxf(e0, e1), fmaxf(e2, e3)) * scale_log2;
                 } else {
 #pragma unroll
-                    for (int i = 4; i < ATT_BN; i += 4) {
-                        e0 = fminf(e0, __uint_as_float(s[i]));
-                        e1 = fminf(e1, __uint_as_float(s[i + 1]));
-                        e2 = fminf(e2, __uint_as_float(s[i + 2]));
-                        e3 = fminf(e3, __uint_as_float(s[i + 3]));
+                    for (int i = 4; i + 8 <= ATT_BN; i += 8) {
+                        e0 = att_min3(e0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                        e1 = att_min3(e1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                        e2 = att_min3(e2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                        e3 = att_min3(e3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
                     }
+                    e0 = att_min3(e0, __uint_as_float(s[ATT_BN - 4]), __uint_as_float(s[ATT_BN - 3]));
+                    e1 = att_min3(e1, __uint_as_float(s[ATT_BN - 2]), __uint_as_float(s[ATT_BN - 1]));
                     m_tile = fminf(fminf(e0, e1), fminf(e2, e3)) * scale_log2;
                 }
             } else {
