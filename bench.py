@@ -78,7 +78,7 @@ NCU_TRAFFIC_BYTES = {
     "bf16_dense_gelu": 517800000,   # profiles/gemm_tcgen05_bf16_dense_gelu_8192x11008x4096.txt: 351.7 MB read + 166.1 MB written
     "bf16_batched_qk": 547412224,   # profiles/gemm_tcgen05_bf16_batched_qk_96x1024x1024x128.txt: 67.2 MB read + 480.2 MB written
     "fp8_8192": 402100000,          # profiles/gemm_tcgen05_fp8_8192x8192x8192.txt: 284.4 MB read + 117.7 MB written
-    "attention_64x2048x128": 115696896,   # profiles/attention_tcgen05_64x2048x128_bf16.txt: 100.8 MB read + 14.9 MB written
+    "attention_64x2048x128": 115489280,   # profiles/attention_tcgen05_64x2048x128_bf16.txt: 100.7 MB read + 14.7 MB written
 }
 
 
