@@ -180,3 +180,49 @@ def test_cast_fp8_with_given_scale_and_non_finite_input(ops, binding):
     assert float(s) == 112.0
     qf = q.float()
     assert float(qf[0]) == 112.0 and float(qf[2]) == -448.0 and bool(torch.isnan(qf[1]))
+
+
+_SWEEP_ROWS = [1, 3, 17, 64, 129, 500, 1024, 3000]
+_SWEEP_COLS = [1, 2, 7, 8, 33, 64, 200, 264, 1000, 1032, 4100]
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_companion_kernels_seeded_sweep(ops, binding, seed):
+    """One of the HBM-bound companions (activation with and without bias, bias gradient, softmax along a random axis,
+    FP8 quantiser) on a shape, type and argument set drawn from a seeded stream, against the float64 oracle."""
+    rng = np.random.default_rng(8000 + seed)
+    pick = lambda xs: xs[int(rng.integers(len(xs)))]
+    op = pick(["activation", "bias_activation", "bias_grad", "softmax", "quantize"])
+    dtype = pick(["float32", "float16", "bfloat16"])
+    rows, cols = pick(_SWEEP_ROWS), pick(_SWEEP_COLS)
+    x = ref.quantize(2.0 * rng.standard_normal((rows, cols), dtype=np.float32), dtype)
+    tx = U.to_cuda(x)
+    what = (op, dtype, rows, cols)
+    if op in ("activation", "bias_activation"):
+        code = int(rng.integers(0, 10))
+        bias = None
+        if op == "bias_activation":
+            bias = ref.quantize(rng.standard_normal(cols, dtype=np.float32), pick([dtype, "float32"]))
+        got = ops.fused_activation(tx, code, bias=None if bias is None else U.to_cuda(bias))
+        want = _act_oracle(x, code, dtype, bias=bias)
+        err = np.max(np.abs(U.to_numpy(got).astype(np.float64) - want) / (1.0 + np.abs(want)))
+        assert got.shape == tx.shape and err <= TOL_ABS[dtype], what + (code, err)
+    elif op == "bias_grad":
+        got = ops.bias_grad(tx, out_dtype=torch.float32)
+        want = x.astype(np.float64).sum(axis=0)
+        assert np.max(np.abs(got.cpu().numpy() - want)) <= 4e-6 * (rows + np.sqrt(rows)), what
+    elif op == "softmax":
+        t3 = tx.reshape(rows, cols, 1).expand(rows, cols, 3).contiguous() if cols <= 264 else tx
+        axis = int(rng.integers(0, t3.dim()))
+        got = ops.softmax(t3, axis=axis)
+        want = ref.softmax_oracle(U.to_numpy(t3), axis=axis)
+        tol = {"float32": 2e-6, "float16": 6e-4, "bfloat16": 5e-3}[dtype]
+        assert np.max(np.abs(U.to_numpy(got).astype(np.float64) - want)) <= tol, what + (axis,)
+    else:
+        q, s = ops.quantize_fp8(tx)
+        x32 = x.astype(np.float32)
+        want_s = np.float32(ref.fp8_scale(x32))
+        assert abs(float(s) - float(want_s)) <= 1.2e-7 * float(want_s), what
+        want_q = ref.quantize(x32 * np.float32(float(s)), "fp8_e4m3")          # the device's own scale: bytes must match
+        assert np.array_equal(U.to_numpy(q).view(np.uint8), want_q.view(np.uint8)), what
+    torch.cuda.synchronize()
