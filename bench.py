@@ -27,7 +27,7 @@ Other workloads (`--workload`): f32_1024, f16_4096_tn, bf16_4096_tn,
 bf16_dense_gelu, bf16_batched_qk, fp8_65536 (M split over the ranks), fp8_8192,
 f32_1024_ffma, f32_4096, f32_4096_ffma, bf16_1024x1024x8192 (split along K), and the HBM-bound kernels quant_fp8_64m,
 activation_gelu_64m, bias_grad_8192x11008, softmax_131072x2048 and the fused attention
-attention_64x2048x128 (batch x heads = 64, sequence 2048, head 128, bf16).  `--trace FILE` also writes the
+attention_<batch x heads>x<sequence>x<head size>[_causal] (bf16; the listed shapes, default 64x2048x128).  `--trace FILE` also writes the
 launch timeline (SM120_TUNE_TRACE) of one launch of the workload to FILE.
 """
 import argparse
@@ -64,7 +64,10 @@ WORKLOADS = {
     "f32_4096_ffma":   dict(M=4096, N=4096, K=4096, batch=1, dtype="f32", layout="nn", ffma=True, oracle_idx=1),
     "bf16_1024x1024x8192": dict(M=1024, N=1024, K=8192, batch=1, dtype="bf16", layout="tn", oracle_idx=2),   # few tiles, long K: split-K
 }
-AUX_WORKLOADS = ("quant_fp8_64m", "activation_gelu_64m", "bias_grad_8192x11008", "softmax_131072x2048", "attention_64x2048x128")
+# attention_<batch x heads>x<sequence>x<head size>[_causal], bf16
+ATTENTION_WORKLOADS = ("attention_64x2048x128", "attention_64x2048x128_causal", "attention_16x8192x128", "attention_16x8192x128_causal",
+                       "attention_8x16384x128_causal", "attention_256x512x128", "attention_128x2048x64", "attention_16x16384x64")
+AUX_WORKLOADS = ("quant_fp8_64m", "activation_gelu_64m", "bias_grad_8192x11008", "softmax_131072x2048") + ATTENTION_WORKLOADS
 ALIASES = {"cfg1": "f32_1024", "cfg2": "f16_4096_tn", "cfg2bf16": "bf16_4096_tn", "cfg3": "bf16_dense_gelu",
            "cfg4": "bf16_batched_qk", "cfg5": "fp8_65536"}
 IN_BYTES = {"f32": 4, "f16": 2, "bf16": 2, "f8e4m3": 1}
@@ -646,7 +649,7 @@ def run_aux(args, torch, pkg, device, peaks, peak_kind):
 
         def step(i):
             ops.softmax(xs[i % 2], out=outs[i % 2])
-    elif args.workload == "attention_64x2048x128":
+    elif args.workload in ATTENTION_WORKLOADS:
         return run_attention(args, torch, pkg, device, peaks, peak_kind)
     else:
         xs = [torch.randn(8192, 11008, device=device).bfloat16() for _ in range(3)]
@@ -678,13 +681,16 @@ def run_aux(args, torch, pkg, device, peaks, peak_kind):
 
 
 def run_attention(args, torch, pkg, device, peaks, peak_kind):
-    """Fused attention forward on the attention-score benchmark shape: batch x heads = 64, sequence 2048, head 128,
-    bf16.  4 S^2 D FLOPs per batch entry; beside it the same result as GEMM + softmax + GEMM (scores through HBM)."""
+    """Fused attention forward, bf16; the default shape is the attention-score benchmark's (batch x heads = 64, sequence
+    2048, head 128).  4 S^2 D FLOPs per batch entry (half of that with the causal mask); beside it the same result as
+    GEMM + softmax + GEMM on this library (scores through HBM; sequences up to 4096) and the framework's own attention
+    (torch.nn.functional.scaled_dot_product_attention, a yardstick only)."""
     ops, binding = pkg.sm120_ops, pkg._binding
-    bh, s, d = 64, 2048, 128
+    dims = args.workload.split("_")[1].split("x")
+    bh, s, d = int(dims[0]), int(dims[1]), int(dims[2])
+    causal = args.workload.endswith("_causal")
     sets = [tuple(torch.randn(bh, s, d, device=device).bfloat16() for _ in range(3)) for _ in range(3)]
-    flops = 4.0 * s * s * d * bh
-    zero_mask = torch.zeros(s, s, device=device)
+    flops = 4.0 * s * s * d * bh * (0.5 if causal else 1.0)
 
     def timed(fn, steps, warmup):
         for i in range(warmup):
@@ -699,23 +705,35 @@ def run_attention(args, torch, pkg, device, peaks, peak_kind):
         return e0.elapsed_time(e1) * 1e-3 / steps
 
     launches0 = binding.launch_count()
-    secs = timed(lambda q, k, v: ops.scaled_dot_product_attention(q, k, v), args.steps, args.warmup)
+    secs = timed(lambda q, k, v: ops.scaled_dot_product_attention(q, k, v, causal_mask=causal), args.steps, args.warmup)
     launches = (binding.launch_count() - launches0) * args.steps // (args.steps + args.warmup)
     kernel = binding.last_kernel_name()
-    unfused = timed(lambda q, k, v: ops.scaled_dot_product_attention(q, k, v, attention_mask=zero_mask), max(3, args.steps // 5), 2)
+    unfused = None
+    if s <= 4096 and not args.lean:
+        zero_mask = torch.zeros(s, s, device=device)        # an explicit mask takes the unfused route
+        unfused = timed(lambda q, k, v: ops.scaled_dot_product_attention(q, k, v, attention_mask=zero_mask, causal_mask=causal),
+                        max(3, args.steps // 5), 2)
+    library = None
+    if not args.lean:
+        try:
+            sdpa = torch.nn.functional.scaled_dot_product_attention
+            library = timed(lambda q, k, v: sdpa(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), is_causal=causal), args.steps, args.warmup)
+        except Exception:                                    # a yardstick only: absent or unsupported is not an error
+            library = None
     peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
     tf = flops / secs / 1e12
     line = {"metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": args.workload, "batch_x_heads": bh, "seq": s, "head_dim": d,
+            "config": {"workload": args.workload, "batch_x_heads": bh, "seq": s, "head_dim": d, "causal": causal,
                        "what": "softmax(Q K^T / sqrt(d)) V in one kernel", "l2": "three sets of Q, K, V rotate"},
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "kernel": kernel, "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": 4 * bh * s * d * 2,
                          "peak_source": f"{peak_kind}: bf16_tflops (cuBLAS bf16 8192^3 burst)"},
             "pct_of_nominal_dense_peak": 100.0 * tf / NOMINAL_PEAK["bf16"],
-            "unfused_gemm_softmax_gemm": {"ms_per_step": unfused * 1e3, "tflops": flops / unfused / 1e12,
-                                          "hbm_bytes_of_scores": bh * s * s * (4 + 4 + 2 + 2)},
+            "unfused_gemm_softmax_gemm": None if unfused is None else {"ms_per_step": unfused * 1e3, "tflops": flops / unfused / 1e12,
+                                                                       "hbm_bytes_of_scores": bh * s * s * (4 + 4 + 2 + 2)},
+            "torch_sdpa_same_process": None if library is None else {"ms_per_step": library * 1e3, "tflops": flops / library / 1e12},
             "gpu_launches": int(launches)}
     print(json.dumps(line), flush=True)
 
