@@ -33,22 +33,43 @@
 namespace sm120 {
 
 // One operand's split: `rows` is M (for A) or N (for B); element (r, k) of op(X) is X[r*ld + k] when k is
-// contiguous in memory and X[k*ld + r] otherwise.
+// contiguous in memory and X[k*ld + r] otherwise.  `vec`: base, pitch and batch stride are multiples of 16 bytes and
+// the contiguous extent is a multiple of 4 elements, so the operand can be read in 16-byte pieces.
 struct SplitJob {
     const float* X;
     float* X2;
     long long rows, ld, stride_x;
-    int k_contiguous;
+    int k_contiguous, vec;
     unsigned row_tiles, batches;
 };
 
-// One 32 x 32 tile of op(X) per block, 32 x 8 threads; both operands in ONE launch (grid z: A's batch entries, then
-// B's), because at the sizes where fp32 products are small the launches cost as much as the work.
+constexpr int SPLIT_TILE = 64;           // rows and K elements of op(X) per block
+
+__device__ __forceinline__ void split_hi_lo(float v, float& hi, float& lo) {
+    hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    lo = __uint_as_float(__float_as_uint(v - hi) & 0xFFFFE000u);
+}
+
+__device__ __forceinline__ void split_store4(float* row, long long k, long long Kp, const float4 v) {
+    float4 hi, lo;
+    split_hi_lo(v.x, hi.x, lo.x);
+    split_hi_lo(v.y, hi.y, lo.y);
+    split_hi_lo(v.z, hi.z, lo.z);
+    split_hi_lo(v.w, hi.w, lo.w);
+    *reinterpret_cast<float4*>(row + k) = hi;
+    *reinterpret_cast<float4*>(row + Kp + k) = lo;
+}
+
+// One 64 x 64 tile of op(X) per block of 256 threads; both operands in ONE launch (grid z: A's batch entries, then
+// B's), because at the sizes where fp32 products are small the launches cost as much as the work.  The pass is
+// HBM-bound (4 bytes read, 8 written per element): aligned operands move in 16-byte pieces, 256 contiguous bytes per
+// row and 16 threads, directly when K is the contiguous dimension and through a shared-memory transpose when it is
+// not; anything else takes the element-wise path.
 __global__ void __launch_bounds__(256)
 sm120_split_tf32_kernel(const SplitJob ja, const SplitJob jb, long long K, long long Kp) {
     // the GEMM that consumes the split operands may start its set-up now; it waits for this grid before it reads
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    __shared__ float tile[32][33];
+    __shared__ float tile[SPLIT_TILE][SPLIT_TILE + 1];
     const bool is_a = blockIdx.z < ja.batches;
     const SplitJob& job = is_a ? ja : jb;
     if (blockIdx.y >= job.row_tiles) return;
@@ -57,36 +78,91 @@ sm120_split_tf32_kernel(const SplitJob ja, const SplitJob jb, long long K, long 
     const int k_contiguous = job.k_contiguous;
     const float* x = job.X + bz * job.stride_x;
     float* x2 = job.X2 + bz * rows * 2 * Kp;
-    const long long r0 = static_cast<long long>(blockIdx.y) * 32;
-    const long long k0 = static_cast<long long>(blockIdx.x) * 32;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    // load op(X)[r0 + .., k0 + ..] into tile[r][k], walking the contiguous dimension with tx
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int j = ty + 8 * i;
-        float v = 0.0f;
+    const long long r0 = static_cast<long long>(blockIdx.y) * SPLIT_TILE;
+    const long long k0 = static_cast<long long>(blockIdx.x) * SPLIT_TILE;
+    if (job.vec) {
+        const int l16 = threadIdx.x & 15, sub = threadIdx.x >> 4;     // 16 threads x 16 bytes per row piece, 16 pieces per step
         if (k_contiguous) {
-            const long long r = r0 + j, k = k0 + tx;
-            if (r < rows && k < K) v = x[r * ld + k];
-            tile[j][tx] = v;
-        } else {
-            const long long k = k0 + j, r = r0 + tx;
-            if (r < rows && k < K) v = x[k * ld + r];
-            tile[tx][j] = v;
-        }
-    }
-    __syncthreads();
+            const long long k = k0 + l16 * 4;                         // K % 4 == 0: a piece is inside K or outside
+            if (k >= Kp) return;
+            float4 v[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int j = ty + 8 * i;
-        const long long r = r0 + j, k = k0 + tx;         // k < Kp always: the grid covers Kp / 32 tiles
-        if (r >= rows) continue;
-        const float v = tile[j][tx];
-        const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-        const float lo = __uint_as_float(__float_as_uint(v - hi) & 0xFFFFE000u);
-        float* row = x2 + r * 2 * Kp;
-        row[k] = hi;
-        row[Kp + k] = lo;
+            for (int i = 0; i < 4; ++i) {
+                const long long r = r0 + sub + 16 * i;
+                v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (r < rows && k < K) v[i] = __ldcs(reinterpret_cast<const float4*>(x + r * ld + k));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const long long r = r0 + sub + 16 * i;
+                if (r < rows) split_store4(x2 + r * 2 * Kp, k, Kp, v[i]);
+            }
+            return;
+        }
+        // rows are the contiguous dimension (rows % 4 == 0): 16-byte pieces along r in, a transpose, 16-byte pieces along k out
+        {
+            const long long r = r0 + l16 * 4;
+            float4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const long long k = k0 + sub + 16 * i;
+                v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (k < K && r < rows) v[i] = __ldcs(reinterpret_cast<const float4*>(x + k * ld + r));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int kk = sub + 16 * i;
+                tile[kk][l16 * 4 + 0] = v[i].x;
+                tile[kk][l16 * 4 + 1] = v[i].y;
+                tile[kk][l16 * 4 + 2] = v[i].z;
+                tile[kk][l16 * 4 + 3] = v[i].w;
+            }
+        }
+        __syncthreads();
+        const long long k = k0 + l16 * 4;
+        if (k >= Kp) return;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rr = sub + 16 * i;
+            const long long r = r0 + rr;
+            if (r >= rows) continue;
+            const float4 v = make_float4(tile[l16 * 4 + 0][rr], tile[l16 * 4 + 1][rr], tile[l16 * 4 + 2][rr], tile[l16 * 4 + 3][rr]);
+            split_store4(x2 + r * 2 * Kp, k, Kp, v);
+        }
+        return;
+    }
+    // element-wise: four 32 x 32 sub-tiles, walking the contiguous dimension with tx
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll 1
+    for (int q = 0; q < 4; ++q) {
+        const long long rq = r0 + 32 * (q >> 1), kq = k0 + 32 * (q & 1);
+        if (q != 0) __syncthreads();                                  // the previous sub-tile has been read
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = ty + 8 * i;
+            float v = 0.0f;
+            if (k_contiguous) {
+                const long long r = rq + j, k = kq + tx;
+                if (r < rows && k < K) v = x[r * ld + k];
+                tile[j][tx] = v;
+            } else {
+                const long long k = kq + j, r = rq + tx;
+                if (r < rows && k < K) v = x[k * ld + r];
+                tile[tx][j] = v;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = ty + 8 * i;
+            const long long r = rq + j, k = kq + tx;
+            if (r >= rows || k >= Kp) continue;
+            float hi, lo;
+            split_hi_lo(tile[j][tx], hi, lo);
+            float* row = x2 + r * 2 * Kp;
+            row[k] = hi;
+            row[Kp + k] = lo;
+        }
     }
 }
 
@@ -118,11 +194,15 @@ cudaError_t tf32x3_launch(const GemmProblem& p, void* workspace, uint64_t wait_l
     const char* why = nullptr;
     if (!tc_supported(g, &why)) return cudaErrorInvalidValue;
     // A: op(A)[m,k]; k is contiguous unless A is stored transposed.  B: op(B)^T[n,k]; k is contiguous when B is stored [N,K].
-    const SplitJob ja{static_cast<const float*>(p.A), a2, p.M, p.lda, p.stride_a, p.transpose_a ? 0 : 1,
-                      static_cast<unsigned>((p.M + 31) / 32), static_cast<unsigned>(nb_a)};
-    const SplitJob jb{static_cast<const float*>(p.B), b2, p.N, p.ldb, p.stride_b, p.transpose_b ? 1 : 0,
-                      static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(nb_b)};
-    const dim3 grid(static_cast<unsigned>(kp / 32), ja.row_tiles > jb.row_tiles ? ja.row_tiles : jb.row_tiles,
+    const auto vec_ok = [&](const void* x, long long ld, long long stride, long long contiguous_extent) {
+        return (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && ld % 4 == 0 && stride % 4 == 0 && contiguous_extent % 4 == 0 ? 1 : 0;
+    };
+    const int ka = p.transpose_a ? 0 : 1, kb = p.transpose_b ? 1 : 0;
+    const SplitJob ja{static_cast<const float*>(p.A), a2, p.M, p.lda, p.stride_a, ka, vec_ok(p.A, p.lda, p.stride_a, ka ? p.K : p.M),
+                      static_cast<unsigned>((p.M + SPLIT_TILE - 1) / SPLIT_TILE), static_cast<unsigned>(nb_a)};
+    const SplitJob jb{static_cast<const float*>(p.B), b2, p.N, p.ldb, p.stride_b, kb, vec_ok(p.B, p.ldb, p.stride_b, kb ? p.K : p.N),
+                      static_cast<unsigned>((p.N + SPLIT_TILE - 1) / SPLIT_TILE), static_cast<unsigned>(nb_b)};
+    const dim3 grid(static_cast<unsigned>((kp + SPLIT_TILE - 1) / SPLIT_TILE), ja.row_tiles > jb.row_tiles ? ja.row_tiles : jb.row_tiles,
                     static_cast<unsigned>(nb_a + nb_b));
     sm120_split_tf32_kernel<<<grid, 256, 0, p.stream>>>(ja, jb, p.K, kp);
     cudaError_t e = cudaGetLastError();
