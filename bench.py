@@ -452,9 +452,22 @@ def host_overhead(torch, ops, binding, device):
 def cublas_yardstick(torch, spec, sets, kw, steps, warmup):
     """torch.matmul (cuBLAS) on the same buffers, same rotation, same events: TFLOP/s, or None where
     torch has no plain matmul for the type.  A yardstick for the bench only; the package never calls it."""
-    if spec["dtype"] == "f8e4m3":
-        return None
     tb = bool(kw.get("transpose_b"))
+    if spec["dtype"] == "f8e4m3":
+        # FP8: torch._scaled_mm (cuBLASLt) wants A [M, K] row-major and B column-major, i.e. B stored [N, K]
+        if not tb or not hasattr(torch, "_scaled_mm"):
+            return None
+        one = torch.ones((), device=sets[0][0].device)
+
+        def step8(a, b, out):
+            torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=out.dtype)
+
+        try:
+            secs = time_device_steps(torch, step8, sets, steps, warmup, lambda: None)
+        except Exception as e:
+            return {"error": str(e)[:160]}
+        return {"tflops": spec["flops"] / (secs / steps) / 1e12, "ms_per_step": 1e3 * secs / steps,
+                "what": "torch._scaled_mm (cuBLASLt FP8) on the same buffer sets, unit scales, product only"}
 
     def step(a, b, out):
         torch.matmul(a, b.transpose(-1, -2) if tb else b, out=out)
