@@ -25,7 +25,7 @@ times only the CPU product.
 
 Other workloads (`--workload`): f32_1024, f16_4096_tn, bf16_4096_tn,
 bf16_dense_gelu, bf16_batched_qk, fp8_65536 (M split over the ranks), fp8_8192,
-f32_1024_ffma, f32_4096, f32_4096_ffma, bf16_1024x1024x8192 (split along K), and the HBM-bound kernels quant_fp8_64m,
+f32_1024_ffma, f32_4096, f32_4096_ffma, bf16_8192_tn, bf16_1024x1024x8192 (split along K), and the HBM-bound kernels quant_fp8_64m,
 activation_gelu_64m, bias_grad_8192x11008, softmax_131072x2048 and the fused attention
 attention_<batch x heads>x<sequence>x<head size>[_causal] (bf16; the listed shapes, default 64x2048x128).  `--trace FILE` also writes the
 launch timeline (SM120_TUNE_TRACE) of one launch of the workload to FILE.
@@ -62,6 +62,7 @@ WORKLOADS = {
     "f32_1024_ffma":   dict(M=1024, N=1024, K=1024, batch=1, dtype="f32", layout="nn", ffma=True, oracle_idx=1),
     "f32_4096":        dict(M=4096, N=4096, K=4096, batch=1, dtype="f32", layout="nn", oracle_idx=1),
     "f32_4096_ffma":   dict(M=4096, N=4096, K=4096, batch=1, dtype="f32", layout="nn", ffma=True, oracle_idx=1),
+    "bf16_8192_tn":    dict(M=8192, N=8192, K=8192, batch=1, dtype="bf16", layout="tn", oracle_idx=2),   # the shape the measured peak is taken on
     "bf16_1024x1024x8192": dict(M=1024, N=1024, K=8192, batch=1, dtype="bf16", layout="tn", oracle_idx=2),   # few tiles, long K: split-K
 }
 # attention_<batch x heads>x<sequence>x<head size>[_causal], bf16
